@@ -1,0 +1,159 @@
+/*
+ * jabas_b200 — C ABI of the B200 (sm_100a) gradient-path library, libjabas_b200.so.
+ *
+ * The reference (unist-ssl/JABAS on top of IIDP) is pure Python: it has no FFI of its
+ * own.  Each entry point below therefore names the reference call site whose sequence
+ * of stock PyTorch ops it replaces; the Python mirror of the reference's comm-hook,
+ * trainer and optimizer interfaces binds these symbols with ctypes.
+ *
+ * Conventions
+ *  - Every function returns 0 on success and a negative JABAS_E* code on failure;
+ *    jabas_last_error() then returns a message for the calling thread.
+ *  - Every `float*` / `double*` data argument is a DEVICE pointer owned by the caller.
+ *    Arrays of pointers (`const float* const*`) and all structs are HOST memory; they
+ *    are consumed before the call returns.
+ *  - `stream` is a cudaStream_t passed as void*.  Calls only enqueue work on it; they
+ *    never synchronise the device and never block on the GPU.
+ *  - Calls are thread-safe.  Calls that accumulate a statistic borrow a small
+ *    reduction workspace that the context keeps per stream, so two such calls race
+ *    only if the caller itself gives them the same `stat` accumulator on two streams.
+ *  - There is no CPU fallback: without a CUDA device jabas_ctx_create() fails.
+ */
+#ifndef JABAS_B200_H
+#define JABAS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define JABAS_API __attribute__((visibility("default")))
+#else
+#define JABAS_API
+#endif
+
+#define JABAS_B200_VERSION 1
+#define JABAS_MAX_VSW      16   /* virtual stream workers (model replicas) per GPU */
+#define JABAS_MAX_GROUPS   16   /* optimizer param groups per launch               */
+
+#define JABAS_OK         0
+#define JABAS_EINVAL    -1      /* bad argument (null, size, K, group index ...)   */
+#define JABAS_ECUDA     -2      /* a CUDA runtime call failed                      */
+#define JABAS_ENOMEM    -3      /* host or device allocation failed                */
+
+typedef struct jabas_ctx    jabas_ctx_t;
+typedef struct jabas_layout jabas_layout_t;
+
+/* One run of consecutive elements of a flat parameter buffer that belongs to one
+ * optimizer param group: the flat form of the group lists the reference builds at
+ * examples/resnet50/main.py:340-349 and examples/vit/main.py:405-423. */
+typedef struct {
+    uint64_t begin;     /* first element (inclusive), in elements of the flat buffer */
+    uint64_t end;       /* last element (exclusive)                                  */
+    uint32_t group;     /* index into the `groups` array of the update call          */
+    uint32_t reserved;
+} jabas_seg_t;
+
+/* Per-launch hyper-parameters of one param group: `param_groups[i]['lr']` is mutated
+ * every iteration by the reference (jabas/train/trainer.py:693-700). */
+typedef struct {
+    double  lr;
+    double  weight_decay;
+    int64_t step;       /* Adam/AdamW: step count AFTER this update's increment      */
+    int64_t reserved;
+} jabas_group_t;
+
+typedef struct {
+    double momentum;
+    double dampening;
+    int    nesterov;
+    int    first_step;  /* 1: momentum buffer is created from the gradient (m = d)   */
+} jabas_sgd_hp_t;
+
+typedef struct {
+    double beta1;
+    double beta2;
+    double eps;
+    int    decoupled;   /* 1: AdamW (p *= 1 - lr*wd); 0: Adam (g += wd*p)            */
+    int    reserved;
+} jabas_adam_hp_t;
+
+JABAS_API int         jabas_version(void);
+JABAS_API const char* jabas_last_error(void);
+
+/* Context: device id, SM count, per-stream reduction workspaces. */
+JABAS_API int jabas_ctx_create(int device, jabas_ctx_t** ctx);
+JABAS_API int jabas_ctx_destroy(jabas_ctx_t* ctx);
+
+/* Uploads a segment table covering [0, total) of a flat parameter buffer.  Segments
+ * must be sorted, non-empty and contiguous (seg[i].end == seg[i+1].begin).
+ * Synchronous (one small cudaMemcpy); call at set-up, not per iteration. */
+JABAS_API int jabas_layout_create(jabas_ctx_t* ctx, const jabas_seg_t* segs, int nseg, uint64_t total,
+                        jabas_layout_t** layout);
+JABAS_API int jabas_layout_destroy(jabas_layout_t* layout);
+
+/* Local aggregation of the K VSW gradient buckets of one GPU.
+ *   sum      = g[0] + g[1] + ... + g[K-1]       (fp32, ascending k: order is fixed)
+ *   out      = sum / divisor                    (IEEE division; out may alias g[0])
+ *   half_out = sum                              (nullable)
+ *   stat3   += (<E,O>, |E|^2, |O|^2), E/O = sum of the even-/odd-index VSWs divided by
+ *              half_divisor (nullable; the single-GPU form of the two-half statistic)
+ * Replaces: the IIDP reducer's local aggregation behind the hook layout of
+ * jabas/train/trainer.py:461-468, the `div_(T)` of iidp_allreduce_hook, and the
+ * `detach().clone()` of jabas/ddp_comm_hooks/similarity_allreduce.py:28. */
+JABAS_API int jabas_vsw_aggregate_f32(jabas_ctx_t* ctx, const float* const* grads, int K, float* out,
+                            float* half_out, uint64_t n, float divisor, float half_divisor,
+                            double* stat3, void* stream);
+
+/* x /= divisor in place.  Replaces `div_(T/2)` at
+ * jabas/ddp_comm_hooks/similarity_allreduce.py:32. */
+JABAS_API int jabas_div_f32(jabas_ctx_t* ctx, float* x, uint64_t n, float divisor, void* stream);
+
+/* Fused SGD(-momentum) update of n elements starting at element `base` of the flat
+ * buffer that `layout` describes (layout == NULL: every element is in group 0), with
+ * write-back of the new weights to all K replicas and, optionally, the two-half
+ * statistic in the same pass:
+ *   e = half[i] / half_divisor, o = 2*g[i] - e, stat3 += (<e,o>, |e|^2, |o|^2).
+ * w[0] is the main replica (read and written); w[1..K-1] are written only.
+ * m may be NULL iff hp->momentum == 0.  half and stat3 are both NULL or both set.
+ * Replaces: torch.optim.SGD.step / ShardSGD.step(gradients)
+ * (examples/resnet50/main.py:351-359), the weight copy main -> VSWs
+ * (jabas/train/trainer.py:530-534) and, for the statistic, the cat / all_gather /
+ * cosine_similarity of jabas/train/trainer.py:470-483. */
+JABAS_API int jabas_sgd_momentum_f32(jabas_ctx_t* ctx, const float* g, float* const* w, int K, float* m,
+                           uint64_t n, uint64_t base, const jabas_layout_t* layout,
+                           const jabas_group_t* groups, int ngroups, const jabas_sgd_hp_t* hp,
+                           const float* half, float half_divisor, double* stat3, void* stream);
+
+/* Fused Adam / AdamW update; same contract as jabas_sgd_momentum_f32.
+ * Replaces: torch.optim.AdamW / ShardAdamW (examples/vit/main.py:433-437),
+ * torch.optim.Adam (examples/gnmt/train.py:786-792) and the body of
+ * ShardGNMTAdam.step (examples/gnmt/seq2seq/train/shard_optimizer.py:30-90). */
+JABAS_API int jabas_adam_f32(jabas_ctx_t* ctx, const float* g, float* const* w, int K, float* m, float* v,
+                   uint64_t n, uint64_t base, const jabas_layout_t* layout,
+                   const jabas_group_t* groups, int ngroups, const jabas_adam_hp_t* hp,
+                   const float* half, float half_divisor, double* stat3, void* stream);
+
+/* stat3 += (<a,b>, |a|^2, |b|^2).  Replaces the three reductions inside
+ * F.cosine_similarity at jabas/train/trainer.py:478. */
+JABAS_API int jabas_dot_norms_f32(jabas_ctx_t* ctx, const float* a, const float* b, uint64_t n,
+                        double* stat3, void* stream);
+
+/* cos_out[0] = stat3[0] / sqrt(max(stat3[1]*stat3[2], eps^2)), evaluated in fp64.
+ * Replaces the final division of F.cosine_similarity (jabas/train/trainer.py:478). */
+JABAS_API int jabas_cosine_finalize(jabas_ctx_t* ctx, const double* stat3, double eps, float* cos_out,
+                          void* stream);
+
+/* dst[k][i] = src[i] for k < ndst (entries equal to src are skipped): one read of the
+ * main replica, ndst writes.  Replaces the per-parameter copy loop of
+ * jabas/train/trainer.py:530-534 (IIDP's `copy_time` stage). */
+JABAS_API int jabas_replicate_f32(jabas_ctx_t* ctx, const float* src, float* const* dst, int ndst,
+                        uint64_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JABAS_B200_H */

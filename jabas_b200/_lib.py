@@ -1,0 +1,94 @@
+"""ctypes binding of ``libjabas_b200.so`` (declarations: ``include/jabas_b200.h``).
+
+The library is the only implementation of the gradient path: if it cannot be loaded
+this module raises, and nothing in the package substitutes a PyTorch or CPU path.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, "libjabas_b200.so")
+
+MAX_VSW = 16
+MAX_GROUPS = 16
+
+#: every symbol ``include/jabas_b200.h`` declares
+EXPORTS = (
+    "jabas_version", "jabas_last_error", "jabas_ctx_create", "jabas_ctx_destroy",
+    "jabas_layout_create", "jabas_layout_destroy", "jabas_vsw_aggregate_f32", "jabas_div_f32",
+    "jabas_sgd_momentum_f32", "jabas_adam_f32", "jabas_dot_norms_f32", "jabas_cosine_finalize",
+    "jabas_replicate_f32",
+)
+
+
+class Seg(ctypes.Structure):
+    _fields_ = [("begin", ctypes.c_uint64), ("end", ctypes.c_uint64),
+                ("group", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
+
+
+class Group(ctypes.Structure):
+    _fields_ = [("lr", ctypes.c_double), ("weight_decay", ctypes.c_double),
+                ("step", ctypes.c_int64), ("reserved", ctypes.c_int64)]
+
+
+class SgdHp(ctypes.Structure):
+    _fields_ = [("momentum", ctypes.c_double), ("dampening", ctypes.c_double),
+                ("nesterov", ctypes.c_int), ("first_step", ctypes.c_int)]
+
+
+class AdamHp(ctypes.Structure):
+    _fields_ = [("beta1", ctypes.c_double), ("beta2", ctypes.c_double), ("eps", ctypes.c_double),
+                ("decoupled", ctypes.c_int), ("reserved", ctypes.c_int)]
+
+
+class JabasError(RuntimeError):
+    """A libjabas_b200 call returned a negative status."""
+
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library once and declare every prototype."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m jabas_b200.build` "
+            "(nvcc, sm_100a). There is no fallback implementation.")
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, u64, f32, i32, f64 = (ctypes.c_void_p, ctypes.c_uint64, ctypes.c_float, ctypes.c_int,
+                              ctypes.c_double)
+    pvp = ctypes.POINTER(ctypes.c_void_p)
+    lib.jabas_version.argtypes = []
+    lib.jabas_last_error.argtypes = []
+    lib.jabas_last_error.restype = ctypes.c_char_p
+    lib.jabas_ctx_create.argtypes = [i32, pvp]
+    lib.jabas_ctx_destroy.argtypes = [vp]
+    lib.jabas_layout_create.argtypes = [vp, ctypes.POINTER(Seg), i32, u64, pvp]
+    lib.jabas_layout_destroy.argtypes = [vp]
+    lib.jabas_vsw_aggregate_f32.argtypes = [vp, pvp, i32, vp, vp, u64, f32, f32, vp, vp]
+    lib.jabas_div_f32.argtypes = [vp, vp, u64, f32, vp]
+    lib.jabas_sgd_momentum_f32.argtypes = [vp, vp, pvp, i32, vp, u64, u64, vp,
+                                           ctypes.POINTER(Group), i32, ctypes.POINTER(SgdHp),
+                                           vp, f32, vp, vp]
+    lib.jabas_adam_f32.argtypes = [vp, vp, pvp, i32, vp, vp, u64, u64, vp,
+                                   ctypes.POINTER(Group), i32, ctypes.POINTER(AdamHp),
+                                   vp, f32, vp, vp]
+    lib.jabas_dot_norms_f32.argtypes = [vp, vp, vp, u64, vp, vp]
+    lib.jabas_cosine_finalize.argtypes = [vp, vp, f64, vp, vp]
+    lib.jabas_replicate_f32.argtypes = [vp, vp, pvp, i32, u64, vp]
+    for name in EXPORTS:
+        if name != "jabas_last_error":
+            getattr(lib, name).restype = i32
+    _lib = lib
+    return lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        msg = load().jabas_last_error()
+        raise JabasError(f"libjabas_b200 error {rc}: {msg.decode() if msg else '?'}")

@@ -1,0 +1,942 @@
+// Gradient-path kernels for B200 (sm_100a) and their C ABI (include/jabas_b200.h).
+//
+// Everything here is HBM-bound streaming work: no tensor cores, no shared-memory
+// tiling beyond the reduction trees.  Design points:
+//   * 128-bit loads/stores, block-cyclic tiles so that a warp always touches 512
+//     contiguous bytes per stream, all loads of a tile issued before the first use;
+//   * grids of (SM count x resident CTAs) persistent CTAs walking the buffer;
+//   * fp32 arithmetic written with explicit-rounding intrinsics (__fmaf_rn, __fmul_rn,
+//     __fadd_rn, __fdiv_rn, __fsqrt_rn) so that the result is bit-identical to the CPU
+//     oracle whatever the compiler's contraction rules are;
+//   * the three sums of the cosine statistic accumulate in fp64 per thread, reduce by
+//     warp shuffle and a shared-memory tree to one partial per CTA, and the last CTA
+//     to finish (ticket counter) adds the partials in index order: the result does
+//     not depend on scheduling.
+#include "jabas_b200.h"
+
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kMaxCtasPerSm = 8;
+
+thread_local std::string g_err;
+
+int fail(int code, const std::string& msg)
+{
+    g_err = msg;
+    return code;
+}
+
+#define JB_CUDA(expr)                                                                     \
+    do {                                                                                  \
+        cudaError_t e__ = (expr);                                                         \
+        if (e__ != cudaSuccess)                                                           \
+            return fail(JABAS_ECUDA, std::string(#expr) + ": " + cudaGetErrorString(e__)); \
+    } while (0)
+
+// ----------------------------------------------------------------------------------
+// device helpers
+// ----------------------------------------------------------------------------------
+
+// Plain (coherent) 128-bit load that does not allocate in L1: every input is read once
+// per launch, and outputs may alias inputs, which rules out the non-coherent path.
+__device__ __forceinline__ float4 ld4(const float* p)
+{
+    float4 v;
+    asm volatile("ld.global.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void st4(float* p, float4 v)
+{
+    *reinterpret_cast<float4*>(p) = v;
+}
+
+struct Acc3 {
+    double d, a, b;
+};
+
+struct StatWs {
+    double* partials;       // 3 doubles per CTA
+    unsigned int* counter;  // ticket, returns to 0 at the end of every launch
+};
+
+__device__ __forceinline__ void acc_vec(Acc3& acc, float4 e, float4 o)
+{
+    float d = __fmul_rn(e.x, o.x), a = __fmul_rn(e.x, e.x), b = __fmul_rn(o.x, o.x);
+    d = __fmaf_rn(e.y, o.y, d); a = __fmaf_rn(e.y, e.y, a); b = __fmaf_rn(o.y, o.y, b);
+    d = __fmaf_rn(e.z, o.z, d); a = __fmaf_rn(e.z, e.z, a); b = __fmaf_rn(o.z, o.z, b);
+    d = __fmaf_rn(e.w, o.w, d); a = __fmaf_rn(e.w, e.w, a); b = __fmaf_rn(o.w, o.w, b);
+    acc.d += (double)d; acc.a += (double)a; acc.b += (double)b;
+}
+__device__ __forceinline__ void acc_one(Acc3& acc, float e, float o)
+{
+    acc.d += (double)e * (double)o; acc.a += (double)e * (double)e; acc.b += (double)o * (double)o;
+}
+
+__device__ __forceinline__ Acc3 warp_sum(Acc3 v)
+{
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        v.d += __shfl_down_sync(0xffffffffu, v.d, off);
+        v.a += __shfl_down_sync(0xffffffffu, v.a, off);
+        v.b += __shfl_down_sync(0xffffffffu, v.b, off);
+    }
+    return v;
+}
+
+// CTA-wide sum, valid in thread 0.
+__device__ __forceinline__ Acc3 block_sum(Acc3 v, double (*sm)[kWarps])
+{
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) { sm[0][warp] = v.d; sm[1][warp] = v.a; sm[2][warp] = v.b; }
+    __syncthreads();
+    Acc3 r = {0.0, 0.0, 0.0};
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) { r.d += sm[0][w]; r.a += sm[1][w]; r.b += sm[2][w]; }
+    }
+    return r;
+}
+
+// One partial per CTA; the last CTA to arrive adds them in CTA order into stat3.
+__device__ __forceinline__ void stat_finish(Acc3 acc, StatWs ws, double* stat3)
+{
+    __shared__ double sm[3][kWarps];
+    __shared__ int is_last;
+    Acc3 r = block_sum(acc, sm);
+    if (threadIdx.x == 0) {
+        ws.partials[3 * blockIdx.x + 0] = r.d;
+        ws.partials[3 * blockIdx.x + 1] = r.a;
+        ws.partials[3 * blockIdx.x + 2] = r.b;
+        __threadfence();
+        const unsigned int t = atomicAdd(ws.counter, 1u);
+        is_last = (t == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    Acc3 t = {0.0, 0.0, 0.0};
+    for (unsigned int i = threadIdx.x; i < gridDim.x; i += kThreads) {
+        t.d += __ldcg(ws.partials + 3 * i + 0);
+        t.a += __ldcg(ws.partials + 3 * i + 1);
+        t.b += __ldcg(ws.partials + 3 * i + 2);
+    }
+    t = block_sum(t, sm);
+    if (threadIdx.x == 0) {
+        stat3[0] += t.d; stat3[1] += t.a; stat3[2] += t.b;
+        *ws.counter = 0u;
+    }
+}
+
+// ----------------------------------------------------------------------------------
+// K-VSW aggregation
+// ----------------------------------------------------------------------------------
+
+struct AggArgs {
+    const float* g[JABAS_MAX_VSW];
+    float* out;
+    float* half;     // nullable
+    double* stat;    // nullable (STAT kernels only)
+    StatWs ws;
+    unsigned long long n;
+    float divisor;
+    float half_divisor;
+    int K;
+};
+
+__host__ __device__ constexpr int agg_unroll(int K) { return K <= 2 ? 4 : (K <= 4 ? 2 : 1); }
+
+__device__ __forceinline__ float4 add4(float4 a, float4 b)
+{
+    return make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w));
+}
+__device__ __forceinline__ float4 div4(float4 a, float d)
+{
+    return make_float4(__fdiv_rn(a.x, d), __fdiv_rn(a.y, d), __fdiv_rn(a.z, d), __fdiv_rn(a.w, d));
+}
+
+// Per-element form: the tail of the vector kernel and the whole of the unaligned path.
+template <bool STAT>
+__device__ __forceinline__ void agg_elem(const AggArgs& a, unsigned long long i, Acc3& acc)
+{
+    float s = a.g[0][i];
+    float e = s, o = 0.0f;
+    for (int k = 1; k < a.K; ++k) {
+        const float x = a.g[k][i];
+        s = __fadd_rn(s, x);
+        if (STAT) {
+            if (k == 1) o = x;
+            else if (k & 1) o = __fadd_rn(o, x);
+            else e = __fadd_rn(e, x);
+        }
+    }
+    if (a.half) a.half[i] = s;
+    a.out[i] = __fdiv_rn(s, a.divisor);
+    if (STAT) acc_one(acc, __fdiv_rn(e, a.half_divisor), __fdiv_rn(o, a.half_divisor));
+}
+
+template <int K, bool STAT>
+__global__ void __launch_bounds__(kThreads) agg_vec_kernel(const AggArgs a)
+{
+    constexpr int U = agg_unroll(K);
+    const unsigned long long nvec = a.n >> 2;
+    const unsigned long long tile = (unsigned long long)kThreads * U;
+    Acc3 acc = {0.0, 0.0, 0.0};
+    for (unsigned long long t0 = (unsigned long long)blockIdx.x * tile; t0 < nvec;
+         t0 += (unsigned long long)gridDim.x * tile) {
+        float4 x[U][K];
+        const bool full = t0 + tile <= nvec;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const unsigned long long v = t0 + (unsigned long long)u * kThreads + threadIdx.x;
+            if (full || v < nvec) {
+#pragma unroll
+                for (int k = 0; k < K; ++k) x[u][k] = ld4(a.g[k] + 4 * v);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const unsigned long long v = t0 + (unsigned long long)u * kThreads + threadIdx.x;
+            if (full || v < nvec) {
+                float4 s = x[u][0];
+#pragma unroll
+                for (int k = 1; k < K; ++k) s = add4(s, x[u][k]);
+                if (a.half) st4(a.half + 4 * v, s);
+                st4(a.out + 4 * v, div4(s, a.divisor));
+                if (STAT) {
+                    float4 e = x[u][0];
+                    float4 o = K > 1 ? x[u][K > 1 ? 1 : 0] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int k = 2; k < K; ++k) {
+                        if (k & 1) o = add4(o, x[u][k]); else e = add4(e, x[u][k]);
+                    }
+                    acc_vec(acc, div4(e, a.half_divisor), div4(o, a.half_divisor));
+                }
+            }
+        }
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (a.n & 3ull))
+        agg_elem<STAT>(a, (nvec << 2) + threadIdx.x, acc);
+    if (STAT) stat_finish(acc, a.ws, a.stat);
+}
+
+template <bool STAT>
+__global__ void __launch_bounds__(kThreads) agg_scalar_kernel(const AggArgs a)
+{
+    Acc3 acc = {0.0, 0.0, 0.0};
+    for (unsigned long long i = (unsigned long long)blockIdx.x * kThreads + threadIdx.x; i < a.n;
+         i += (unsigned long long)gridDim.x * kThreads)
+        agg_elem<STAT>(a, i, acc);
+    if (STAT) stat_finish(acc, a.ws, a.stat);
+}
+
+// ----------------------------------------------------------------------------------
+// fused optimizer update + write-back + statistic
+// ----------------------------------------------------------------------------------
+
+struct SegDev {
+    unsigned long long begin, end;
+    unsigned int group, pad;
+};
+
+struct GroupDev {
+    float wd;      // weight decay
+    float s0;      // SGD: -lr             Adam: 1 - lr*wd (decoupled decay factor)
+    float s1;      // SGD: unused          Adam: -(lr / (1 - beta1^t))
+    float s2;      // SGD: unused          Adam: sqrt(1 - beta2^t)
+};
+
+enum { OPT_SGD = 0, OPT_ADAM = 1 };
+enum { F_NESTEROV = 1, F_FIRST = 2, F_MOMENTUM = 4, F_DECOUPLED = 8 };
+
+struct UpdArgs {
+    const float* g;
+    float* w[JABAS_MAX_VSW];
+    float* m;
+    float* v;
+    const float* half;   // nullable
+    double* stat;
+    StatWs ws;
+    const SegDev* segs;  // nullable: one group
+    unsigned long long n, base;
+    int nseg;
+    int K;
+    unsigned int flags;
+    unsigned int wd_mask;     // bit i: group i has weight_decay != 0
+    float c0, c1, c2, c3, c4; // SGD: mu, 1-dampening | Adam: b1, b2, 1-b1, 1-b2, eps
+    float half_divisor;
+    GroupDev grp[JABAS_MAX_GROUPS];
+};
+
+// index of the segment that holds element `idx` (segments are contiguous and sorted)
+__device__ __forceinline__ int seg_find(const SegDev* segs, int nseg, unsigned long long idx)
+{
+    int lo = 0, hi = nseg - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (__ldg(&segs[mid].end) <= idx) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+}
+
+template <int OPT>
+__device__ __forceinline__ void upd_math(const UpdArgs& a, const GroupDev& h, bool has_wd, float g,
+                                         float& p, float& m, float& v)
+{
+    if (OPT == OPT_SGD) {
+        float d = g;
+        if (has_wd) d = __fmaf_rn(h.wd, p, d);
+        if (a.flags & F_MOMENTUM) {
+            float b;
+            if (a.flags & F_FIRST) b = d;
+            else b = __fmaf_rn(a.c1, d, __fmul_rn(a.c0, m));
+            m = b;
+            d = (a.flags & F_NESTEROV) ? __fmaf_rn(a.c0, b, d) : b;
+        }
+        p = __fmaf_rn(h.s0, d, p);
+    } else {
+        if (a.flags & F_DECOUPLED) p = __fmul_rn(p, h.s0);
+        else if (has_wd) g = __fmaf_rn(h.wd, p, g);
+        m = __fmaf_rn(a.c2, g, __fmul_rn(a.c0, m));
+        v = __fmaf_rn(__fmul_rn(a.c3, g), g, __fmul_rn(a.c1, v));
+        const float denom = __fadd_rn(__fdiv_rn(__fsqrt_rn(v), h.s2), a.c4);
+        p = __fmaf_rn(h.s1, __fdiv_rn(m, denom), p);
+    }
+}
+
+template <int OPT>
+__device__ __forceinline__ void upd_math4(const UpdArgs& a, const GroupDev& h, bool has_wd, float4 g,
+                                          float4& p, float4& m, float4& v)
+{
+    upd_math<OPT>(a, h, has_wd, g.x, p.x, m.x, v.x);
+    upd_math<OPT>(a, h, has_wd, g.y, p.y, m.y, v.y);
+    upd_math<OPT>(a, h, has_wd, g.z, p.z, m.z, v.z);
+    upd_math<OPT>(a, h, has_wd, g.w, p.w, m.w, v.w);
+}
+
+template <bool STAT>
+__device__ __forceinline__ void half_stat4(const UpdArgs& a, float4 g, float4 hs, Acc3& acc)
+{
+    if (!STAT) return;
+    const float4 e = div4(hs, a.half_divisor);
+    const float4 o = make_float4(__fmaf_rn(2.0f, g.x, -e.x), __fmaf_rn(2.0f, g.y, -e.y),
+                                 __fmaf_rn(2.0f, g.z, -e.z), __fmaf_rn(2.0f, g.w, -e.w));
+    acc_vec(acc, e, o);
+}
+
+// Per-element form (tail, unaligned path, tiles that straddle a segment boundary).
+template <int OPT, bool STAT>
+__device__ __forceinline__ void upd_elem(const UpdArgs& a, unsigned long long i, int seg, Acc3& acc)
+{
+    int gi = 0;
+    if (a.segs) {
+        while (__ldg(&a.segs[seg].end) <= a.base + i) ++seg;
+        gi = (int)__ldg(&a.segs[seg].group);
+    }
+    const float g = a.g[i];
+    float p = a.w[0][i];
+    float m = (OPT == OPT_ADAM || ((a.flags & F_MOMENTUM) && !(a.flags & F_FIRST))) ? a.m[i] : 0.0f;
+    float v = OPT == OPT_ADAM ? a.v[i] : 0.0f;
+    upd_math<OPT>(a, a.grp[gi], (a.wd_mask >> gi) & 1u, g, p, m, v);
+    for (int k = 0; k < a.K; ++k) a.w[k][i] = p;
+    if (OPT == OPT_ADAM || (a.flags & F_MOMENTUM)) a.m[i] = m;
+    if (OPT == OPT_ADAM) a.v[i] = v;
+    if (STAT) {
+        const float e = __fdiv_rn(a.half[i], a.half_divisor);
+        acc_one(acc, e, __fmaf_rn(2.0f, g, -e));
+    }
+}
+
+template <int OPT, bool STAT, int U>
+__global__ void __launch_bounds__(kThreads) upd_vec_kernel(const UpdArgs a)
+{
+    const unsigned long long nvec = a.n >> 2;
+    const unsigned long long tile = (unsigned long long)kThreads * U;
+    const bool use_m = OPT == OPT_ADAM || (a.flags & F_MOMENTUM);
+    const bool load_m = OPT == OPT_ADAM || ((a.flags & F_MOMENTUM) && !(a.flags & F_FIRST));
+    Acc3 acc = {0.0, 0.0, 0.0};
+    for (unsigned long long t0 = (unsigned long long)blockIdx.x * tile; t0 < nvec;
+         t0 += (unsigned long long)gridDim.x * tile) {
+        const bool full = t0 + tile <= nvec;
+        float4 g[U], p[U], m[U], v[U], hs[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const unsigned long long x = t0 + (unsigned long long)u * kThreads + threadIdx.x;
+            m[u] = v[u] = hs[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (full || x < nvec) {
+                g[u] = ld4(a.g + 4 * x);
+                p[u] = ld4(a.w[0] + 4 * x);
+                if (load_m) m[u] = ld4(a.m + 4 * x);
+                if (OPT == OPT_ADAM) v[u] = ld4(a.v + 4 * x);
+                if (STAT) hs[u] = ld4(a.half + 4 * x);
+            }
+        }
+        // segment of the tile's first element; uniform over the CTA
+        int seg0 = 0, gi0 = 0;
+        bool uniform = true;
+        if (a.segs) {
+            const unsigned long long e0 = a.base + 4 * t0;
+            unsigned long long e1 = a.base + 4 * (t0 + tile);
+            if (e1 > a.base + a.n) e1 = a.base + a.n;
+            seg0 = seg_find(a.segs, a.nseg, e0);
+            uniform = __ldg(&a.segs[seg0].end) >= e1;
+            gi0 = (int)__ldg(&a.segs[seg0].group);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const unsigned long long x = t0 + (unsigned long long)u * kThreads + threadIdx.x;
+            if (!(full || x < nvec)) continue;
+            half_stat4<STAT>(a, g[u], hs[u], acc);
+            if (uniform) {
+                upd_math4<OPT>(a, a.grp[gi0], (a.wd_mask >> gi0) & 1u, g[u], p[u], m[u], v[u]);
+            } else {
+                int s = seg0;
+                auto one = [&](int c, float gx, float& px, float& mx, float& vx) {
+                    while (__ldg(&a.segs[s].end) <= a.base + 4 * x + c) ++s;
+                    const int gi = (int)__ldg(&a.segs[s].group);
+                    upd_math<OPT>(a, a.grp[gi], (a.wd_mask >> gi) & 1u, gx, px, mx, vx);
+                };
+                one(0, g[u].x, p[u].x, m[u].x, v[u].x);
+                one(1, g[u].y, p[u].y, m[u].y, v[u].y);
+                one(2, g[u].z, p[u].z, m[u].z, v[u].z);
+                one(3, g[u].w, p[u].w, m[u].w, v[u].w);
+            }
+            for (int k = 0; k < a.K; ++k) st4(a.w[k] + 4 * x, p[u]);
+            if (use_m) st4(a.m + 4 * x, m[u]);
+            if (OPT == OPT_ADAM) st4(a.v + 4 * x, v[u]);
+        }
+    }
+    const unsigned int rem = (unsigned int)(a.n & 3ull);
+    if (blockIdx.x == 0 && threadIdx.x < rem) {
+        const unsigned long long i = (nvec << 2) + threadIdx.x;
+        upd_elem<OPT, STAT>(a, i, a.segs ? seg_find(a.segs, a.nseg, a.base + i) : 0, acc);
+    }
+    if (STAT) stat_finish(acc, a.ws, a.stat);
+}
+
+template <int OPT, bool STAT>
+__global__ void __launch_bounds__(kThreads) upd_scalar_kernel(const UpdArgs a)
+{
+    Acc3 acc = {0.0, 0.0, 0.0};
+    for (unsigned long long i = (unsigned long long)blockIdx.x * kThreads + threadIdx.x; i < a.n;
+         i += (unsigned long long)gridDim.x * kThreads)
+        upd_elem<OPT, STAT>(a, i, a.segs ? seg_find(a.segs, a.nseg, a.base + i) : 0, acc);
+    if (STAT) stat_finish(acc, a.ws, a.stat);
+}
+
+// ----------------------------------------------------------------------------------
+// small kernels: in-place division, dot/norms, finalize, replicate
+// ----------------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(kThreads) div_kernel(float* x, unsigned long long n, float d, int vec)
+{
+    const unsigned long long tid = (unsigned long long)blockIdx.x * kThreads + threadIdx.x;
+    const unsigned long long stride = (unsigned long long)gridDim.x * kThreads;
+    if (vec) {
+        const unsigned long long nvec = n >> 2;
+        for (unsigned long long i = tid; i < nvec; i += stride) st4(x + 4 * i, div4(ld4(x + 4 * i), d));
+        if (tid < (n & 3ull)) x[(nvec << 2) + tid] = __fdiv_rn(x[(nvec << 2) + tid], d);
+    } else {
+        for (unsigned long long i = tid; i < n; i += stride) x[i] = __fdiv_rn(x[i], d);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) dot_norms_kernel(const float* a, const float* b,
+                                                             unsigned long long n, int vec,
+                                                             StatWs ws, double* stat)
+{
+    constexpr int U = 4;
+    Acc3 acc = {0.0, 0.0, 0.0};
+    if (vec) {
+        const unsigned long long nvec = n >> 2;
+        const unsigned long long tile = (unsigned long long)kThreads * U;
+        for (unsigned long long t0 = (unsigned long long)blockIdx.x * tile; t0 < nvec;
+             t0 += (unsigned long long)gridDim.x * tile) {
+            float4 x[U], y[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const unsigned long long i = t0 + (unsigned long long)u * kThreads + threadIdx.x;
+                x[u] = y[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (i < nvec) { x[u] = ld4(a + 4 * i); y[u] = ld4(b + 4 * i); }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) acc_vec(acc, x[u], y[u]);
+        }
+        if (blockIdx.x == 0 && threadIdx.x < (n & 3ull)) {
+            const unsigned long long i = (nvec << 2) + threadIdx.x;
+            acc_one(acc, a[i], b[i]);
+        }
+    } else {
+        for (unsigned long long i = (unsigned long long)blockIdx.x * kThreads + threadIdx.x; i < n;
+             i += (unsigned long long)gridDim.x * kThreads)
+            acc_one(acc, a[i], b[i]);
+    }
+    stat_finish(acc, ws, stat);
+}
+
+__global__ void cosine_finalize_kernel(const double* stat, double eps, float* out)
+{
+    double den = stat[1] * stat[2];
+    if (den < eps * eps) den = eps * eps;
+    out[0] = (float)(stat[0] / sqrt(den));
+}
+
+struct RepArgs {
+    const float* src;
+    float* dst[JABAS_MAX_VSW];
+    int ndst;
+    int vec;
+    unsigned long long n;
+};
+
+__global__ void __launch_bounds__(kThreads) replicate_kernel(const RepArgs a)
+{
+    constexpr int U = 4;
+    if (a.vec) {
+        const unsigned long long nvec = a.n >> 2;
+        const unsigned long long tile = (unsigned long long)kThreads * U;
+        for (unsigned long long t0 = (unsigned long long)blockIdx.x * tile; t0 < nvec;
+             t0 += (unsigned long long)gridDim.x * tile) {
+            float4 x[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const unsigned long long i = t0 + (unsigned long long)u * kThreads + threadIdx.x;
+                if (i < nvec) x[u] = ld4(a.src + 4 * i);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const unsigned long long i = t0 + (unsigned long long)u * kThreads + threadIdx.x;
+                if (i < nvec)
+                    for (int k = 0; k < a.ndst; ++k) st4(a.dst[k] + 4 * i, x[u]);
+            }
+        }
+        if (blockIdx.x == 0 && threadIdx.x < (a.n & 3ull)) {
+            const unsigned long long i = (nvec << 2) + threadIdx.x;
+            for (int k = 0; k < a.ndst; ++k) a.dst[k][i] = a.src[i];
+        }
+    } else {
+        for (unsigned long long i = (unsigned long long)blockIdx.x * kThreads + threadIdx.x; i < a.n;
+             i += (unsigned long long)gridDim.x * kThreads)
+            for (int k = 0; k < a.ndst; ++k) a.dst[k][i] = a.src[i];
+    }
+}
+
+// ----------------------------------------------------------------------------------
+// host side
+// ----------------------------------------------------------------------------------
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+struct jabas_ctx {
+    int device = 0;
+    int sm_count = 0;
+    int max_grid = 0;
+    std::mutex mu;
+    std::unordered_map<void*, StatWs> ws;   // one reduction workspace per stream
+    std::unordered_map<const void*, int> occ;
+};
+
+struct jabas_layout {
+    int device = 0;
+    int nseg = 0;
+    unsigned long long total = 0;
+    SegDev* dsegs = nullptr;
+};
+
+namespace {
+
+int ctx_bind(jabas_ctx_t* ctx)
+{
+    if (!ctx) return fail(JABAS_EINVAL, "ctx is null");
+    int cur = -1;
+    JB_CUDA(cudaGetDevice(&cur));
+    if (cur != ctx->device) JB_CUDA(cudaSetDevice(ctx->device));
+    return JABAS_OK;
+}
+
+// Resident CTAs per SM of a kernel, cached per context.
+template <typename KernelT>
+int grid_for(jabas_ctx_t* ctx, KernelT kernel, unsigned long long work_items, unsigned long long per_cta,
+             int* grid)
+{
+    int per_sm = 0;
+    {
+        std::lock_guard<std::mutex> lk(ctx->mu);
+        auto it = ctx->occ.find(reinterpret_cast<const void*>(kernel));
+        if (it != ctx->occ.end()) per_sm = it->second;
+    }
+    if (per_sm == 0) {
+        JB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0));
+        if (per_sm < 1) per_sm = 1;
+        if (per_sm > kMaxCtasPerSm) per_sm = kMaxCtasPerSm;
+        std::lock_guard<std::mutex> lk(ctx->mu);
+        ctx->occ[reinterpret_cast<const void*>(kernel)] = per_sm;
+    }
+    unsigned long long need = (work_items + per_cta - 1) / per_cta;
+    if (need < 1) need = 1;
+    const unsigned long long cap = (unsigned long long)ctx->sm_count * per_sm;
+    *grid = (int)(need < cap ? need : cap);
+    return JABAS_OK;
+}
+
+int ws_for(jabas_ctx_t* ctx, void* stream, StatWs* out)
+{
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    auto it = ctx->ws.find(stream);
+    if (it != ctx->ws.end()) { *out = it->second; return JABAS_OK; }
+    StatWs w{};
+    char* raw = nullptr;
+    const size_t bytes = 256 + sizeof(double) * 3 * (size_t)ctx->max_grid;
+    JB_CUDA(cudaMalloc(&raw, bytes));
+    cudaError_t e = cudaMemset(raw, 0, bytes);
+    if (e != cudaSuccess) { cudaFree(raw); return fail(JABAS_ECUDA, cudaGetErrorString(e)); }
+    w.counter = reinterpret_cast<unsigned int*>(raw);
+    w.partials = reinterpret_cast<double*>(raw + 256);
+    ctx->ws[stream] = w;
+    *out = w;
+    return JABAS_OK;
+}
+
+template <int K>
+struct AggLaunch {
+    static int run(jabas_ctx_t* ctx, const AggArgs& a, cudaStream_t st)
+    {
+        constexpr int U = agg_unroll(K);
+        int grid = 0, rc;
+        if (a.stat) {
+            if ((rc = grid_for(ctx, agg_vec_kernel<K, true>, a.n >> 2, (unsigned long long)kThreads * U, &grid))) return rc;
+            agg_vec_kernel<K, true><<<grid, kThreads, 0, st>>>(a);
+        } else {
+            if ((rc = grid_for(ctx, agg_vec_kernel<K, false>, a.n >> 2, (unsigned long long)kThreads * U, &grid))) return rc;
+            agg_vec_kernel<K, false><<<grid, kThreads, 0, st>>>(a);
+        }
+        return JABAS_OK;
+    }
+};
+
+template <int K>
+int agg_dispatch(jabas_ctx_t* ctx, const AggArgs& a, cudaStream_t st)
+{
+    if (a.K == K) return AggLaunch<K>::run(ctx, a, st);
+    if constexpr (K < JABAS_MAX_VSW) return agg_dispatch<K + 1>(ctx, a, st);
+    return fail(JABAS_EINVAL, "K out of range");
+}
+
+template <int OPT>
+int upd_launch(jabas_ctx_t* ctx, const UpdArgs& a, bool vec, cudaStream_t st)
+{
+    constexpr int U = OPT == OPT_SGD ? 2 : 2;
+    int grid = 0, rc;
+    if (vec) {
+        if (a.stat) {
+            if ((rc = grid_for(ctx, upd_vec_kernel<OPT, true, U>, a.n >> 2, (unsigned long long)kThreads * U, &grid))) return rc;
+            upd_vec_kernel<OPT, true, U><<<grid, kThreads, 0, st>>>(a);
+        } else {
+            if ((rc = grid_for(ctx, upd_vec_kernel<OPT, false, U>, a.n >> 2, (unsigned long long)kThreads * U, &grid))) return rc;
+            upd_vec_kernel<OPT, false, U><<<grid, kThreads, 0, st>>>(a);
+        }
+    } else {
+        if (a.stat) {
+            if ((rc = grid_for(ctx, upd_scalar_kernel<OPT, true>, a.n, kThreads, &grid))) return rc;
+            upd_scalar_kernel<OPT, true><<<grid, kThreads, 0, st>>>(a);
+        } else {
+            if ((rc = grid_for(ctx, upd_scalar_kernel<OPT, false>, a.n, kThreads, &grid))) return rc;
+            upd_scalar_kernel<OPT, false><<<grid, kThreads, 0, st>>>(a);
+        }
+    }
+    JB_CUDA(cudaGetLastError());
+    return JABAS_OK;
+}
+
+// Validation and argument marshalling shared by the two optimizers.
+int upd_prepare(jabas_ctx_t* ctx, UpdArgs& a, bool* vec, const float* g, float* const* w, int K,
+                float* m, float* v, uint64_t n, uint64_t base, const jabas_layout_t* layout,
+                const jabas_group_t* groups, int ngroups, const float* half, float half_divisor,
+                double* stat3, void* stream)
+{
+    int rc = ctx_bind(ctx);
+    if (rc) return rc;
+    if (!g || !w) return fail(JABAS_EINVAL, "g or w is null");
+    if (K < 1 || K > JABAS_MAX_VSW) return fail(JABAS_EINVAL, "K must be in [1, JABAS_MAX_VSW]");
+    if (!groups || ngroups < 1 || ngroups > JABAS_MAX_GROUPS)
+        return fail(JABAS_EINVAL, "ngroups must be in [1, JABAS_MAX_GROUPS]");
+    if ((half == nullptr) != (stat3 == nullptr))
+        return fail(JABAS_EINVAL, "half and stat3 must both be set or both be null");
+    if (half && !(half_divisor != 0.0f)) return fail(JABAS_EINVAL, "half_divisor must be non-zero");
+    std::memset(&a, 0, sizeof(a));
+    a.g = g; a.m = m; a.v = v; a.half = half; a.stat = stat3;
+    a.n = n; a.base = base; a.K = K; a.half_divisor = half_divisor;
+    *vec = aligned16(g) && (!m || aligned16(m)) && (!v || aligned16(v)) && (!half || aligned16(half));
+    for (int k = 0; k < K; ++k) {
+        if (!w[k]) return fail(JABAS_EINVAL, "w[k] is null");
+        a.w[k] = w[k];
+        *vec = *vec && aligned16(w[k]);
+    }
+    if (layout) {
+        if (layout->device != ctx->device) return fail(JABAS_EINVAL, "layout belongs to another device");
+        if (base + n > layout->total) return fail(JABAS_EINVAL, "base + n exceeds the layout");
+        a.segs = layout->dsegs; a.nseg = layout->nseg;
+    }
+    if (stat3 && (rc = ws_for(ctx, stream, &a.ws))) return rc;
+    return JABAS_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int jabas_version(void) { return JABAS_B200_VERSION; }
+
+const char* jabas_last_error(void) { return g_err.c_str(); }
+
+int jabas_ctx_create(int device, jabas_ctx_t** out)
+{
+    if (!out) return fail(JABAS_EINVAL, "ctx out pointer is null");
+    *out = nullptr;
+    int count = 0;
+    JB_CUDA(cudaGetDeviceCount(&count));
+    if (device < 0 || device >= count) return fail(JABAS_EINVAL, "no such CUDA device");
+    jabas_ctx_t* c = new (std::nothrow) jabas_ctx_t();
+    if (!c) return fail(JABAS_ENOMEM, "out of host memory");
+    c->device = device;
+    cudaError_t e = cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, device);
+    if (e != cudaSuccess) { delete c; return fail(JABAS_ECUDA, cudaGetErrorString(e)); }
+    c->max_grid = c->sm_count * kMaxCtasPerSm;
+    *out = c;
+    return JABAS_OK;
+}
+
+int jabas_ctx_destroy(jabas_ctx_t* ctx)
+{
+    if (!ctx) return JABAS_OK;
+    int rc = ctx_bind(ctx);
+    if (rc == JABAS_OK)
+        for (auto& kv : ctx->ws) cudaFree(kv.second.counter);
+    delete ctx;
+    return rc;
+}
+
+int jabas_layout_create(jabas_ctx_t* ctx, const jabas_seg_t* segs, int nseg, uint64_t total,
+                        jabas_layout_t** out)
+{
+    int rc = ctx_bind(ctx);
+    if (rc) return rc;
+    if (!out) return fail(JABAS_EINVAL, "layout out pointer is null");
+    *out = nullptr;
+    if (!segs || nseg < 1) return fail(JABAS_EINVAL, "empty segment table");
+    std::vector<SegDev> h((size_t)nseg);
+    uint64_t pos = 0;
+    for (int i = 0; i < nseg; ++i) {
+        if (segs[i].begin != pos || segs[i].end <= segs[i].begin)
+            return fail(JABAS_EINVAL, "segments must be sorted, non-empty and contiguous from 0");
+        if (segs[i].group >= JABAS_MAX_GROUPS) return fail(JABAS_EINVAL, "segment group out of range");
+        h[i].begin = segs[i].begin; h[i].end = segs[i].end; h[i].group = segs[i].group; h[i].pad = 0;
+        pos = segs[i].end;
+    }
+    if (pos != total) return fail(JABAS_EINVAL, "segments do not cover [0, total)");
+    jabas_layout_t* l = new (std::nothrow) jabas_layout_t();
+    if (!l) return fail(JABAS_ENOMEM, "out of host memory");
+    l->device = ctx->device; l->nseg = nseg; l->total = total;
+    cudaError_t e = cudaMalloc(&l->dsegs, sizeof(SegDev) * (size_t)nseg);
+    if (e == cudaSuccess) e = cudaMemcpy(l->dsegs, h.data(), sizeof(SegDev) * (size_t)nseg, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        if (l->dsegs) cudaFree(l->dsegs);
+        delete l;
+        return fail(JABAS_ECUDA, cudaGetErrorString(e));
+    }
+    *out = l;
+    return JABAS_OK;
+}
+
+int jabas_layout_destroy(jabas_layout_t* layout)
+{
+    if (!layout) return JABAS_OK;
+    int cur = -1;
+    if (cudaGetDevice(&cur) == cudaSuccess && cur != layout->device) cudaSetDevice(layout->device);
+    cudaFree(layout->dsegs);
+    delete layout;
+    return JABAS_OK;
+}
+
+int jabas_vsw_aggregate_f32(jabas_ctx_t* ctx, const float* const* grads, int K, float* out,
+                            float* half_out, uint64_t n, float divisor, float half_divisor,
+                            double* stat3, void* stream)
+{
+    int rc = ctx_bind(ctx);
+    if (rc) return rc;
+    if (!grads || !out) return fail(JABAS_EINVAL, "grads or out is null");
+    if (K < 1 || K > JABAS_MAX_VSW) return fail(JABAS_EINVAL, "K must be in [1, JABAS_MAX_VSW]");
+    if (!(divisor != 0.0f)) return fail(JABAS_EINVAL, "divisor must be non-zero");
+    if (stat3 && K < 2) return fail(JABAS_EINVAL, "the VSW-parity statistic needs K >= 2");
+    if (stat3 && !(half_divisor != 0.0f)) return fail(JABAS_EINVAL, "half_divisor must be non-zero");
+    if (n == 0) return JABAS_OK;
+    AggArgs a;
+    std::memset(&a, 0, sizeof(a));
+    bool vec = aligned16(out) && (!half_out || aligned16(half_out));
+    for (int k = 0; k < K; ++k) {
+        if (!grads[k]) return fail(JABAS_EINVAL, "grads[k] is null");
+        a.g[k] = grads[k];
+        vec = vec && aligned16(grads[k]);
+    }
+    a.out = out; a.half = half_out; a.stat = stat3; a.n = n; a.divisor = divisor;
+    a.half_divisor = half_divisor; a.K = K;
+    if (stat3 && (rc = ws_for(ctx, stream, &a.ws))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (vec) {
+        if ((rc = agg_dispatch<1>(ctx, a, st))) return rc;
+    } else {
+        int grid = 0;
+        if (stat3) {
+            if ((rc = grid_for(ctx, agg_scalar_kernel<true>, n, kThreads, &grid))) return rc;
+            agg_scalar_kernel<true><<<grid, kThreads, 0, st>>>(a);
+        } else {
+            if ((rc = grid_for(ctx, agg_scalar_kernel<false>, n, kThreads, &grid))) return rc;
+            agg_scalar_kernel<false><<<grid, kThreads, 0, st>>>(a);
+        }
+    }
+    JB_CUDA(cudaGetLastError());
+    return JABAS_OK;
+}
+
+int jabas_div_f32(jabas_ctx_t* ctx, float* x, uint64_t n, float divisor, void* stream)
+{
+    int rc = ctx_bind(ctx);
+    if (rc) return rc;
+    if (!x) return fail(JABAS_EINVAL, "x is null");
+    if (!(divisor != 0.0f)) return fail(JABAS_EINVAL, "divisor must be non-zero");
+    if (n == 0) return JABAS_OK;
+    const int vec = aligned16(x) ? 1 : 0;
+    int grid = 0;
+    if ((rc = grid_for(ctx, div_kernel, vec ? (n + 3) / 4 : n, kThreads, &grid))) return rc;
+    div_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, n, divisor, vec);
+    JB_CUDA(cudaGetLastError());
+    return JABAS_OK;
+}
+
+int jabas_sgd_momentum_f32(jabas_ctx_t* ctx, const float* g, float* const* w, int K, float* m,
+                           uint64_t n, uint64_t base, const jabas_layout_t* layout,
+                           const jabas_group_t* groups, int ngroups, const jabas_sgd_hp_t* hp,
+                           const float* half, float half_divisor, double* stat3, void* stream)
+{
+    if (!hp) return fail(JABAS_EINVAL, "hp is null");
+    UpdArgs a;
+    bool vec = false;
+    int rc = upd_prepare(ctx, a, &vec, g, w, K, m, nullptr, n, base, layout, groups, ngroups, half,
+                         half_divisor, stat3, stream);
+    if (rc) return rc;
+    if (hp->momentum != 0.0 && !m) return fail(JABAS_EINVAL, "momentum != 0 needs a momentum buffer");
+    if (hp->nesterov && (hp->momentum <= 0.0 || hp->dampening != 0.0))
+        return fail(JABAS_EINVAL, "nesterov needs momentum > 0 and dampening == 0");
+    if (n == 0) return JABAS_OK;
+    a.c0 = (float)hp->momentum;
+    a.c1 = (float)(1.0 - hp->dampening);
+    a.flags = (hp->nesterov ? F_NESTEROV : 0u) | (hp->first_step ? F_FIRST : 0u) |
+              (hp->momentum != 0.0 ? F_MOMENTUM : 0u);
+    for (int i = 0; i < ngroups; ++i) {
+        a.grp[i].wd = (float)groups[i].weight_decay;
+        a.grp[i].s0 = (float)(-groups[i].lr);
+        if (groups[i].weight_decay != 0.0) a.wd_mask |= 1u << i;
+    }
+    return upd_launch<OPT_SGD>(ctx, a, vec, static_cast<cudaStream_t>(stream));
+}
+
+int jabas_adam_f32(jabas_ctx_t* ctx, const float* g, float* const* w, int K, float* m, float* v,
+                   uint64_t n, uint64_t base, const jabas_layout_t* layout,
+                   const jabas_group_t* groups, int ngroups, const jabas_adam_hp_t* hp,
+                   const float* half, float half_divisor, double* stat3, void* stream)
+{
+    if (!hp) return fail(JABAS_EINVAL, "hp is null");
+    UpdArgs a;
+    bool vec = false;
+    int rc = upd_prepare(ctx, a, &vec, g, w, K, m, v, n, base, layout, groups, ngroups, half,
+                         half_divisor, stat3, stream);
+    if (rc) return rc;
+    if (!m || !v) return fail(JABAS_EINVAL, "exp_avg and exp_avg_sq buffers are required");
+    if (n == 0) return JABAS_OK;
+    a.c0 = (float)hp->beta1; a.c1 = (float)hp->beta2;
+    a.c2 = (float)(1.0 - hp->beta1); a.c3 = (float)(1.0 - hp->beta2);
+    a.c4 = (float)hp->eps;
+    a.flags = hp->decoupled ? F_DECOUPLED : 0u;
+    for (int i = 0; i < ngroups; ++i) {
+        if (groups[i].step < 1) return fail(JABAS_EINVAL, "Adam step must be >= 1");
+        const double bc1 = 1.0 - std::pow(hp->beta1, (double)groups[i].step);
+        const double bc2 = 1.0 - std::pow(hp->beta2, (double)groups[i].step);
+        a.grp[i].wd = (float)groups[i].weight_decay;
+        a.grp[i].s0 = (float)(1.0 - groups[i].lr * groups[i].weight_decay);
+        a.grp[i].s1 = (float)(-(groups[i].lr / bc1));
+        a.grp[i].s2 = (float)std::sqrt(bc2);
+        if (groups[i].weight_decay != 0.0) a.wd_mask |= 1u << i;
+    }
+    return upd_launch<OPT_ADAM>(ctx, a, vec, static_cast<cudaStream_t>(stream));
+}
+
+int jabas_dot_norms_f32(jabas_ctx_t* ctx, const float* a, const float* b, uint64_t n, double* stat3,
+                        void* stream)
+{
+    int rc = ctx_bind(ctx);
+    if (rc) return rc;
+    if (!a || !b || !stat3) return fail(JABAS_EINVAL, "a, b or stat3 is null");
+    if (n == 0) return JABAS_OK;
+    StatWs ws;
+    if ((rc = ws_for(ctx, stream, &ws))) return rc;
+    const int vec = (aligned16(a) && aligned16(b)) ? 1 : 0;
+    int grid = 0;
+    if ((rc = grid_for(ctx, dot_norms_kernel, vec ? (n + 3) / 4 : n, vec ? kThreads * 4 : kThreads, &grid))) return rc;
+    dot_norms_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(a, b, n, vec, ws, stat3);
+    JB_CUDA(cudaGetLastError());
+    return JABAS_OK;
+}
+
+int jabas_cosine_finalize(jabas_ctx_t* ctx, const double* stat3, double eps, float* cos_out, void* stream)
+{
+    int rc = ctx_bind(ctx);
+    if (rc) return rc;
+    if (!stat3 || !cos_out) return fail(JABAS_EINVAL, "stat3 or cos_out is null");
+    cosine_finalize_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(stat3, eps, cos_out);
+    JB_CUDA(cudaGetLastError());
+    return JABAS_OK;
+}
+
+int jabas_replicate_f32(jabas_ctx_t* ctx, const float* src, float* const* dst, int ndst, uint64_t n,
+                        void* stream)
+{
+    int rc = ctx_bind(ctx);
+    if (rc) return rc;
+    if (!src || (!dst && ndst > 0)) return fail(JABAS_EINVAL, "src or dst is null");
+    if (ndst < 0 || ndst > JABAS_MAX_VSW) return fail(JABAS_EINVAL, "ndst must be in [0, JABAS_MAX_VSW]");
+    RepArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.src = src; a.n = n; a.vec = aligned16(src) ? 1 : 0;
+    for (int k = 0; k < ndst; ++k) {
+        if (!dst[k]) return fail(JABAS_EINVAL, "dst[k] is null");
+        if (dst[k] == src) continue;
+        a.dst[a.ndst++] = dst[k];
+        a.vec = a.vec && aligned16(dst[k]);
+    }
+    if (n == 0 || a.ndst == 0) return JABAS_OK;
+    int grid = 0;
+    if ((rc = grid_for(ctx, replicate_kernel, a.vec ? (n + 3) / 4 : n, a.vec ? kThreads * 4 : kThreads, &grid))) return rc;
+    replicate_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    JB_CUDA(cudaGetLastError());
+    return JABAS_OK;
+}
+
+}  // extern "C"

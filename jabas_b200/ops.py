@@ -1,0 +1,179 @@
+"""Host-side launchers: torch tensors in, C-ABI calls out.
+
+PyTorch is used here only for device memory and streams.  Every function enqueues one
+kernel of ``libjabas_b200.so`` on the given (default: current) CUDA stream and returns
+immediately.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from ._lib import MAX_GROUPS, MAX_VSW, JabasError
+
+
+def _stream_handle(device: torch.device, stream: Optional[torch.cuda.Stream]) -> int:
+    s = stream if stream is not None else torch.cuda.current_stream(device)
+    return s.cuda_stream
+
+
+def _dev_f32(t: torch.Tensor, device: torch.device, name: str) -> int:
+    if not t.is_cuda or t.device != device:
+        raise JabasError(f"{name} must live on {device} (got {t.device}); there is no CPU path")
+    if t.dtype != torch.float32 or not t.is_contiguous():
+        raise JabasError(f"{name} must be a contiguous float32 tensor")
+    return t.data_ptr()
+
+
+def _stat_ptr(stat: Optional[torch.Tensor], device: torch.device) -> Optional[int]:
+    if stat is None:
+        return None
+    if (not stat.is_cuda or stat.device != device or stat.dtype != torch.float64
+            or stat.numel() != 3 or not stat.is_contiguous()):
+        raise JabasError("stat must be a contiguous float64 tensor of 3 elements on the context's device")
+    return stat.data_ptr()
+
+
+def _ptr_array(ptrs: Sequence[int]):
+    return (ctypes.c_void_p * len(ptrs))(*ptrs)
+
+
+class Context:
+    """Owns a ``jabas_ctx_t``: device id, SM count, per-stream reduction workspaces."""
+
+    def __init__(self, device=None):
+        if not torch.cuda.is_available():
+            raise JabasError("jabas_b200 needs a CUDA device (B200, sm_100a); there is no CPU fallback")
+        self.device = torch.device("cuda", torch.cuda.current_device() if device is None
+                                   else torch.device(device).index or 0)
+        self._lib = _lib.load()
+        h = ctypes.c_void_p()
+        _lib.check(self._lib.jabas_ctx_create(self.device.index, ctypes.byref(h)))
+        self._h = h
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.jabas_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):  # pragma: no cover - interpreter shutdown order
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Layout:
+    """Device copy of a segment table ``[(begin, end, group), ...]`` over a flat buffer."""
+
+    def __init__(self, ctx: Context, segments: Sequence[Sequence[int]], total: int):
+        self.ctx = ctx
+        self.segments = [tuple(int(x) for x in s) for s in segments]
+        self.total = int(total)
+        arr = (_lib.Seg * len(self.segments))()
+        for i, (b, e, g) in enumerate(self.segments):
+            arr[i].begin, arr[i].end, arr[i].group = b, e, g
+        h = ctypes.c_void_p()
+        _lib.check(ctx._lib.jabas_layout_create(ctx._h, arr, len(self.segments), self.total,
+                                                ctypes.byref(h)))
+        self._h = h
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self.ctx._lib.jabas_layout_destroy(self._h)
+            self._h = None
+
+    def __del__(self):  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _groups_array(groups: Sequence[dict]):
+    if not 1 <= len(groups) <= MAX_GROUPS:
+        raise JabasError(f"between 1 and {MAX_GROUPS} param groups per launch")
+    arr = (_lib.Group * len(groups))()
+    for i, g in enumerate(groups):
+        arr[i].lr = float(g["lr"])
+        arr[i].weight_decay = float(g.get("weight_decay", 0.0))
+        arr[i].step = int(g.get("step", 0))
+    return arr
+
+
+def vsw_aggregate(ctx: Context, grads: Sequence[torch.Tensor], out: torch.Tensor, divisor: float, *,
+                  half_out: Optional[torch.Tensor] = None, half_divisor: float = 1.0,
+                  stat: Optional[torch.Tensor] = None, n: Optional[int] = None,
+                  stream: Optional[torch.cuda.Stream] = None) -> None:
+    """out = (sum_k grads[k]) / divisor; half_out = the sum; stat += VSW-parity statistic."""
+    n = out.numel() if n is None else n
+    gp = _ptr_array([_dev_f32(g, ctx.device, "grads[k]") for g in grads])
+    _lib.check(ctx._lib.jabas_vsw_aggregate_f32(
+        ctx._h, gp, len(grads), _dev_f32(out, ctx.device, "out"),
+        None if half_out is None else _dev_f32(half_out, ctx.device, "half_out"),
+        n, divisor, half_divisor, _stat_ptr(stat, ctx.device), _stream_handle(ctx.device, stream)))
+
+
+def div_(ctx: Context, x: torch.Tensor, divisor: float, *, stream=None) -> None:
+    _lib.check(ctx._lib.jabas_div_f32(ctx._h, _dev_f32(x, ctx.device, "x"), x.numel(), divisor,
+                                      _stream_handle(ctx.device, stream)))
+
+
+def sgd_momentum(ctx: Context, g: torch.Tensor, weights: Sequence[torch.Tensor],
+                 m: Optional[torch.Tensor], groups: Sequence[dict], *, momentum: float = 0.0,
+                 dampening: float = 0.0, nesterov: bool = False, first_step: bool = False,
+                 layout: Optional[Layout] = None, base: int = 0,
+                 half: Optional[torch.Tensor] = None, half_divisor: float = 1.0,
+                 stat: Optional[torch.Tensor] = None, stream=None) -> None:
+    """Fused SGD-momentum update of ``weights[0]`` with write-back to every replica."""
+    hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step))
+    wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
+    _lib.check(ctx._lib.jabas_sgd_momentum_f32(
+        ctx._h, _dev_f32(g, ctx.device, "g"), wp, len(weights),
+        None if m is None else _dev_f32(m, ctx.device, "m"), g.numel(), base,
+        None if layout is None else layout._h, _groups_array(groups), len(groups), ctypes.byref(hp),
+        None if half is None else _dev_f32(half, ctx.device, "half"), half_divisor,
+        _stat_ptr(stat, ctx.device), _stream_handle(ctx.device, stream)))
+
+
+def adam(ctx: Context, g: torch.Tensor, weights: Sequence[torch.Tensor], m: torch.Tensor,
+         v: torch.Tensor, groups: Sequence[dict], *, beta1: float, beta2: float, eps: float,
+         decoupled: bool, layout: Optional[Layout] = None, base: int = 0,
+         half: Optional[torch.Tensor] = None, half_divisor: float = 1.0,
+         stat: Optional[torch.Tensor] = None, stream=None) -> None:
+    """Fused Adam (``decoupled=False``) / AdamW (``True``) update with write-back."""
+    hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0)
+    wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
+    _lib.check(ctx._lib.jabas_adam_f32(
+        ctx._h, _dev_f32(g, ctx.device, "g"), wp, len(weights), _dev_f32(m, ctx.device, "m"),
+        _dev_f32(v, ctx.device, "v"), g.numel(), base, None if layout is None else layout._h,
+        _groups_array(groups), len(groups), ctypes.byref(hp),
+        None if half is None else _dev_f32(half, ctx.device, "half"), half_divisor,
+        _stat_ptr(stat, ctx.device), _stream_handle(ctx.device, stream)))
+
+
+def dot_norms(ctx: Context, a: torch.Tensor, b: torch.Tensor, stat: torch.Tensor, *, stream=None) -> None:
+    _lib.check(ctx._lib.jabas_dot_norms_f32(ctx._h, _dev_f32(a, ctx.device, "a"),
+                                            _dev_f32(b, ctx.device, "b"), a.numel(),
+                                            _stat_ptr(stat, ctx.device),
+                                            _stream_handle(ctx.device, stream)))
+
+
+def cosine_finalize(ctx: Context, stat: torch.Tensor, cos_out: torch.Tensor, *, eps: float = 1e-8,
+                    stream=None) -> None:
+    _lib.check(ctx._lib.jabas_cosine_finalize(ctx._h, _stat_ptr(stat, ctx.device), eps,
+                                              _dev_f32(cos_out, ctx.device, "cos_out"),
+                                              _stream_handle(ctx.device, stream)))
+
+
+def replicate(ctx: Context, src: torch.Tensor, dsts: Sequence[torch.Tensor], *, stream=None) -> None:
+    dp = _ptr_array([_dev_f32(d, ctx.device, "dsts[k]") for d in dsts])
+    _lib.check(ctx._lib.jabas_replicate_f32(ctx._h, _dev_f32(src, ctx.device, "src"), dp, len(dsts),
+                                            src.numel(), _stream_handle(ctx.device, stream)))
+
+
+__all__ = ["Context", "Layout", "JabasError", "MAX_VSW", "MAX_GROUPS", "vsw_aggregate", "div_",
+           "sgd_momentum", "adam", "dot_norms", "cosine_finalize", "replicate"]
