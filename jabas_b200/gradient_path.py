@@ -1,0 +1,264 @@
+"""The per-iteration gradient path of one GPU, bucket by bucket, over flat HBM buffers.
+
+For every DDP bucket ``b`` (a contiguous element range of the flat buffers) the path is
+
+  1. ``aggregate(b)``  K VSW gradient buckets -> main bucket (÷T)     [one kernel]
+                        (+ undivided copy for the parity sub-group, or, on one GPU,
+                        the VSW-parity statistic in the same pass)
+  2. ``allreduce(b)``  sub-group SUM of the copy, world SUM of the main bucket [NCCL]
+  3. ``update(b)``     fused SGD-momentum / Adam / AdamW on the main replica, new weights
+                        written to all K replicas, two-half statistic from the sub-group
+                        sum in the same pass                                [one kernel]
+
+and once per iteration ``finish_similarity()`` turns the three fp64 sums into the cosine.
+
+This replaces, op for op, the reference's chain
+``subgroup_allreduce_hook`` -> ``iidp_allreduce_hook`` -> optimizer step -> weight copy
+-> ``_compute_cosine_similarity`` (jabas/ddp_comm_hooks/similarity_allreduce.py:20-45,
+jabas/train/trainer.py:470-483).  Two forms of the statistic are provided:
+
+* ``"fused"`` (default): each rank derives the other half as ``o = 2g - e`` from the
+  world mean ``g`` and its own sub-group mean ``e``; no model-sized exchange, no extra
+  pass.  Rank 0's value is broadcast so that every rank takes the same decision.
+* ``"pair_exchange"``: the reference's data flow — materialise ``E = half/(T/2)``,
+  ``all_gather`` it between the first rank of each sub-group, reduce on rank 0, broadcast.
+
+All device work is enqueued on the CURRENT CUDA stream; collectives are asynchronous
+``torch.distributed`` calls whose completion the current stream waits on (no host sync).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from .layout import FlatLayout
+
+
+@dataclass
+class OptimizerSpec:
+    """Hyper-parameters of the fused update.  ``groups`` holds one dict per optimizer
+    param group (``lr``, ``weight_decay``); ``lr`` may be changed between iterations, as
+    the reference does at jabas/train/trainer.py:693-700."""
+    kind: str                                    # "sgd" | "adam" | "adamw"
+    groups: List[Dict[str, float]]
+    momentum: float = 0.0
+    dampening: float = 0.0
+    nesterov: bool = False
+    betas: Sequence[float] = (0.9, 0.999)
+    eps: float = 1e-8
+
+    def __post_init__(self):
+        if self.kind not in ("sgd", "adam", "adamw"):
+            raise ValueError(f"unsupported optimizer kind {self.kind!r}")
+
+
+class GradientPath:
+    def __init__(self, layout: FlatLayout, num_vsw: int, device, optimizer: OptimizerSpec, *,
+                 total_num_decoupled_workers: int, process_group=None, sub_group=None,
+                 pair_group=None, first_subgroup_src_rank: int = 0, second_subgroup_src_rank: int = 1,
+                 similarity: bool = True, similarity_mode: str = "fused", backend=None):
+        if backend is None:
+            from . import ops as backend          # the CUDA library; raises without a GPU
+        self.ops = backend
+        self.layout = layout
+        self.K = int(num_vsw)
+        self.device = torch.device(device)
+        self.opt = optimizer
+        self.T = int(total_num_decoupled_workers)
+        self.pg = process_group
+        self.sub_group = sub_group
+        self.pair_group = pair_group
+        self.src0, self.src1 = first_subgroup_src_rank, second_subgroup_src_rank
+        self.world = dist.get_world_size(process_group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.rank = dist.get_rank(process_group) if self.world > 1 else 0
+        self.similarity = bool(similarity)
+        if similarity_mode not in ("fused", "pair_exchange"):
+            raise ValueError("similarity_mode must be 'fused' or 'pair_exchange'")
+        self.similarity_mode = similarity_mode
+        if self.similarity:
+            # jabas/ddp_comm_hooks/similarity_allreduce.py:13-14
+            assert self.T % 2 == 0, f"total_num_decoupled_workers must be even, but {self.T}"
+            if self.world > 1:
+                assert self.world % 2 == 0          # jabas/train/trainer.py:430
+            else:
+                assert self.K >= 2 and self.K % 2 == 0, \
+                    "on one GPU the two halves are the even and the odd VSWs: K must be even"
+        self.ctx = self.ops.Context(self.device)
+        self.dev_layout = self.ops.Layout(self.ctx, layout.segments, layout.total) \
+            if len(layout.segments) > 1 else None
+        n = layout.total
+        f32 = dict(dtype=torch.float32, device=self.device)
+        self.weights = [torch.zeros(n, **f32) for _ in range(self.K)]
+        self.grads = [torch.zeros(n, **f32) for _ in range(self.K)]
+        self.m = torch.zeros(n, **f32) if (optimizer.kind != "sgd" or optimizer.momentum != 0) else None
+        self.v = torch.zeros(n, **f32) if optimizer.kind != "sgd" else None
+        self.half = torch.zeros(n, **f32) if (self.similarity and self.world > 1) else None
+        self.stat = torch.zeros(3, dtype=torch.float64, device=self.device)
+        self.cos = torch.zeros(1, **f32)
+        self.steps = 0                               # completed optimizer steps
+        self._pending: Dict[int, list] = {}
+        self._sim_step = False
+        self.launches = 0                            # kernels of libjabas_b200 enqueued so far
+        self.profile_events: Optional[list] = None   # set to [] to time every kernel with CUDA events
+
+    # -- views ---------------------------------------------------------------------
+    def bucket_range(self, b: int):
+        return self.layout.buckets[b]
+
+    def _sl(self, t: torch.Tensor, b: int) -> torch.Tensor:
+        begin, end = self.layout.buckets[b]
+        return t[begin:end]
+
+    @property
+    def main_grad(self) -> torch.Tensor:
+        return self.grads[0]
+
+    def _ev_begin(self):
+        if self.profile_events is None:
+            return None
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    def _ev_end(self, kind: str, b, e0) -> None:
+        if e0 is None:
+            return
+        e1 = torch.cuda.Event(enable_timing=True)
+        e1.record()
+        self.profile_events.append((kind, b, e0, e1))
+
+    # -- per iteration ---------------------------------------------------------------
+    def begin_iteration(self, similarity_step: Optional[bool] = None) -> None:
+        self._sim_step = self.similarity if similarity_step is None else (similarity_step and self.similarity)
+        self._pending.clear()
+        if self._sim_step:
+            self.stat.zero_()
+
+    def aggregate(self, b: int) -> None:
+        """Kernel 1: K VSW buckets -> main bucket / T (in place into VSW 0's buffer)."""
+        gs = [self._sl(g, b) for g in self.grads]
+        out = gs[0]
+        kw = {}
+        if self._sim_step:
+            if self.world > 1:
+                kw["half_out"] = self._sl(self.half, b)
+            else:
+                kw.update(half_divisor=self.T / 2, stat=self.stat)
+        ev = self._ev_begin()
+        self.ops.vsw_aggregate(self.ctx, gs, out, float(self.T), **kw)
+        self._ev_end("aggregate", b, ev)
+        self.launches += 1
+
+    def allreduce(self, b: int) -> None:
+        """Sub-group SUM of the undivided copy and world SUM of the (already ÷T) bucket,
+        both asynchronous; ``update`` waits for them on the current stream."""
+        if self.world == 1:
+            return
+        works = []
+        if self._sim_step:
+            works.append(dist.all_reduce(self._sl(self.half, b), group=self.sub_group, async_op=True))
+        works.append(dist.all_reduce(self._sl(self.main_grad, b), group=self.pg, async_op=True))
+        self._pending[b] = works
+
+    def wait_allreduce(self, b: int) -> None:
+        for w in self._pending.pop(b, ()):
+            w.wait()                               # stream-level wait, does not block the host
+
+    def update(self, b: Optional[int] = None) -> None:
+        """Kernel 2: fused optimizer update + write-back (+ statistic) on bucket ``b``, or
+        on the whole flat buffer in one launch when ``b`` is None."""
+        if b is None:
+            for bb in list(self._pending):
+                self.wait_allreduce(bb)
+            begin, end = 0, self.layout.total
+        else:
+            self.wait_allreduce(b)
+            begin, end = self.layout.buckets[b]
+        if end == begin:
+            return
+        kw = dict(layout=self.dev_layout, base=begin)
+        fused_stat = self._sim_step and self.world > 1 and self.similarity_mode == "fused"
+        if fused_stat:
+            kw.update(half=self.half[begin:end], half_divisor=self.T / 2, stat=self.stat)
+        elif self._sim_step and self.world > 1:
+            self.ops.div_(self.ctx, self.half[begin:end], self.T / 2)      # E = half / (T/2)
+            self.launches += 1
+        g = self.main_grad[begin:end]
+        ws = [w[begin:end] for w in self.weights]
+        o = self.opt
+        ev = self._ev_begin()
+        if o.kind == "sgd":
+            self.ops.sgd_momentum(self.ctx, g, ws, None if self.m is None else self.m[begin:end],
+                                  o.groups, momentum=o.momentum, dampening=o.dampening,
+                                  nesterov=o.nesterov, first_step=(self.steps == 0), **kw)
+        else:
+            groups = [dict(gr, step=self.steps + 1) for gr in o.groups]
+            self.ops.adam(self.ctx, g, ws, self.m[begin:end], self.v[begin:end], groups,
+                          beta1=o.betas[0], beta2=o.betas[1], eps=o.eps,
+                          decoupled=(o.kind == "adamw"), **kw)
+        self._ev_end("update", b, ev)
+        self.launches += 1
+
+    def end_iteration(self) -> None:
+        self.steps += 1
+
+    def finish_similarity(self) -> Optional[torch.Tensor]:
+        """Cosine of the two half-gradients; identical on every rank (rank 0's value)."""
+        if not self._sim_step:
+            return None
+        if self.world > 1 and self.similarity_mode == "pair_exchange":
+            # jabas/train/trainer.py:470-483
+            if self.rank in (self.src0, self.src1):
+                n = self.layout.total
+                both = [torch.empty(n, dtype=torch.float32, device=self.device) for _ in range(2)]
+                dist.all_gather(both, self.half, group=self.pair_group)
+                if self.rank == self.src0:
+                    self.ops.dot_norms(self.ctx, both[0], both[1], self.stat)
+                    self.launches += 1
+        if self.rank == self.src0 or self.world == 1:
+            self.ops.cosine_finalize(self.ctx, self.stat, self.cos)
+            self.launches += 1
+        if self.world > 1:
+            dist.broadcast(self.cos, self.src0, group=self.pg)
+        return self.cos
+
+    # -- whole iteration, buckets in ready order (used by the benchmark and by tests) ---
+    def run_iteration(self, similarity_step: Optional[bool] = None, overlap: bool = True):
+        self.begin_iteration(similarity_step)
+        nb = self.layout.num_buckets
+        if overlap:
+            # software pipeline: bucket b's collectives fly while bucket b-1 is updated
+            for b in range(nb):
+                self.aggregate(b)
+                self.allreduce(b)
+                if b > 0:
+                    self.update(b - 1)
+            self.update(nb - 1)
+        else:
+            for b in range(nb):
+                self.aggregate(b)
+                self.allreduce(b)
+            self.update(None)
+        cos = self.finish_similarity()
+        self.end_iteration()
+        return cos
+
+    # -- bookkeeping for roofline reports ----------------------------------------------
+    def algorithmic_bytes(self, similarity_step: bool = True) -> Dict[str, int]:
+        """Bytes each stage must move per iteration on this GPU (fp32 = 4 B)."""
+        n, K = self.layout.num_params, self.K
+        multi = self.world > 1
+        agg = 4 * n * (K + 1) + (4 * n if (similarity_step and multi) else 0)
+        per_elem = (K + 4) if self.opt.kind == "sgd" else (K + 6)
+        if self.opt.kind == "sgd" and self.opt.momentum == 0:
+            per_elem = K + 2
+        upd = 4 * n * per_elem + (4 * n if (similarity_step and multi) else 0)
+        return {"aggregate": agg, "update": upd, "total": agg + upd}
+
+    def close(self) -> None:
+        if self.dev_layout is not None:
+            self.dev_layout.close()
+        self.ctx.close()
