@@ -39,7 +39,7 @@ WORKLOADS = {
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="resnet50",
@@ -48,6 +48,8 @@ def parse_args():
     ap.add_argument("--optimizer", default=None, choices=[None, "sgd", "adam", "adamw"])
     ap.add_argument("--similarity-mode", default="fused", choices=["fused", "pair_exchange"])
     ap.add_argument("--no-overlap", action="store_true")
+    ap.add_argument("--per-bucket", default="auto", choices=["auto", "yes", "no"],
+                    help="walk the DDP buckets (default when N > 1) or launch over the whole flat model")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-steps", type=int, default=None)
@@ -85,7 +87,10 @@ def config_dict(args, layout, K, lbs, opt, desc, world):
         "buckets_mib": layout.bucket_sizes_mib(), "vsw_per_gpu": K, "local_batch_per_vsw": lbs,
         "global_batch": world * K * lbs, "optimizer": opt["kind"], "param_groups": len(opt["groups"]),
         "similarity": "every iteration", "similarity_mode": args.similarity_mode if world > 1 else "vsw_parity",
-        "overlap": not args.no_overlap, "parallelism": f"dp{world} x vsw{K}",
+        "overlap": not args.no_overlap,
+        "launch_granularity": "bucket" if (args.per_bucket == "yes" or (args.per_bucket == "auto" and world > 1))
+                              else "whole flat model",
+        "parallelism": f"dp{world} x vsw{K}",
         "l2": "inputs larger than L2: %.0f MB of gradients, weights and state per GPU vs 126 MB"
               % (4 * layout.total * (2 * K + 2) / 1e6),
     }
@@ -278,6 +283,8 @@ def run_ours(args):
         g = torch.Generator(device=dev).manual_seed(1000 * rank + k)
         eng.grads[k].normal_(0.0, 1e-3, generator=g)
     overlap = not args.no_overlap
+    per_bucket = None if args.per_bucket == "auto" else (args.per_bucket == "yes")
+    step_fn = lambda: eng.run_iteration(overlap=overlap, per_bucket=per_bucket)
 
     def barrier():
         if world > 1:
@@ -293,7 +300,7 @@ def run_ours(args):
 
     # ---- device-resident timing ---------------------------------------------------
     for _ in range(max(args.warmup, 3)):
-        eng.run_iteration(overlap=overlap)
+        step_fn()
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -305,7 +312,7 @@ def run_ours(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        eng.run_iteration(overlap=overlap)
+        step_fn()
     e1.record()
     barrier()
     ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
@@ -338,7 +345,7 @@ def run_ours(args):
         def e2e_step():
             for k in range(K):
                 eng.grads[k].copy_(host[k], non_blocking=True)
-            c = eng.run_iteration(overlap=overlap)
+            c = step_fn()
             cos_host.copy_(c, non_blocking=True)
             torch.cuda.current_stream().synchronize()      # the caller reads the statistic
 

@@ -56,7 +56,7 @@ class OptimizerSpec:
 
 
 class GradientPath:
-    def __init__(self, layout: FlatLayout, num_vsw: int, device, optimizer: OptimizerSpec, *,
+    def __init__(self, layout: FlatLayout, num_vsw: int, device, optimizer: Optional[OptimizerSpec] = None, *,
                  total_num_decoupled_workers: int, process_group=None, sub_group=None,
                  pair_group=None, first_subgroup_src_rank: int = 0, second_subgroup_src_rank: int = 1,
                  similarity: bool = True, similarity_mode: str = "fused", backend=None):
@@ -66,7 +66,8 @@ class GradientPath:
         self.layout = layout
         self.K = int(num_vsw)
         self.device = torch.device(device)
-        self.opt = optimizer
+        self.opt = None
+        self.m = self.v = None
         self.T = int(total_num_decoupled_workers)
         self.pg = process_group
         self.sub_group = sub_group
@@ -87,14 +88,11 @@ class GradientPath:
                 assert self.K >= 2 and self.K % 2 == 0, \
                     "on one GPU the two halves are the even and the odd VSWs: K must be even"
         self.ctx = self.ops.Context(self.device)
-        self.dev_layout = self.ops.Layout(self.ctx, layout.segments, layout.total) \
-            if len(layout.segments) > 1 else None
+        self.dev_layout = None
         n = layout.total
         f32 = dict(dtype=torch.float32, device=self.device)
         self.weights = [torch.zeros(n, **f32) for _ in range(self.K)]
         self.grads = [torch.zeros(n, **f32) for _ in range(self.K)]
-        self.m = torch.zeros(n, **f32) if (optimizer.kind != "sgd" or optimizer.momentum != 0) else None
-        self.v = torch.zeros(n, **f32) if optimizer.kind != "sgd" else None
         self.half = torch.zeros(n, **f32) if (self.similarity and self.world > 1) else None
         self.stat = torch.zeros(3, dtype=torch.float64, device=self.device)
         self.cos = torch.zeros(1, **f32)
@@ -103,12 +101,41 @@ class GradientPath:
         self._sim_step = False
         self.launches = 0                            # kernels of libjabas_b200 enqueued so far
         self.profile_events: Optional[list] = None   # set to [] to time every kernel with CUDA events
+        if optimizer is not None:
+            self.set_optimizer(optimizer)
+
+    def set_optimizer(self, optimizer: OptimizerSpec) -> None:
+        """Bind the fused update: uploads the param-group segment table of the layout and
+        allocates the flat momentum / Adam moment buffers (kept if already present)."""
+        self.opt = optimizer
+        ngroups = 1 + max(g for _, _, g in self.layout.segments)
+        if len(optimizer.groups) < ngroups:
+            raise ValueError(f"the layout names {ngroups} param groups, the optimizer has {len(optimizer.groups)}")
+        if self.dev_layout is not None:
+            self.dev_layout.close()
+        self.dev_layout = self.ops.Layout(self.ctx, self.layout.segments, self.layout.total) \
+            if len(self.layout.segments) > 1 else None
+        f32 = dict(dtype=torch.float32, device=self.device)
+        n = self.layout.total
+        if self.m is None and (optimizer.kind != "sgd" or optimizer.momentum != 0):
+            self.m = torch.zeros(n, **f32)
+        if self.v is None and optimizer.kind != "sgd":
+            self.v = torch.zeros(n, **f32)
+
+    def set_total_workers(self, total_num_decoupled_workers: int) -> None:
+        """T changes when VSWs are added or removed at run time
+        (jabas/train/trainer.py:543-544, 570-571)."""
+        self.T = int(total_num_decoupled_workers)
+        if self.similarity:
+            assert self.T % 2 == 0
 
     # -- views ---------------------------------------------------------------------
     def bucket_range(self, b: int):
         return self.layout.buckets[b]
 
-    def _sl(self, t: torch.Tensor, b: int) -> torch.Tensor:
+    def _sl(self, t: torch.Tensor, b: Optional[int]) -> torch.Tensor:
+        if b is None:                                  # the whole flat buffer, padding included
+            return t
         begin, end = self.layout.buckets[b]
         return t[begin:end]
 
@@ -137,12 +164,25 @@ class GradientPath:
         if self._sim_step:
             self.stat.zero_()
 
-    def aggregate(self, b: int) -> None:
-        """Kernel 1: K VSW buckets -> main bucket / T (in place into VSW 0's buffer)."""
+    def aggregate(self, b: Optional[int], divide: bool = True, similarity: Optional[bool] = None) -> None:
+        """Kernel 1: K VSW buckets -> main bucket / T (in place into VSW 0's buffer).
+        ``divide=False`` leaves the plain local sum, for a caller-supplied comm hook that
+        does its own averaging.  ``similarity`` (default: this iteration's setting) adds
+        the undivided copy for the sub-group allreduce or, on one GPU, the statistic."""
         gs = [self._sl(g, b) for g in self.grads]
         out = gs[0]
         kw = {}
-        if self._sim_step:
+        if not divide:
+            if self.K > 1:
+                self.ops.vsw_aggregate(self.ctx, gs, out, 1.0)
+                self.launches += 1
+            return
+        if similarity is None:
+            similarity = self._sim_step
+        if similarity:
+            if not self._sim_step:                     # first similarity bucket of the iteration
+                self._sim_step = True
+                self.stat.zero_()
             if self.world > 1:
                 kw["half_out"] = self._sl(self.half, b)
             else:
@@ -152,7 +192,12 @@ class GradientPath:
         self._ev_end("aggregate", b, ev)
         self.launches += 1
 
-    def allreduce(self, b: int) -> None:
+    def zero_grads(self) -> None:
+        """One memset per VSW instead of a per-parameter ``zero_grad`` loop."""
+        for g in self.grads:
+            g.zero_()
+
+    def allreduce(self, b: Optional[int]) -> None:
         """Sub-group SUM of the undivided copy and world SUM of the (already ÷T) bucket,
         both asynchronous; ``update`` waits for them on the current stream."""
         if self.world == 1:
@@ -226,10 +271,20 @@ class GradientPath:
         return self.cos
 
     # -- whole iteration, buckets in ready order (used by the benchmark and by tests) ---
-    def run_iteration(self, similarity_step: Optional[bool] = None, overlap: bool = True):
+    def run_iteration(self, similarity_step: Optional[bool] = None, overlap: bool = True,
+                      per_bucket: Optional[bool] = None):
+        """One pass of the path.  ``per_bucket`` (default: only when there are collectives
+        to overlap) walks the DDP buckets as the comm hooks do during backward; otherwise
+        the whole flat model goes through each kernel in one launch."""
         self.begin_iteration(similarity_step)
         nb = self.layout.num_buckets
-        if overlap:
+        if per_bucket is None:
+            per_bucket = self.world > 1
+        if not per_bucket:
+            self.aggregate(None)
+            self.allreduce(None)
+            self.update(None)
+        elif overlap:
             # software pipeline: bucket b's collectives fly while bucket b-1 is updated
             for b in range(nb):
                 self.aggregate(b)

@@ -49,6 +49,14 @@ class FlatLayout:
     def bucket_numel(self, b: int) -> int:
         return self.buckets[b][1] - self.buckets[b][0]
 
+    def set_groups(self, groups: Sequence[int]) -> None:
+        """Re-assign the optimizer param group of every parameter (in ``slots`` order) and
+        rebuild the segment table; offsets and buckets do not move."""
+        for slot, g in zip(self.slots, groups):
+            slot.group = int(g)
+        runs = sorted((s.offset, s.offset + s.numel, s.group) for s in self.slots if s.numel)
+        self.segments = _merge_runs(runs, self.total)
+
     def bucket_sizes_mib(self) -> List[float]:
         return [round(self.bucket_numel(b) * 4 / 2 ** 20, 2) for b in range(self.num_buckets)]
 
@@ -71,6 +79,22 @@ def assign_buckets(numels: Sequence[int], bucket_cap_mb: float = DEFAULT_BUCKET_
     if cur:
         out.append(cur)
     return out
+
+
+def _merge_runs(runs, total: int) -> List[Tuple[int, int, int]]:
+    """Merge neighbouring runs of one group; padding joins the run before it."""
+    segs: List[List[int]] = []
+    for begin, end, g in runs:
+        if segs:
+            segs[-1][1] = begin
+        if segs and segs[-1][2] == g:
+            segs[-1][1] = end
+        else:
+            segs.append([begin if segs else 0, end, g])
+    if not segs:
+        segs = [[0, total, 0]]
+    segs[-1][1] = total
+    return [(s[0], s[1], s[2]) for s in segs]
 
 
 def _align(x: int) -> int:
@@ -103,19 +127,7 @@ def build_layout(names: Sequence[str], shapes: Sequence[Sequence[int]], groups: 
         buckets.append((begin, pos))
         pos = _align(pos)
     total = max(pos, ALIGN_ELEMS)
-    # merge neighbouring runs of one group; padding joins the run before it
-    segs: List[List[int]] = []
-    for begin, end, g in runs:
-        if segs:
-            segs[-1][1] = begin
-        if segs and segs[-1][2] == g:
-            segs[-1][1] = end
-        else:
-            segs.append([begin if segs else 0, end, g])
-    if not segs:
-        segs = [[0, total, 0]]
-    segs[-1][1] = total
-    segments = [(s[0], s[1], s[2]) for s in segs]
+    segments = _merge_runs(runs, total)
     return FlatLayout([slots[i] for i in range(len(names))], buckets, bucket_indices, segments, total,
                       sum(numels))
 
