@@ -99,6 +99,7 @@ class GradientPath:
         self.steps = 0                               # completed optimizer steps
         self._pending: Dict[int, list] = {}
         self._sim_step = False
+        self.half_divided = set()                    # pair_exchange: buckets whose E is materialised
         self.launches = 0                            # kernels of libjabas_b200 enqueued so far
         self.profile_events: Optional[list] = None   # set to [] to time every kernel with CUDA events
         if optimizer is not None:
@@ -161,6 +162,7 @@ class GradientPath:
     def begin_iteration(self, similarity_step: Optional[bool] = None) -> None:
         self._sim_step = self.similarity if similarity_step is None else (similarity_step and self.similarity)
         self._pending.clear()
+        self.half_divided = set()
         if self._sim_step:
             self.stat.zero_()
 
@@ -229,8 +231,11 @@ class GradientPath:
         if fused_stat:
             kw.update(half=self.half[begin:end], half_divisor=self.T / 2, stat=self.stat)
         elif self._sim_step and self.world > 1:
-            self.ops.div_(self.ctx, self.half[begin:end], self.T / 2)      # E = half / (T/2)
-            self.launches += 1
+            for bb in (range(self.layout.num_buckets) if b is None else (b,)):
+                if bb not in self.half_divided:                            # E = half / (T/2)
+                    self.ops.div_(self.ctx, self._sl(self.half, bb), self.T / 2)
+                    self.half_divided.add(bb)
+                    self.launches += 1
         g = self.main_grad[begin:end]
         ws = [w[begin:end] for w in self.weights]
         o = self.opt

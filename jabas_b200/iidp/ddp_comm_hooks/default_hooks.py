@@ -12,12 +12,11 @@ def _allreduce_sum_fut(process_group, tensor: torch.Tensor) -> torch.futures.Fut
     """Asynchronous SUM allreduce of ``tensor`` in place.  The future's ``value()[0]`` is
     the reduced tensor, the form jabas/ddp_comm_hooks/similarity_allreduce.py:30-33 reads.
     For NCCL the future completes on the stream level: waiting on it never blocks the host."""
-    group = process_group if process_group is not None else dist.group.WORLD
-    if dist.get_world_size(group) == 1:
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(process_group) == 1:
         fut = torch.futures.Future()
         fut.set_result([tensor])
         return fut
-    return dist.all_reduce(tensor, group=group, async_op=True).get_future().then(
+    return dist.all_reduce(tensor, group=process_group, async_op=True).get_future().then(
         lambda f: [tensor])
 
 

@@ -15,7 +15,7 @@ class IIDPState(object):
     (sum over ranks of VSWs x (accumulation steps + 1), jabas/train/trainer.py:152)."""
 
     def __init__(self, process_group, total_num_decoupled_workers):
-        self.process_group = process_group if process_group is not None else dist.group.WORLD
+        self.process_group = process_group
         self.total_num_decoupled_workers = total_num_decoupled_workers
 
 

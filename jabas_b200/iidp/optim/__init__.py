@@ -1,0 +1,153 @@
+"""Mirror of ``iidp.optim``: ``ShardSGD``, ``ShardAdam``, ``ShardAdamW`` — optimizers whose
+``step(gradients)`` updates only the parameters of one DDP bucket, so that the update of
+bucket b overlaps the allreduce of bucket b+1 (contract visible at
+examples/gnmt/seq2seq/train/shard_optimizer.py:30-50 and examples/resnet50/main.py:351-359).
+
+Here every optimizer, sharded or stock (``torch.optim.SGD/Adam/AdamW``), is bound to the
+flat HBM storage by ``FusedBinding`` and stepped by ONE fused kernel per bucket (or per
+model): gradient, weight and state are read once, the new weights are written to all K
+VSW replicas in the same pass.  ``optimizer.param_groups`` stays the source of truth for
+``lr`` / ``weight_decay`` (they are re-read at every step), and ``optimizer.state`` holds
+views of the flat state buffers, so ``state_dict()`` keeps its per-parameter shape.
+"""
+from __future__ import annotations
+
+from typing import Iterable, List, Optional, Sequence
+
+import torch
+
+from ...gradient_path import GradientPath, OptimizerSpec
+
+
+class FusedBinding:
+    """Ties a ``torch.optim.Optimizer`` over the MAIN replica's parameters to a
+    ``GradientPath``."""
+
+    def __init__(self, optimizer: torch.optim.Optimizer, engine: GradientPath,
+                 main_params: Sequence[torch.nn.Parameter]):
+        self.optimizer, self.engine = optimizer, engine
+        self.params = list(main_params)
+        group_of = {}
+        for gi, g in enumerate(optimizer.param_groups):
+            for p in g["params"]:
+                group_of[id(p)] = gi
+        missing = [i for i, p in enumerate(self.params) if id(p) not in group_of]
+        if missing:
+            raise ValueError(f"{len(missing)} parameters of the main model are not in the optimizer")
+        engine.layout.set_groups([group_of[id(p)] for p in self.params])
+        for i, p in enumerate(self.params):
+            p.index = i                              # the matching key of ShardOptimizer.step
+        self.kind = self._kind(optimizer)
+        engine.set_optimizer(self._spec())
+        self._install_state_views()
+
+    @staticmethod
+    def _kind(opt) -> str:
+        d = opt.defaults
+        if isinstance(opt, torch.optim.AdamW):       # AdamW subclasses Adam in current torch
+            kind = "adamw"
+        elif isinstance(opt, torch.optim.Adam):
+            kind = "adamw" if d.get("decoupled_weight_decay", False) else "adam"
+        elif isinstance(opt, torch.optim.SGD):
+            kind = "sgd"
+        else:
+            raise NotImplementedError(f"no fused update for {type(opt).__name__}: use SGD, Adam or AdamW")
+        if d.get("amsgrad", False) or d.get("maximize", False):
+            raise NotImplementedError("amsgrad / maximize are not supported by the fused update")
+        return kind
+
+    def _spec(self) -> OptimizerSpec:
+        o, d = self.optimizer, self.optimizer.defaults
+        groups = [dict(lr=float(g["lr"]), weight_decay=float(g.get("weight_decay", 0.0)))
+                  for g in o.param_groups]
+        if self.kind == "sgd":
+            g0 = o.param_groups[0]
+            return OptimizerSpec("sgd", groups, momentum=float(g0.get("momentum", 0.0)),
+                                 dampening=float(g0.get("dampening", 0.0)),
+                                 nesterov=bool(g0.get("nesterov", False)))
+        g0 = o.param_groups[0]
+        return OptimizerSpec(self.kind, groups, betas=tuple(g0.get("betas", d["betas"])),
+                             eps=float(g0.get("eps", d["eps"])))
+
+    def _install_state_views(self) -> None:
+        eng, lay = self.engine, self.engine.layout
+        for p, slot in zip(self.params, lay.slots):
+            sl = slice(slot.offset, slot.offset + slot.numel)
+            st = self.optimizer.state[p]
+            if self.kind == "sgd":
+                if eng.m is not None:
+                    st["momentum_buffer"] = eng.m[sl].view(slot.shape)
+            else:
+                st["step"] = torch.tensor(float(eng.steps))
+                st["exp_avg"] = eng.m[sl].view(slot.shape)
+                st["exp_avg_sq"] = eng.v[sl].view(slot.shape)
+
+    def sync_hyperparams(self) -> None:
+        """Copy the (possibly rescheduled) lr / weight decay of every group to the engine."""
+        spec = self.engine.opt
+        for g, dst in zip(self.optimizer.param_groups, spec.groups):
+            dst["lr"], dst["weight_decay"] = float(g["lr"]), float(g.get("weight_decay", 0.0))
+
+    def step(self, buckets: Optional[Iterable[int]] = None) -> None:
+        self.sync_hyperparams()
+        if buckets is None:
+            self.engine.update(None)
+        else:
+            for b in buckets:
+                self.engine.update(b)
+
+    def finish_step(self) -> None:
+        """Once per iteration, after every bucket was updated."""
+        self.engine.end_iteration()
+        if self.kind != "sgd":
+            for p in self.params:
+                self.optimizer.state[p]["step"] = torch.tensor(float(self.engine.steps))
+
+    def buckets_of(self, gradients: Sequence[torch.Tensor]) -> List[int]:
+        """Buckets covered by a list of gradient tensors carrying ``.index``."""
+        lay = self.engine.layout
+        idx = sorted(int(g.index) for g in gradients)
+        buckets = sorted({lay.slots[i].bucket for i in idx})
+        want = sorted(i for b in buckets for i in lay.bucket_indices[b])
+        if want != idx:
+            raise ValueError("step(gradients) must receive the gradients of whole buckets")
+        return buckets
+
+
+class _ShardMixin:
+    """``step(gradients)`` of the overlap mode; ``step()`` updates the whole model."""
+    _binding: Optional[FusedBinding] = None
+
+    def bind(self, binding: FusedBinding) -> None:
+        self._binding = binding
+
+    @torch.no_grad()
+    def step(self, gradients=None, closure=None):
+        if self._binding is None:
+            raise RuntimeError(f"{type(self).__name__} is not bound to the flat gradient storage: "
+                               "pass it to IIDPTrainer.prepare_weight_sync_method first")
+        if gradients is None:
+            self._binding.step(None)
+        else:
+            self._binding.step(self._binding.buckets_of(gradients))
+
+
+class ShardSGD(_ShardMixin, torch.optim.SGD):
+    def __init__(self, params, lr=1e-3, momentum=0, dampening=0, weight_decay=0, nesterov=False):
+        torch.optim.SGD.__init__(self, params, lr=lr, momentum=momentum, dampening=dampening,
+                                 weight_decay=weight_decay, nesterov=nesterov)
+
+
+class ShardAdam(_ShardMixin, torch.optim.Adam):
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0, amsgrad=False):
+        torch.optim.Adam.__init__(self, params, lr=lr, betas=betas, eps=eps,
+                                  weight_decay=weight_decay, amsgrad=amsgrad)
+
+
+class ShardAdamW(_ShardMixin, torch.optim.AdamW):
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, amsgrad=False):
+        torch.optim.AdamW.__init__(self, params, lr=lr, betas=betas, eps=eps,
+                                   weight_decay=weight_decay, amsgrad=amsgrad)
+
+
+__all__ = ["FusedBinding", "ShardSGD", "ShardAdam", "ShardAdamW"]

@@ -1,0 +1,295 @@
+"""Mirror of ``iidp.train.trainer.IIDPTrainer`` as far as the gradient path needs it: the
+constructor, ``prepare_stream_parallel``, ``prepare_weight_sync_method``, ``compute``,
+``step`` and the profiling entry points, with the attribute names the reference reads
+(jabas/train/trainer.py:40-43, 82-98, 171-197, 327-337; examples/resnet50/main.py:230-446).
+
+K virtual stream workers (VSWs) are K copies of the model on K CUDA streams of ONE GPU.
+Their parameters, gradients and the optimizer state live in flat HBM buffers owned by a
+``VSWReducer``; backward fires one comm hook per DDP bucket; the optimizer update writes
+the new weights to all K replicas in the same kernel, so there is no separate copy stage.
+"""
+from __future__ import annotations
+
+import copy
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ...nn.parallel import IndependentIdenticalDataParallel, VSWReducer
+from ..ddp_comm_hooks import IIDPState, dummy_hook, iidp_allreduce_hook
+from ..optim import FusedBinding
+
+WEIGHT_SYNC_METHODS = ("recommend", "overlap", "sequential")
+
+
+def _dist_on() -> bool:
+    return dist.is_available() and dist.is_initialized()
+
+
+class _ReplicaOptimizer:
+    """Stands where the reference keeps one optimizer clone per VSW
+    (jabas/train/trainer.py:501-510): the replicas have no optimizer state of their own —
+    their weights are written by the main update — so only ``zero_grad`` means anything."""
+
+    def __init__(self, main, reducer: VSWReducer, k: int):
+        self._main, self._reducer, self._k = main, reducer, k
+        self.param_groups, self.defaults = main.param_groups, main.defaults
+
+    def zero_grad(self, set_to_none: bool = False) -> None:
+        self._reducer.engine.grads[self._k].zero_()
+
+    def state_dict(self):
+        return self._main.state_dict()
+
+    def load_state_dict(self, sd) -> None:
+        pass
+
+
+class IIDPTrainer(object):
+    def __init__(self, gpu, local_batch_size, num_models, accum_step, weight_sync_method="recommend"):
+        if weight_sync_method not in WEIGHT_SYNC_METHODS:
+            raise ValueError(f"weight_sync_method must be one of {WEIGHT_SYNC_METHODS}")
+        self.gpu = gpu
+        self.device = torch.device("cuda", gpu) if isinstance(gpu, int) else torch.device(gpu)
+        self.local_batch_size = int(local_batch_size)
+        self.num_models = self.num_local_models = int(num_models)
+        self.accum_step = self.max_accum_step = int(accum_step)
+        self.is_accum_mode = self.accum_step > 0
+        self.weight_sync_method = "overlap" if weight_sync_method == "recommend" else weight_sync_method
+        self.batch_size_per_gpu = self.local_batch_size * self.num_models
+        self._get_total_num_decoupled_workers()
+        self.global_batch_size = self.local_batch_size * self.total_num_decoupled_workers
+        self.local_accum_step = -1
+        self.sync_step = 0
+        self.epoch = 0
+        self.total_epoch_time = 0.0
+        self.prepared_for_ddp = False
+        self.local_models: List[IndependentIdenticalDataParallel] = []
+        self.original_local_models: List[torch.nn.Module] = []
+        self.model_streams: List[Optional[torch.cuda.Stream]] = []
+        self.local_optimizers, self.local_schedulers = [], []
+        self.main_optimizer = self.main_scheduler = None
+        self.states, self.hooks = [], []
+        self.losses = {}
+        self.param_groups_func = None
+        self.reducer: Optional[VSWReducer] = None
+        self.binding: Optional[FusedBinding] = None
+        self._backend = None            # tests on CPU inject an oracle-backed double here
+
+    # -- helpers -----------------------------------------------------------------------
+    def trainer_print(self, message, status="info"):
+        rank = dist.get_rank() if _dist_on() else 0
+        if rank == 0:
+            print(f"[{status.upper()}] {message}")
+
+    def _get_total_num_decoupled_workers(self):
+        """T = sum over ranks of VSWs x (accumulation steps + 1) (jabas/train/trainer.py:152)."""
+        mine = self.num_models * (self.accum_step + 1)
+        if _dist_on() and dist.get_world_size() > 1:
+            gathered = [None] * dist.get_world_size()
+            dist.all_gather_object(gathered, mine)
+            self.all_partition_size_in_process_group = gathered
+            self.total_num_decoupled_workers = int(sum(gathered))
+        else:
+            self.all_partition_size_in_process_group = [mine]
+            self.total_num_decoupled_workers = mine
+        return self.total_num_decoupled_workers
+
+    def _similarity_enabled(self) -> bool:
+        return False
+
+    def _similarity_mode(self) -> str:
+        return "fused"
+
+    def _is_similarity_step(self) -> bool:
+        return False
+
+    @property
+    def _cuda(self) -> bool:
+        return self.device.type == "cuda"
+
+    # -- set-up --------------------------------------------------------------------------
+    def prepare_stream_parallel(self, model, criterion, **kwargs):
+        """K streams, K model copies, K DDP wrappers over one shared flat storage."""
+        kwargs.setdefault("gradient_as_bucket_view", True)
+        bucket_cap_mb = kwargs.pop("bucket_cap_mb", 25)
+        first_bucket_bytes = kwargs.pop("first_bucket_bytes", None)
+        self.criterion = criterion
+        K = self.num_models
+        self.model_streams = [torch.cuda.Stream(self.device) if self._cuda else None for _ in range(K)]
+        self.main_stream = self.model_streams[0]
+        self.original_local_models = [model] + [copy.deepcopy(model) for _ in range(K - 1)]
+        self.reducer = VSWReducer(self.device, K, self.total_num_decoupled_workers, bucket_cap_mb,
+                                  similarity=self._similarity_enabled(),
+                                  similarity_mode=self._similarity_mode(), backend=self._backend,
+                                  first_bucket_bytes=first_bucket_bytes)
+        self._sync_buffer_barrier = [None, None]
+        self.local_models = [
+            IndependentIdenticalDataParallel(
+                m, device_ids=[self.gpu], output_device=[self.gpu], model_index=i, num_local_models=K,
+                total_num_models=self.total_num_decoupled_workers, reducer=self.reducer, **kwargs)
+            for i, m in enumerate(self.original_local_models)]
+        self.main_model = self.local_models[0]
+        self.eval_model = self.main_model.module
+        self.prepared_for_ddp = True
+        if self._cuda:
+            torch.cuda.current_stream(self.device).synchronize()
+
+    def set_original_local_models(self, models):
+        self.original_local_models = list(models)
+
+    def _set_local_optimizers(self, optimizer, param_groups_func=None):
+        self.param_groups_func = param_groups_func
+        self.main_optimizer = optimizer
+        self.binding = FusedBinding(optimizer, self.reducer.engine, self.main_model._params)
+        if hasattr(optimizer, "bind"):
+            optimizer.bind(self.binding)
+        self.local_optimizers = [optimizer] + [_ReplicaOptimizer(optimizer, self.reducer, k)
+                                               for k in range(1, self.num_models)]
+
+    def _set_local_schedulers(self, scheduler=None):
+        self.main_scheduler = scheduler
+        self.local_schedulers = [scheduler] + [None] * (self.num_models - 1)
+
+    def _prepare_hooks(self):
+        self.states = [IIDPState(None, self.total_num_decoupled_workers)] + [None] * (self.num_models - 1)
+        self.hooks = [iidp_allreduce_hook] + [dummy_hook] * (self.num_models - 1)
+
+    def prepare_weight_sync_method(self, optimizer, scheduler=None, param_groups_func=None):
+        self._set_local_optimizers(optimizer, param_groups_func)
+        self._set_local_schedulers(scheduler)
+        self._prepare_hooks()
+        if not self.prepared_for_ddp:
+            raise RuntimeError("prepare_stream_parallel() must be called first")
+        if self.weight_sync_method == "overlap":
+            self._prepare_overlap_optimizer_with_ddp()
+        else:
+            self._register_comm_hook()
+
+    def _create_stream_for_optimizer(self):
+        self.optimizer_stream = self.reducer.path_stream
+
+    def _check_overlap_with_ddp(self):
+        if not hasattr(self.main_optimizer, "bind"):
+            raise ValueError("weight_sync_method='overlap' needs a Shard optimizer (ShardSGD, ShardAdam, "
+                             "ShardAdamW); use 'sequential' with a stock torch.optim optimizer")
+
+    def _create_optimizer_hook(self, hook):
+        """Chain the sharded optimizer step of a bucket behind its comm hook: the update of
+        bucket b is enqueued as soon as its allreduce is, and overlaps the rest of backward."""
+        def hook_with_optimizer_step(state, bucket):
+            fut = hook(state, bucket)
+
+            def optimizer_step(f):
+                grads = bucket.gradients()
+                for g, i in zip(grads, self.reducer.layout.bucket_indices[bucket.index()]):
+                    g.index = i
+                with self.reducer.stream_scope():
+                    self.main_optimizer.step(grads)
+                return f.value()
+            return fut.then(optimizer_step)
+        return hook_with_optimizer_step
+
+    def _prepare_overlap_optimizer_with_ddp(self):                 # jabas/train/trainer.py:327-333
+        self._create_stream_for_optimizer()
+        self._check_overlap_with_ddp()
+        for i, (local_model, state, hook) in enumerate(zip(self.local_models, self.states, self.hooks)):
+            if i == 0:
+                hook = self._create_optimizer_hook(hook)
+            local_model.register_comm_hook(state=state, hook=hook)
+
+    def _register_comm_hook(self):                                 # jabas/train/trainer.py:335-337
+        for local_model, state, hook in zip(self.local_models, self.states, self.hooks):
+            local_model.register_comm_hook(state=state, hook=hook)
+
+    # -- per iteration ---------------------------------------------------------------------
+    def set_model_train(self):
+        for m in self.local_models:
+            m.train()
+
+    def is_sync_step(self) -> bool:
+        return self.local_accum_step == self.accum_step
+
+    def compute(self, data):
+        inputs, targets = data[0], data[1]
+        K = self.num_models
+        self.parallel_compute(torch.chunk(inputs, K), torch.chunk(targets, K))
+
+    def parallel_compute(self, scatter_inputs, scatter_targets, accum_step=0):
+        """Forward + backward of the K VSWs, each on its own stream.  On the synchronising
+        micro-step the comm hooks fire bucket by bucket during the backward passes."""
+        self.local_accum_step += 1
+        sync = self.is_sync_step()
+        self.reducer.require_sync = sync
+        if self.binding is not None:
+            self.binding.sync_hyperparams()
+        if sync:
+            self.reducer.prepare_for_backward(self._is_similarity_step())
+        cur = torch.cuda.current_stream(self.device) if self._cuda else None
+        for k in range(self.num_models):
+            self.reducer.install_grad_views(k)
+            if self._cuda:
+                self.model_streams[k].wait_stream(cur)
+                with torch.cuda.stream(self.model_streams[k]):
+                    self._forward_backward(k, scatter_inputs[k], scatter_targets[k])
+            else:
+                self._forward_backward(k, scatter_inputs[k], scatter_targets[k])
+
+    def _forward_backward(self, k, inputs, targets):
+        out = self.local_models[k](inputs)
+        loss = self.criterion(out, targets)
+        self.losses[k] = loss
+        loss.backward()
+
+    def step(self) -> bool:
+        if not self.is_sync_step():
+            return False
+        eng = self.reducer.engine
+        if self._cuda:
+            cur = torch.cuda.current_stream(self.device)
+            for s in self.model_streams:
+                cur.wait_stream(s)
+        self.reducer.wait()
+        if self.weight_sync_method == "sequential":
+            with self.reducer.stream_scope():
+                self.binding.step(None)          # one fused launch over the whole flat model
+        self.binding.finish_step()
+        self._after_update()
+        eng.zero_grads()
+        self.local_accum_step = -1
+        self.sync_step += 1
+        return True
+
+    def _after_update(self):
+        """Hook for subclasses: runs after the update is enqueued, before gradients are zeroed."""
+
+    def scheduler_step(self):
+        if self.main_scheduler is not None:
+            self.main_scheduler.step()
+
+    def remaining_epochs(self, final_epochs):
+        while self.epoch < final_epochs:
+            yield self.epoch
+            self.epoch += 1
+
+    # -- profiling entry points (examples/resnet50/profiler/comp/comp_profiler.py:61-62) ------
+    def profile_parallel_compute(self, scatter_inputs, scatter_targets):
+        """(forward+backward ms, 0.0): the two phases are not separated here."""
+        a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        self.parallel_compute(scatter_inputs, scatter_targets)
+        for s in self.model_streams:
+            torch.cuda.current_stream(self.device).wait_stream(s)
+        z.record()
+        z.synchronize()
+        return a.elapsed_time(z), 0.0
+
+    def profile_step(self):
+        """(update ms, copy ms).  The weight copy is part of the update kernel: copy is 0."""
+        a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        self.step()
+        z.record()
+        z.synchronize()
+        return a.elapsed_time(z), 0.0
