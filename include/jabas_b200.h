@@ -153,6 +153,22 @@ JABAS_API int jabas_cosine_finalize(jabas_ctx_t* ctx, const double* stat3, doubl
 JABAS_API int jabas_replicate_f32(jabas_ctx_t* ctx, const float* src, float* const* dst, int ndst,
                         uint64_t n, void* stream);
 
+/* No counterpart in the reference.  Same reduction as jabas_dot_norms_f32
+ * (stat3 += (<a,b>, |a|^2, |b|^2)) for callers that cannot allocate device memory when
+ * they need it: a process whose allocator already owns all of HBM, a section that must not
+ * hit a synchronising cudaMalloc, a plugin without a context to keep a workspace in.
+ * It takes no context and calls no cudaMalloc / cudaFree: the per-CTA partial sums live in
+ * a static device array inside the library (about 48 KiB per GPU, held until exit).
+ *  - n may not exceed JABAS_STATIC_MAX_ELEMS; larger inputs are refused with JABAS_EINVAL.
+ *  - The first call on each device looks up the array's device address; make that first
+ *    call (with the device current) before any stream capture.
+ *  - All calls share the one array: two calls that overlap on the GPU (different streams,
+ *    or different threads on different streams) race.  Keep them on one stream or order
+ *    them with events. */
+#define JABAS_STATIC_MAX_ELEMS (1ull << 31)
+JABAS_API int jabas_dot_norms_static_f32(const float* a, const float* b, uint64_t n, double* stat3,
+                                         void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -940,3 +940,69 @@ int jabas_replicate_f32(jabas_ctx_t* ctx, const float* src, float* const* dst, i
 }
 
 }  // extern "C"
+
+// ----------------------------------------------------------------------------------
+// jabas_dot_norms_static_f32: the dot/norms reduction for callers that must not allocate
+// ----------------------------------------------------------------------------------
+//
+// Some hosts of this library cannot call cudaMalloc when the statistic is needed: code
+// running inside a memory pool that owns the whole device (a training process whose
+// caching allocator has reserved all HBM), a stream-ordered section that forbids
+// synchronising allocations, or a plugin that is handed raw pointers and has no context
+// of its own to keep a workspace in.  For them the per-CTA partial sums and the ticket
+// counter live in this file-scope array instead of a workspace from cudaMalloc.  Every GPU
+// that loads the library carries these 48 KiB + 256 B until the process exits.
+constexpr int kStaticMaxCtas = 2048;     // partial-sum slots: 3 doubles per CTA
+static __device__ __align__(256) unsigned char g_static_scratch[256 + sizeof(double) * 3 * kStaticMaxCtas];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+unsigned char* g_static_ptr[kMaxDevices];   // device addresses of g_static_scratch, one per device
+int g_static_sms[kMaxDevices];
+}  // namespace
+
+extern "C" int jabas_dot_norms_static_f32(const float* a, const float* b, uint64_t n, double* stat3,
+                                          void* stream)
+{
+    if (!a || !b || !stat3) return fail(JABAS_EINVAL, "a, b or stat3 is null");
+    if (n > JABAS_STATIC_MAX_ELEMS)
+        return fail(JABAS_EINVAL, "n exceeds JABAS_STATIC_MAX_ELEMS (2^31 elements): split the input or "
+                                  "use jabas_dot_norms_f32 with a context");
+    if (n == 0) return JABAS_OK;
+    int dev = -1;
+    JB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(JABAS_EINVAL, "device index beyond the static table");
+    unsigned char* base = nullptr;
+    int sms = 0;
+    {
+        // First call on this device: resolve the DEVICE address of the array.  In host code the
+        // symbol's name is only a host-side handle, never a pointer a kernel may dereference.
+        std::lock_guard<std::mutex> lk(g_static_mu);
+        if (!g_static_ptr[dev]) {
+            void* p = nullptr;
+            JB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+            JB_CUDA(cudaDeviceGetAttribute(&g_static_sms[dev], cudaDevAttrMultiProcessorCount, dev));
+            g_static_ptr[dev] = static_cast<unsigned char*>(p);
+        }
+        base = g_static_ptr[dev];
+        sms = g_static_sms[dev];
+    }
+    StatWs ws;
+    ws.counter = reinterpret_cast<unsigned int*>(base);
+    ws.partials = reinterpret_cast<double*>(base + 256);
+    const int vec = (aligned16(a) && aligned16(b)) ? 1 : 0;
+    const unsigned long long items = vec ? (n + 3) / 4 : n;
+    const unsigned long long per_cta = vec ? kThreads * 4 : kThreads;
+    unsigned long long grid = (items + per_cta - 1) / per_cta;
+    const unsigned long long cap = (unsigned long long)sms * kMaxCtasPerSm;
+    if (grid > cap) grid = cap;
+    if (grid > (unsigned long long)kStaticMaxCtas)
+        return fail(JABAS_EINVAL, "this device needs more partial-sum slots than the static scratch holds");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // The array keeps whatever the previous call left: the ticket must start at zero.
+    JB_CUDA(cudaMemsetAsync(ws.counter, 0, sizeof(unsigned int), st));
+    dot_norms_kernel<<<(int)grid, kThreads, 0, st>>>(a, b, n, vec, ws, stat3);
+    JB_CUDA(cudaGetLastError());
+    return JABAS_OK;
+}

@@ -162,6 +162,24 @@ def dot_norms(ctx: Context, a: torch.Tensor, b: torch.Tensor, stat: torch.Tensor
                                             _stream_handle(ctx.device, stream)))
 
 
+STATIC_MAX_ELEMS = 1 << 31
+
+
+def dot_norms_static(a: torch.Tensor, b: torch.Tensor, stat: torch.Tensor, *, stream=None) -> None:
+    """``stat += (<a,b>, |a|^2, |b|^2)`` without a context and without any device allocation.
+
+    For callers that cannot allocate when they need the statistic (the process's allocator
+    already owns the device, or a synchronising ``cudaMalloc`` is not acceptable where they
+    are): the reduction scratch is a static array inside the library.  At most
+    ``STATIC_MAX_ELEMS`` elements per call; all calls share the scratch, so calls that can
+    overlap on the GPU (different streams) must be ordered by the caller.  The first call on
+    a device resolves the scratch address and should come before any stream capture."""
+    dev = a.device
+    _lib.check(_lib.load().jabas_dot_norms_static_f32(
+        _dev_f32(a, dev, "a"), _dev_f32(b, dev, "b"), a.numel(), _stat_ptr(stat, dev),
+        _stream_handle(dev, stream)))
+
+
 def cosine_finalize(ctx: Context, stat: torch.Tensor, cos_out: torch.Tensor, *, eps: float = 1e-8,
                     stream=None) -> None:
     _lib.check(ctx._lib.jabas_cosine_finalize(ctx._h, _stat_ptr(stat, ctx.device), eps,
@@ -176,4 +194,4 @@ def replicate(ctx: Context, src: torch.Tensor, dsts: Sequence[torch.Tensor], *, 
 
 
 __all__ = ["Context", "Layout", "JabasError", "MAX_VSW", "MAX_GROUPS", "vsw_aggregate", "div_",
-           "sgd_momentum", "adam", "dot_norms", "cosine_finalize", "replicate"]
+           "sgd_momentum", "adam", "dot_norms", "dot_norms_static", "cosine_finalize", "replicate"]
