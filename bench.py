@@ -163,7 +163,8 @@ def _cpu_worker(rank, world, port, layout, K, opt, steps, warmup, threads, q):
     torch.set_num_threads(max(1, threads))
     if world > 1:
         dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
-    ref = ReferencePath(layout, K, opt, total_num_decoupled_workers=world * K, similarity=True, arith="torch")
+    ref = ReferencePath(layout, K, opt, total_num_decoupled_workers=world * K, similarity=True, arith="torch",
+                        world=world)
     gen = torch.Generator().manual_seed(7)
     ref.weights[0].normal_(generator=gen)
     for k in range(1, K):
@@ -263,7 +264,8 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank)
     sub_group = pair_group = None
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
         idx = [[r for r in range(world) if r % 2 == p] for p in (0, 1)]
         groups = [dist.new_group(ix) for ix in idx]
         sub_group = groups[rank % 2]
@@ -396,7 +398,7 @@ def run_ours(args):
     }
     if bus is not None:
         line["allreduce"] = bus
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:      # the CPU baseline is reported at N = 1 only
         cpu_steps = args.cpu_steps or 10
         dt, cores, threads = run_cpu_path(layout, K, opt, 1, cpu_steps, 2)
         line["cpu_baseline"] = {

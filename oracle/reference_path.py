@@ -43,12 +43,15 @@ from . import gradpath as C
 
 class ReferencePath:
     def __init__(self, layout, num_vsw: int, optimizer: dict, *, total_num_decoupled_workers: int,
-                 similarity: bool = True, arith: str = "torch", process_group=None):
+                 similarity: bool = True, arith: str = "torch", process_group=None,
+                 world: Optional[int] = None):
         self.layout, self.K, self.opt = layout, int(num_vsw), dict(optimizer)
         self.T = int(total_num_decoupled_workers)
         self.similarity = similarity
         self.arith = arith
-        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        if world is None:
+            world = dist.get_world_size() if dist.is_initialized() else 1
+        self.world = world
         self.rank = dist.get_rank() if self.world > 1 else 0
         self.pg = process_group
         n = layout.total
