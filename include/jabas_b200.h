@@ -137,6 +137,31 @@ JABAS_API int jabas_adam_f32(jabas_ctx_t* ctx, const float* g, float* const* w, 
                    const jabas_group_t* groups, int ngroups, const jabas_adam_hp_t* hp,
                    const float* half, float half_divisor, double* stat3, void* stream);
 
+/* Single-GPU form of the whole path in ONE pass: the Kg VSW gradients are summed in
+ * registers (ascending k), divided by `divisor` (T) and fed straight to the optimizer
+ * update, so the averaged gradient never makes a round trip through HBM: 4(Kg + K + 3)
+ * bytes per element for SGD-momentum instead of 4(Kg + 1) + 4(K + 4).  Kg <= 8.
+ *   grad_out  nullable: also store the averaged gradient (what jabas_vsw_aggregate_f32 writes)
+ *   stat3     nullable: += the VSW-parity statistic (even-/odd-index VSW sums / half_divisor)
+ * Results are bit-identical to jabas_vsw_aggregate_f32 followed by jabas_sgd_momentum_f32.
+ * Only valid when no collective sits between aggregation and update (one GPU).
+ * Replaces, in one launch: IIDP local aggregation + div_(T) + optimizer step
+ * (examples/resnet50/main.py:351-359) + weight copy (jabas/train/trainer.py:530-534)
+ * + cosine sums (jabas/train/trainer.py:470-483). */
+JABAS_API int jabas_vsw_sgd_momentum_f32(jabas_ctx_t* ctx, const float* const* grads, int Kg, float divisor,
+                               float* grad_out, float* const* w, int K, float* m, uint64_t n,
+                               uint64_t base, const jabas_layout_t* layout, const jabas_group_t* groups,
+                               int ngroups, const jabas_sgd_hp_t* hp, float half_divisor, double* stat3,
+                               void* stream);
+
+/* Adam / AdamW counterpart of jabas_vsw_sgd_momentum_f32 (examples/vit/main.py:433-437,
+ * examples/gnmt/seq2seq/train/shard_optimizer.py:30-90). */
+JABAS_API int jabas_vsw_adam_f32(jabas_ctx_t* ctx, const float* const* grads, int Kg, float divisor,
+                       float* grad_out, float* const* w, int K, float* m, float* v, uint64_t n,
+                       uint64_t base, const jabas_layout_t* layout, const jabas_group_t* groups,
+                       int ngroups, const jabas_adam_hp_t* hp, float half_divisor, double* stat3,
+                       void* stream);
+
 /* stat3 += (<a,b>, |a|^2, |b|^2).  Replaces the three reductions inside
  * F.cosine_similarity at jabas/train/trainer.py:478. */
 JABAS_API int jabas_dot_norms_f32(jabas_ctx_t* ctx, const float* a, const float* b, uint64_t n,

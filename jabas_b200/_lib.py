@@ -19,7 +19,8 @@ EXPORTS = (
     "jabas_version", "jabas_last_error", "jabas_ctx_create", "jabas_ctx_destroy",
     "jabas_layout_create", "jabas_layout_destroy", "jabas_vsw_aggregate_f32", "jabas_div_f32",
     "jabas_sgd_momentum_f32", "jabas_adam_f32", "jabas_dot_norms_f32", "jabas_cosine_finalize",
-    "jabas_replicate_f32", "jabas_dot_norms_static_f32",
+    "jabas_replicate_f32", "jabas_dot_norms_static_f32", "jabas_vsw_sgd_momentum_f32",
+    "jabas_vsw_adam_f32",
 )
 
 
@@ -78,6 +79,11 @@ def load() -> ctypes.CDLL:
     lib.jabas_adam_f32.argtypes = [vp, vp, pvp, i32, vp, vp, u64, u64, vp,
                                    ctypes.POINTER(Group), i32, ctypes.POINTER(AdamHp),
                                    vp, f32, vp, vp]
+    lib.jabas_vsw_sgd_momentum_f32.argtypes = [vp, pvp, i32, f32, vp, pvp, i32, vp, u64, u64, vp,
+                                               ctypes.POINTER(Group), i32, ctypes.POINTER(SgdHp),
+                                               f32, vp, vp]
+    lib.jabas_vsw_adam_f32.argtypes = [vp, pvp, i32, f32, vp, pvp, i32, vp, vp, u64, u64, vp,
+                                       ctypes.POINTER(Group), i32, ctypes.POINTER(AdamHp), f32, vp, vp]
     lib.jabas_dot_norms_f32.argtypes = [vp, vp, vp, u64, vp, vp]
     lib.jabas_cosine_finalize.argtypes = [vp, vp, f64, vp, vp]
     lib.jabas_replicate_f32.argtypes = [vp, vp, pvp, i32, u64, vp]

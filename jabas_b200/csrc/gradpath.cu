@@ -266,7 +266,11 @@ enum { OPT_SGD = 0, OPT_ADAM = 1 };
 enum { F_NESTEROV = 1, F_FIRST = 2, F_MOMENTUM = 4, F_DECOUPLED = 8 };
 
 struct UpdArgs {
-    const float* g;
+    const float* g;                     // averaged gradient (two-kernel form) ...
+    const float* gk[JABAS_MAX_VSW];     // ... or the kagg VSW gradients to aggregate on the fly
+    float* gout;                        // fused form: nullable destination of the averaged gradient
+    float divisor;                      // fused form: T
+    int kagg;                           // 0: two-kernel form
     float* w[JABAS_MAX_VSW];
     float* m;
     float* v;
@@ -349,7 +353,22 @@ __device__ __forceinline__ void upd_elem(const UpdArgs& a, unsigned long long i,
         while (__ldg(&a.segs[seg].end) <= a.base + i) ++seg;
         gi = (int)__ldg(&a.segs[seg].group);
     }
-    const float g = a.g[i];
+    float g, pe = 0.0f, po = 0.0f;
+    if (a.kagg > 0) {                   // aggregate the VSW gradients, ascending k
+        float s = a.gk[0][i];
+        pe = s;
+        for (int k = 1; k < a.kagg; ++k) {
+            const float x = a.gk[k][i];
+            s = __fadd_rn(s, x);
+            if (k == 1) po = x;
+            else if (k & 1) po = __fadd_rn(po, x);
+            else pe = __fadd_rn(pe, x);
+        }
+        g = __fdiv_rn(s, a.divisor);
+        if (a.gout) a.gout[i] = g;
+    } else {
+        g = a.g[i];
+    }
     float p = a.w[0][i];
     float m = (OPT == OPT_ADAM || ((a.flags & F_MOMENTUM) && !(a.flags & F_FIRST))) ? a.m[i] : 0.0f;
     float v = OPT == OPT_ADAM ? a.v[i] : 0.0f;
@@ -358,14 +377,23 @@ __device__ __forceinline__ void upd_elem(const UpdArgs& a, unsigned long long i,
     if (OPT == OPT_ADAM || (a.flags & F_MOMENTUM)) a.m[i] = m;
     if (OPT == OPT_ADAM) a.v[i] = v;
     if (STAT) {
-        const float e = __fdiv_rn(a.half[i], a.half_divisor);
-        acc_one(acc, e, __fmaf_rn(2.0f, g, -e));
+        if (a.kagg > 0) {
+            acc_one(acc, __fdiv_rn(pe, a.half_divisor), __fdiv_rn(po, a.half_divisor));
+        } else {
+            const float e = __fdiv_rn(a.half[i], a.half_divisor);
+            acc_one(acc, e, __fmaf_rn(2.0f, g, -e));
+        }
     }
 }
 
-template <int OPT, bool STAT, int U>
+// KAGG = 0: g is read from a.g.  KAGG > 0 (single-GPU form): the KAGG VSW gradients are
+// summed in registers (ascending k), divided by T and consumed at once, so the averaged
+// gradient never makes a round trip through HBM; the statistic then comes from the
+// even-/odd-VSW partial sums that are in registers anyway.
+template <int OPT, bool STAT, int U, int KAGG>
 __global__ void __launch_bounds__(kThreads) upd_vec_kernel(const UpdArgs a)
 {
+    constexpr int KX = KAGG > 0 ? KAGG : 1;
     const unsigned long long nvec = a.n >> 2;
     const unsigned long long tile = (unsigned long long)kThreads * U;
     const bool use_m = OPT == OPT_ADAM || (a.flags & F_MOMENTUM);
@@ -374,17 +402,43 @@ __global__ void __launch_bounds__(kThreads) upd_vec_kernel(const UpdArgs a)
     for (unsigned long long t0 = (unsigned long long)blockIdx.x * tile; t0 < nvec;
          t0 += (unsigned long long)gridDim.x * tile) {
         const bool full = t0 + tile <= nvec;
-        float4 g[U], p[U], m[U], v[U], hs[U];
+        float4 g[U], p[U], m[U], v[U], hs[U], xk[U][KX];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const unsigned long long x = t0 + (unsigned long long)u * kThreads + threadIdx.x;
             m[u] = v[u] = hs[u] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (full || x < nvec) {
-                g[u] = ld4(a.g + 4 * x);
+                if (KAGG > 0) {
+#pragma unroll
+                    for (int k = 0; k < KX; ++k) xk[u][k] = ld4(a.gk[k] + 4 * x);
+                } else {
+                    g[u] = ld4(a.g + 4 * x);
+                }
                 p[u] = ld4(a.w[0] + 4 * x);
                 if (load_m) m[u] = ld4(a.m + 4 * x);
                 if (OPT == OPT_ADAM) v[u] = ld4(a.v + 4 * x);
-                if (STAT) hs[u] = ld4(a.half + 4 * x);
+                if (STAT && KAGG == 0) hs[u] = ld4(a.half + 4 * x);
+            }
+        }
+        if (KAGG > 0) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const unsigned long long x = t0 + (unsigned long long)u * kThreads + threadIdx.x;
+                if (!(full || x < nvec)) continue;
+                float4 s = xk[u][0];
+#pragma unroll
+                for (int k = 1; k < KX; ++k) s = add4(s, xk[u][k]);
+                g[u] = div4(s, a.divisor);
+                if (a.gout) st4(a.gout + 4 * x, g[u]);
+                if (STAT) {
+                    float4 e = xk[u][0];
+                    float4 o = xk[u][KX > 1 ? 1 : 0];
+#pragma unroll
+                    for (int k = 2; k < KX; ++k) {
+                        if (k & 1) o = add4(o, xk[u][k]); else e = add4(e, xk[u][k]);
+                    }
+                    acc_vec(acc, div4(e, a.half_divisor), div4(o, a.half_divisor));
+                }
             }
         }
         // segment of the tile's first element; uniform over the CTA
@@ -402,7 +456,7 @@ __global__ void __launch_bounds__(kThreads) upd_vec_kernel(const UpdArgs a)
         for (int u = 0; u < U; ++u) {
             const unsigned long long x = t0 + (unsigned long long)u * kThreads + threadIdx.x;
             if (!(full || x < nvec)) continue;
-            half_stat4<STAT>(a, g[u], hs[u], acc);
+            half_stat4<(STAT && KAGG == 0)>(a, g[u], hs[u], acc);
             if (uniform) {
                 upd_math4<OPT>(a, a.grp[gi0], (a.wd_mask >> gi0) & 1u, g[u], p[u], m[u], v[u]);
             } else {
@@ -640,19 +694,33 @@ int agg_dispatch(jabas_ctx_t* ctx, const AggArgs& a, cudaStream_t st)
     return fail(JABAS_EINVAL, "K out of range");
 }
 
+constexpr int kMaxFusedVsw = 8;     // the fused aggregate+update form is instantiated for K <= 8
+
+template <int OPT, int KAGG>
+int upd_launch_vec(jabas_ctx_t* ctx, const UpdArgs& a, cudaStream_t st)
+{
+    if (a.kagg != KAGG) {
+        if constexpr (KAGG < kMaxFusedVsw) return upd_launch_vec<OPT, KAGG + 1>(ctx, a, st);
+        return fail(JABAS_EINVAL, "fused aggregate+update supports at most 8 VSWs");
+    }
+    constexpr int U = KAGG > 4 ? 1 : 2;
+    int grid = 0, rc;
+    if (a.stat) {
+        if ((rc = grid_for(ctx, upd_vec_kernel<OPT, true, U, KAGG>, a.n >> 2, (unsigned long long)kThreads * U, &grid))) return rc;
+        upd_vec_kernel<OPT, true, U, KAGG><<<grid, kThreads, 0, st>>>(a);
+    } else {
+        if ((rc = grid_for(ctx, upd_vec_kernel<OPT, false, U, KAGG>, a.n >> 2, (unsigned long long)kThreads * U, &grid))) return rc;
+        upd_vec_kernel<OPT, false, U, KAGG><<<grid, kThreads, 0, st>>>(a);
+    }
+    return JABAS_OK;
+}
+
 template <int OPT>
 int upd_launch(jabas_ctx_t* ctx, const UpdArgs& a, bool vec, cudaStream_t st)
 {
-    constexpr int U = OPT == OPT_SGD ? 2 : 2;
     int grid = 0, rc;
     if (vec) {
-        if (a.stat) {
-            if ((rc = grid_for(ctx, upd_vec_kernel<OPT, true, U>, a.n >> 2, (unsigned long long)kThreads * U, &grid))) return rc;
-            upd_vec_kernel<OPT, true, U><<<grid, kThreads, 0, st>>>(a);
-        } else {
-            if ((rc = grid_for(ctx, upd_vec_kernel<OPT, false, U>, a.n >> 2, (unsigned long long)kThreads * U, &grid))) return rc;
-            upd_vec_kernel<OPT, false, U><<<grid, kThreads, 0, st>>>(a);
-        }
+        if ((rc = upd_launch_vec<OPT, 0>(ctx, a, st))) return rc;
     } else {
         if (a.stat) {
             if ((rc = grid_for(ctx, upd_scalar_kernel<OPT, true>, a.n, kThreads, &grid))) return rc;
@@ -666,25 +734,56 @@ int upd_launch(jabas_ctx_t* ctx, const UpdArgs& a, bool vec, cudaStream_t st)
     return JABAS_OK;
 }
 
+// Where the gradient of an update comes from: one averaged buffer, or K VSW buffers that the
+// kernel aggregates itself (single-GPU form).
+struct GradSrc {
+    const float* g;
+    const float* const* grads;
+    int kg;
+    float divisor;
+    float* gout;
+};
+
 // Validation and argument marshalling shared by the two optimizers.
-int upd_prepare(jabas_ctx_t* ctx, UpdArgs& a, bool* vec, const float* g, float* const* w, int K,
+int upd_prepare(jabas_ctx_t* ctx, UpdArgs& a, bool* vec, const GradSrc& src, float* const* w, int K,
                 float* m, float* v, uint64_t n, uint64_t base, const jabas_layout_t* layout,
                 const jabas_group_t* groups, int ngroups, const float* half, float half_divisor,
                 double* stat3, void* stream)
 {
     int rc = ctx_bind(ctx);
     if (rc) return rc;
-    if (!g || !w) return fail(JABAS_EINVAL, "g or w is null");
+    if (!w) return fail(JABAS_EINVAL, "w is null");
     if (K < 1 || K > JABAS_MAX_VSW) return fail(JABAS_EINVAL, "K must be in [1, JABAS_MAX_VSW]");
+    const bool fused = src.grads != nullptr;
+    if (!fused && !src.g) return fail(JABAS_EINVAL, "g is null");
+    if (fused) {
+        if (src.kg < 1 || src.kg > kMaxFusedVsw)
+            return fail(JABAS_EINVAL, "fused aggregate+update supports 1..8 VSW gradients");
+        if (!(src.divisor != 0.0f)) return fail(JABAS_EINVAL, "divisor must be non-zero");
+        if (half) return fail(JABAS_EINVAL, "the fused form takes its statistic from the VSW gradients, not from half");
+        if (stat3 && (src.kg < 2 || !(half_divisor != 0.0f)))
+            return fail(JABAS_EINVAL, "the VSW-parity statistic needs K >= 2 and a non-zero half_divisor");
+    }
     if (!groups || ngroups < 1 || ngroups > JABAS_MAX_GROUPS)
         return fail(JABAS_EINVAL, "ngroups must be in [1, JABAS_MAX_GROUPS]");
-    if ((half == nullptr) != (stat3 == nullptr))
+    if (!fused && (half == nullptr) != (stat3 == nullptr))
         return fail(JABAS_EINVAL, "half and stat3 must both be set or both be null");
     if (half && !(half_divisor != 0.0f)) return fail(JABAS_EINVAL, "half_divisor must be non-zero");
     std::memset(&a, 0, sizeof(a));
-    a.g = g; a.m = m; a.v = v; a.half = half; a.stat = stat3;
+    a.g = src.g; a.m = m; a.v = v; a.half = half; a.stat = stat3;
     a.n = n; a.base = base; a.K = K; a.half_divisor = half_divisor;
-    *vec = aligned16(g) && (!m || aligned16(m)) && (!v || aligned16(v)) && (!half || aligned16(half));
+    *vec = (!m || aligned16(m)) && (!v || aligned16(v)) && (!half || aligned16(half));
+    if (fused) {
+        a.kagg = src.kg; a.divisor = src.divisor; a.gout = src.gout;
+        *vec = *vec && (!src.gout || aligned16(src.gout));
+        for (int k = 0; k < src.kg; ++k) {
+            if (!src.grads[k]) return fail(JABAS_EINVAL, "grads[k] is null");
+            a.gk[k] = src.grads[k];
+            *vec = *vec && aligned16(src.grads[k]);
+        }
+    } else {
+        *vec = *vec && aligned16(src.g);
+    }
     for (int k = 0; k < K; ++k) {
         if (!w[k]) return fail(JABAS_EINVAL, "w[k] is null");
         a.w[k] = w[k];
@@ -831,15 +930,15 @@ int jabas_div_f32(jabas_ctx_t* ctx, float* x, uint64_t n, float divisor, void* s
     return JABAS_OK;
 }
 
-int jabas_sgd_momentum_f32(jabas_ctx_t* ctx, const float* g, float* const* w, int K, float* m,
-                           uint64_t n, uint64_t base, const jabas_layout_t* layout,
-                           const jabas_group_t* groups, int ngroups, const jabas_sgd_hp_t* hp,
-                           const float* half, float half_divisor, double* stat3, void* stream)
+static int sgd_impl(jabas_ctx_t* ctx, const GradSrc& src, float* const* w, int K, float* m,
+                    uint64_t n, uint64_t base, const jabas_layout_t* layout,
+                    const jabas_group_t* groups, int ngroups, const jabas_sgd_hp_t* hp,
+                    const float* half, float half_divisor, double* stat3, void* stream)
 {
     if (!hp) return fail(JABAS_EINVAL, "hp is null");
     UpdArgs a;
     bool vec = false;
-    int rc = upd_prepare(ctx, a, &vec, g, w, K, m, nullptr, n, base, layout, groups, ngroups, half,
+    int rc = upd_prepare(ctx, a, &vec, src, w, K, m, nullptr, n, base, layout, groups, ngroups, half,
                          half_divisor, stat3, stream);
     if (rc) return rc;
     if (hp->momentum != 0.0 && !m) return fail(JABAS_EINVAL, "momentum != 0 needs a momentum buffer");
@@ -858,15 +957,36 @@ int jabas_sgd_momentum_f32(jabas_ctx_t* ctx, const float* g, float* const* w, in
     return upd_launch<OPT_SGD>(ctx, a, vec, static_cast<cudaStream_t>(stream));
 }
 
-int jabas_adam_f32(jabas_ctx_t* ctx, const float* g, float* const* w, int K, float* m, float* v,
-                   uint64_t n, uint64_t base, const jabas_layout_t* layout,
-                   const jabas_group_t* groups, int ngroups, const jabas_adam_hp_t* hp,
-                   const float* half, float half_divisor, double* stat3, void* stream)
+int jabas_sgd_momentum_f32(jabas_ctx_t* ctx, const float* g, float* const* w, int K, float* m,
+                           uint64_t n, uint64_t base, const jabas_layout_t* layout,
+                           const jabas_group_t* groups, int ngroups, const jabas_sgd_hp_t* hp,
+                           const float* half, float half_divisor, double* stat3, void* stream)
+{
+    const GradSrc src = {g, nullptr, 0, 1.0f, nullptr};
+    if (!g) return fail(JABAS_EINVAL, "g is null");
+    return sgd_impl(ctx, src, w, K, m, n, base, layout, groups, ngroups, hp, half, half_divisor, stat3, stream);
+}
+
+int jabas_vsw_sgd_momentum_f32(jabas_ctx_t* ctx, const float* const* grads, int Kg, float divisor,
+                               float* grad_out, float* const* w, int K, float* m, uint64_t n,
+                               uint64_t base, const jabas_layout_t* layout, const jabas_group_t* groups,
+                               int ngroups, const jabas_sgd_hp_t* hp, float half_divisor, double* stat3,
+                               void* stream)
+{
+    if (!grads) return fail(JABAS_EINVAL, "grads is null");
+    const GradSrc src = {nullptr, grads, Kg, divisor, grad_out};
+    return sgd_impl(ctx, src, w, K, m, n, base, layout, groups, ngroups, hp, nullptr, half_divisor, stat3, stream);
+}
+
+static int adam_impl(jabas_ctx_t* ctx, const GradSrc& src, float* const* w, int K, float* m, float* v,
+                     uint64_t n, uint64_t base, const jabas_layout_t* layout,
+                     const jabas_group_t* groups, int ngroups, const jabas_adam_hp_t* hp,
+                     const float* half, float half_divisor, double* stat3, void* stream)
 {
     if (!hp) return fail(JABAS_EINVAL, "hp is null");
     UpdArgs a;
     bool vec = false;
-    int rc = upd_prepare(ctx, a, &vec, g, w, K, m, v, n, base, layout, groups, ngroups, half,
+    int rc = upd_prepare(ctx, a, &vec, src, w, K, m, v, n, base, layout, groups, ngroups, half,
                          half_divisor, stat3, stream);
     if (rc) return rc;
     if (!m || !v) return fail(JABAS_EINVAL, "exp_avg and exp_avg_sq buffers are required");
@@ -886,6 +1006,26 @@ int jabas_adam_f32(jabas_ctx_t* ctx, const float* g, float* const* w, int K, flo
         if (groups[i].weight_decay != 0.0) a.wd_mask |= 1u << i;
     }
     return upd_launch<OPT_ADAM>(ctx, a, vec, static_cast<cudaStream_t>(stream));
+}
+
+int jabas_adam_f32(jabas_ctx_t* ctx, const float* g, float* const* w, int K, float* m, float* v,
+                   uint64_t n, uint64_t base, const jabas_layout_t* layout,
+                   const jabas_group_t* groups, int ngroups, const jabas_adam_hp_t* hp,
+                   const float* half, float half_divisor, double* stat3, void* stream)
+{
+    const GradSrc src = {g, nullptr, 0, 1.0f, nullptr};
+    if (!g) return fail(JABAS_EINVAL, "g is null");
+    return adam_impl(ctx, src, w, K, m, v, n, base, layout, groups, ngroups, hp, half, half_divisor, stat3, stream);
+}
+
+int jabas_vsw_adam_f32(jabas_ctx_t* ctx, const float* const* grads, int Kg, float divisor, float* grad_out,
+                       float* const* w, int K, float* m, float* v, uint64_t n, uint64_t base,
+                       const jabas_layout_t* layout, const jabas_group_t* groups, int ngroups,
+                       const jabas_adam_hp_t* hp, float half_divisor, double* stat3, void* stream)
+{
+    if (!grads) return fail(JABAS_EINVAL, "grads is null");
+    const GradSrc src = {nullptr, grads, Kg, divisor, grad_out};
+    return adam_impl(ctx, src, w, K, m, v, n, base, layout, groups, ngroups, hp, nullptr, half_divisor, stat3, stream);
 }
 
 int jabas_dot_norms_f32(jabas_ctx_t* ctx, const float* a, const float* b, uint64_t n, double* stat3,

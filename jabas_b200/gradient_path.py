@@ -252,6 +252,41 @@ class GradientPath:
         self._ev_end("update", b, ev)
         self.launches += 1
 
+    def can_fuse_local(self) -> bool:
+        """One GPU and few enough VSWs: aggregation and update can be one kernel."""
+        return self.world == 1 and self.K <= getattr(self.ops, "MAX_FUSED_VSW", 0)
+
+    def fused_local_step(self, b: Optional[int] = None, keep_grad: bool = False) -> None:
+        """Single-GPU path in ONE launch over bucket ``b`` (None: the whole flat model):
+        sum the K VSW gradients in registers, divide by T, update, write the new weights to
+        all K replicas, accumulate the VSW-parity statistic.  The averaged gradient is only
+        stored (into VSW 0's buffer) when ``keep_grad`` is set."""
+        if b is None:
+            begin, end = 0, self.layout.total
+        else:
+            begin, end = self.layout.buckets[b]
+        if end == begin:
+            return
+        gs = [g[begin:end] for g in self.grads]
+        ws = [w[begin:end] for w in self.weights]
+        kw = dict(layout=self.dev_layout, base=begin, grad_out=gs[0] if keep_grad else None)
+        if self._sim_step:
+            kw.update(half_divisor=self.T / 2, stat=self.stat)
+        o = self.opt
+        ev = self._ev_begin()
+        if o.kind == "sgd":
+            self.ops.vsw_sgd_momentum(self.ctx, gs, float(self.T), ws,
+                                      None if self.m is None else self.m[begin:end], o.groups,
+                                      momentum=o.momentum, dampening=o.dampening, nesterov=o.nesterov,
+                                      first_step=(self.steps == 0), **kw)
+        else:
+            groups = [dict(gr, step=self.steps + 1) for gr in o.groups]
+            self.ops.vsw_adam(self.ctx, gs, float(self.T), ws, self.m[begin:end], self.v[begin:end], groups,
+                              beta1=o.betas[0], beta2=o.betas[1], eps=o.eps,
+                              decoupled=(o.kind == "adamw"), **kw)
+        self._ev_end("fused_step", b, ev)
+        self.launches += 1
+
     def end_iteration(self) -> None:
         self.steps += 1
 
@@ -277,7 +312,7 @@ class GradientPath:
 
     # -- whole iteration, buckets in ready order (used by the benchmark and by tests) ---
     def run_iteration(self, similarity_step: Optional[bool] = None, overlap: bool = True,
-                      per_bucket: Optional[bool] = None):
+                      per_bucket: Optional[bool] = None, fuse_local: Optional[bool] = None):
         """One pass of the path.  ``per_bucket`` (default: only when there are collectives
         to overlap) walks the DDP buckets as the comm hooks do during backward; otherwise
         the whole flat model goes through each kernel in one launch."""
@@ -285,7 +320,11 @@ class GradientPath:
         nb = self.layout.num_buckets
         if per_bucket is None:
             per_bucket = self.world > 1
-        if not per_bucket:
+        if fuse_local is None:
+            fuse_local = self.can_fuse_local() and not per_bucket
+        if fuse_local:
+            self.fused_local_step(None)
+        elif not per_bucket:
             self.aggregate(None)
             self.allreduce(None)
             self.update(None)
@@ -316,7 +355,8 @@ class GradientPath:
         if self.opt.kind == "sgd" and self.opt.momentum == 0:
             per_elem = K + 2
         upd = 4 * n * per_elem + (4 * n if (similarity_step and multi) else 0)
-        return {"aggregate": agg, "update": upd, "total": agg + upd}
+        fused = 4 * n * (K + per_elem - 1)          # the averaged gradient stays in registers
+        return {"aggregate": agg, "update": upd, "total": agg + upd, "fused_step": fused}
 
     def close(self) -> None:
         if self.dev_layout is not None:

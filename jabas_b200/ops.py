@@ -155,6 +155,44 @@ def adam(ctx: Context, g: torch.Tensor, weights: Sequence[torch.Tensor], m: torc
         _stat_ptr(stat, ctx.device), _stream_handle(ctx.device, stream)))
 
 
+MAX_FUSED_VSW = 8
+
+
+def vsw_sgd_momentum(ctx: Context, grads: Sequence[torch.Tensor], divisor: float,
+                     weights: Sequence[torch.Tensor], m: Optional[torch.Tensor], groups: Sequence[dict], *,
+                     momentum: float = 0.0, dampening: float = 0.0, nesterov: bool = False,
+                     first_step: bool = False, layout: Optional[Layout] = None, base: int = 0,
+                     grad_out: Optional[torch.Tensor] = None, half_divisor: float = 1.0,
+                     stat: Optional[torch.Tensor] = None, stream=None) -> None:
+    """Single-GPU path in one launch: aggregate the VSW gradients, update, write back."""
+    hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step))
+    gp = _ptr_array([_dev_f32(g, ctx.device, "grads[k]") for g in grads])
+    wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
+    _lib.check(ctx._lib.jabas_vsw_sgd_momentum_f32(
+        ctx._h, gp, len(grads), divisor,
+        None if grad_out is None else _dev_f32(grad_out, ctx.device, "grad_out"), wp, len(weights),
+        None if m is None else _dev_f32(m, ctx.device, "m"), weights[0].numel(), base,
+        None if layout is None else layout._h, _groups_array(groups), len(groups), ctypes.byref(hp),
+        half_divisor, _stat_ptr(stat, ctx.device), _stream_handle(ctx.device, stream)))
+
+
+def vsw_adam(ctx: Context, grads: Sequence[torch.Tensor], divisor: float,
+             weights: Sequence[torch.Tensor], m: torch.Tensor, v: torch.Tensor, groups: Sequence[dict], *,
+             beta1: float, beta2: float, eps: float, decoupled: bool, layout: Optional[Layout] = None,
+             base: int = 0, grad_out: Optional[torch.Tensor] = None, half_divisor: float = 1.0,
+             stat: Optional[torch.Tensor] = None, stream=None) -> None:
+    """Adam / AdamW counterpart of :func:`vsw_sgd_momentum`."""
+    hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0)
+    gp = _ptr_array([_dev_f32(g, ctx.device, "grads[k]") for g in grads])
+    wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
+    _lib.check(ctx._lib.jabas_vsw_adam_f32(
+        ctx._h, gp, len(grads), divisor,
+        None if grad_out is None else _dev_f32(grad_out, ctx.device, "grad_out"), wp, len(weights),
+        _dev_f32(m, ctx.device, "m"), _dev_f32(v, ctx.device, "v"), weights[0].numel(), base,
+        None if layout is None else layout._h, _groups_array(groups), len(groups), ctypes.byref(hp),
+        half_divisor, _stat_ptr(stat, ctx.device), _stream_handle(ctx.device, stream)))
+
+
 def dot_norms(ctx: Context, a: torch.Tensor, b: torch.Tensor, stat: torch.Tensor, *, stream=None) -> None:
     _lib.check(ctx._lib.jabas_dot_norms_f32(ctx._h, _dev_f32(a, ctx.device, "a"),
                                             _dev_f32(b, ctx.device, "b"), a.numel(),
@@ -194,4 +232,4 @@ def replicate(ctx: Context, src: torch.Tensor, dsts: Sequence[torch.Tensor], *, 
 
 
 __all__ = ["Context", "Layout", "JabasError", "MAX_VSW", "MAX_GROUPS", "vsw_aggregate", "div_",
-           "sgd_momentum", "adam", "dot_norms", "dot_norms_static", "cosine_finalize", "replicate"]
+           "sgd_momentum", "adam", "vsw_sgd_momentum", "vsw_adam", "MAX_FUSED_VSW", "dot_norms", "dot_norms_static", "cosine_finalize", "replicate"]

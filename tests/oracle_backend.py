@@ -90,3 +90,19 @@ def replicate(ctx, src, dsts, *, stream=None):
     for d in dsts:
         if d.data_ptr() != src.data_ptr():
             d.copy_(src)
+
+
+MAX_FUSED_VSW = 8
+
+
+def vsw_sgd_momentum(ctx, grads, divisor, weights, m, groups, *, grad_out=None, half_divisor=1.0, stat=None,
+                     **kw):
+    g = torch.empty_like(weights[0]) if grad_out is None else grad_out
+    vsw_aggregate(ctx, grads, g, divisor, half_divisor=half_divisor, stat=stat)
+    sgd_momentum(ctx, g, weights, m, groups, **kw)
+
+
+def vsw_adam(ctx, grads, divisor, weights, m, v, groups, *, grad_out=None, half_divisor=1.0, stat=None, **kw):
+    g = torch.empty_like(weights[0]) if grad_out is None else grad_out
+    vsw_aggregate(ctx, grads, g, divisor, half_divisor=half_divisor, stat=stat)
+    adam(ctx, g, weights, m, v, groups, **kw)

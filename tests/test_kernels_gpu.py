@@ -310,3 +310,64 @@ def test_streams_have_independent_statistic_workspaces(ctx):
     for st in stats:
         assert np.allclose(_host(st), 5 * ref, rtol=1e-6)
         assert np.array_equal(_host(st), _host(stats[0]))
+
+
+@pytest.mark.parametrize("n", [3, 1025, 2 ** 20 + 1, 5 * 2 ** 20 + 2])
+@pytest.mark.parametrize("K", [1, 2, 4, 5, 8])
+@pytest.mark.parametrize("opt", ["sgd", "adamw", "adam"])
+@pytest.mark.parametrize("offset", [0, 1])
+def test_fused_aggregate_update_equals_two_kernel_path(ctx, n, K, opt, offset):
+    """Single-GPU form: one launch must reproduce aggregate -> update bit for bit, with
+    param-group segments, write-back to all replicas and the VSW-parity statistic."""
+    from jabas_b200 import ops
+    if offset and n > 2 ** 20 + 1:
+        pytest.skip("scalar kernels are covered by the smaller sizes")
+    rng = np.random.default_rng(n % 953 + 7 * K)
+    segs = _segments(rng, n, 2, 40)
+    layout = ops.Layout(ctx, segs, n)
+    groups = [dict(lr=0.1, weight_decay=0.0, step=3), dict(lr=0.05, weight_decay=1e-2, step=3)]
+    common = _rand(rng, n, 1e-3)
+    grads = [(_rand(rng, n, 1e-3) + 0.5 * common).astype(np.float32) for _ in range(K)]
+    p, m, v = _rand(rng, n), _rand(rng, n, 1e-3), np.abs(_rand(rng, n, 1e-6))
+    T = float(2 * K)
+    g = np.empty(n, np.float32)
+    O.vsw_aggregate(grads, g, T)
+    st_o = O.vsw_parity_stat(grads, T / 2) if K >= 2 else None
+    if opt == "sgd":
+        O.update_segments("sgd", g, p_o := p.copy(), m_o := m.copy(), None, segs,
+                          [dict(lr=x["lr"], weight_decay=x["weight_decay"]) for x in groups], momentum=0.9)
+        v_o = v
+    else:
+        O.update_segments("adam", g, p_o := p.copy(), m_o := m.copy(), v_o := v.copy(), segs, groups,
+                          beta1=0.9, beta2=0.999, eps=1e-8, decoupled=(opt == "adamw"))
+    dg = [_dev(x, offset) for x in grads]
+    w = [_dev(p, offset)] + [torch.empty(n + offset, device="cuda")[offset:] for _ in range(2)]
+    dm, dv = _dev(m, offset), _dev(v, offset)
+    gout = torch.empty(n + offset, device="cuda")[offset:]
+    stat = torch.zeros(3, dtype=torch.float64, device="cuda") if K >= 2 else None
+    kw = dict(layout=layout, grad_out=gout, half_divisor=T / 2, stat=stat)
+    if opt == "sgd":
+        ops.vsw_sgd_momentum(ctx, dg, T, w, dm, groups, momentum=0.9, **kw)
+    else:
+        ops.vsw_adam(ctx, dg, T, w, dm, dv, groups, beta1=0.9, beta2=0.999, eps=1e-8,
+                     decoupled=(opt == "adamw"), **kw)
+    assert np.array_equal(_host(gout), g)
+    for k in range(3):
+        assert np.array_equal(_host(w[k]), p_o), k
+    assert np.array_equal(_host(dm), m_o)
+    assert np.array_equal(_host(dv), v_o)
+    if K >= 2:
+        assert np.allclose(_host(stat), st_o, rtol=1e-6, atol=0)
+    layout.close()
+
+
+def test_fused_form_argument_errors(ctx):
+    from jabas_b200 import ops, JabasError
+    x = torch.zeros(64, device="cuda")
+    with pytest.raises(JabasError, match="1..8"):
+        ops.vsw_sgd_momentum(ctx, [x] * 9, 9.0, [x.clone()], x.clone(), [dict(lr=0.1)], momentum=0.9)
+    with pytest.raises(JabasError, match="divisor"):
+        ops.vsw_sgd_momentum(ctx, [x] * 2, 0.0, [x.clone()], x.clone(), [dict(lr=0.1)], momentum=0.9)
+    with pytest.raises(JabasError, match="K >= 2"):
+        ops.vsw_sgd_momentum(ctx, [x], 1.0, [x.clone()], x.clone(), [dict(lr=0.1)], momentum=0.9,
+                             stat=torch.zeros(3, dtype=torch.float64, device="cuda"))
