@@ -71,6 +71,8 @@ typedef struct {
     double dampening;
     int    nesterov;
     int    first_step;  /* 1: momentum buffer is created from the gradient (m = d)   */
+    const float* grad_scale;  /* DEVICE scalar, nullable: when *grad_scale < 1 the gradient is
+                                 multiplied by it before the update (jabas_clip_coef)       */
 } jabas_sgd_hp_t;
 
 typedef struct {
@@ -79,6 +81,7 @@ typedef struct {
     double eps;
     int    decoupled;   /* 1: AdamW (p *= 1 - lr*wd); 0: Adam (g += wd*p)            */
     int    reserved;
+    const float* grad_scale;  /* as in jabas_sgd_hp_t */
 } jabas_adam_hp_t;
 
 JABAS_API int         jabas_version(void);
@@ -166,6 +169,17 @@ JABAS_API int jabas_vsw_adam_f32(jabas_ctx_t* ctx, const float* const* grads, in
  * F.cosine_similarity at jabas/train/trainer.py:478. */
 JABAS_API int jabas_dot_norms_f32(jabas_ctx_t* ctx, const float* a, const float* b, uint64_t n,
                         double* stat3, void* stream);
+
+/* stat3[0..2] += sum of x[i]^2 (fp64).  First half of gradient-norm clipping:
+ * clip_grad_norm_for_overlap at examples/gnmt/seq2seq/train/shard_optimizer.py:75-76 and
+ * clip_grad_norm_ at examples/gnmt/seq2seq/train/trainer.py:157-161. */
+JABAS_API int jabas_sumsq_f32(jabas_ctx_t* ctx, const float* x, uint64_t n, double* stat3, void* stream);
+
+/* coef_out[0] = max_norm / (sqrt(sumsq[0]) + 1e-6) in fp32, coef_out[1] = the norm: the
+ * clip coefficient of torch.nn.utils.clip_grad_norm_ (PyTorch v1.8.1).  Pass coef_out as
+ * `grad_scale` of the update: the gradient is scaled only when the coefficient is < 1. */
+JABAS_API int jabas_clip_coef(jabas_ctx_t* ctx, const double* sumsq, double max_norm, float* coef_out,
+                    void* stream);
 
 /* cos_out[0] = stat3[0] / sqrt(max(stat3[1]*stat3[2], eps^2)), evaluated in fp64.
  * Replaces the final division of F.cosine_similarity (jabas/train/trainer.py:478). */

@@ -271,6 +271,7 @@ struct UpdArgs {
     float* gout;                        // fused form: nullable destination of the averaged gradient
     float divisor;                      // fused form: T
     int kagg;                           // 0: two-kernel form
+    const float* grad_scale;            // nullable device scalar: g *= *grad_scale when it is < 1 (norm clipping)
     float* w[JABAS_MAX_VSW];
     float* m;
     float* v;
@@ -369,6 +370,11 @@ __device__ __forceinline__ void upd_elem(const UpdArgs& a, unsigned long long i,
     } else {
         g = a.g[i];
     }
+    const float g_unclipped = g;
+    if (a.grad_scale) {
+        const float gs = __ldg(a.grad_scale);
+        if (gs < 1.0f) g = __fmul_rn(g, gs);
+    }
     float p = a.w[0][i];
     float m = (OPT == OPT_ADAM || ((a.flags & F_MOMENTUM) && !(a.flags & F_FIRST))) ? a.m[i] : 0.0f;
     float v = OPT == OPT_ADAM ? a.v[i] : 0.0f;
@@ -381,7 +387,7 @@ __device__ __forceinline__ void upd_elem(const UpdArgs& a, unsigned long long i,
             acc_one(acc, __fdiv_rn(pe, a.half_divisor), __fdiv_rn(po, a.half_divisor));
         } else {
             const float e = __fdiv_rn(a.half[i], a.half_divisor);
-            acc_one(acc, e, __fmaf_rn(2.0f, g, -e));
+            acc_one(acc, e, __fmaf_rn(2.0f, g_unclipped, -e));
         }
     }
 }
@@ -394,6 +400,8 @@ template <int OPT, bool STAT, int U, int KAGG>
 __global__ void __launch_bounds__(kThreads) upd_vec_kernel(const UpdArgs a)
 {
     constexpr int KX = KAGG > 0 ? KAGG : 1;
+    const float gscale = a.grad_scale ? __ldg(a.grad_scale) : 1.0f;
+    const bool clip = gscale < 1.0f;
     const unsigned long long nvec = a.n >> 2;
     const unsigned long long tile = (unsigned long long)kThreads * U;
     const bool use_m = OPT == OPT_ADAM || (a.flags & F_MOMENTUM);
@@ -457,6 +465,9 @@ __global__ void __launch_bounds__(kThreads) upd_vec_kernel(const UpdArgs a)
             const unsigned long long x = t0 + (unsigned long long)u * kThreads + threadIdx.x;
             if (!(full || x < nvec)) continue;
             half_stat4<(STAT && KAGG == 0)>(a, g[u], hs[u], acc);
+            if (clip)
+                g[u] = make_float4(__fmul_rn(g[u].x, gscale), __fmul_rn(g[u].y, gscale),
+                                   __fmul_rn(g[u].z, gscale), __fmul_rn(g[u].w, gscale));
             if (uniform) {
                 upd_math4<OPT>(a, a.grp[gi0], (a.wd_mask >> gi0) & 1u, g[u], p[u], m[u], v[u]);
             } else {
@@ -511,6 +522,7 @@ __global__ void __launch_bounds__(kThreads) div_kernel(float* x, unsigned long l
     }
 }
 
+template <bool ONE>   // ONE: b is a, read once (sum of squares)
 __global__ void __launch_bounds__(kThreads) dot_norms_kernel(const float* a, const float* b,
                                                              unsigned long long n, int vec,
                                                              StatWs ws, double* stat)
@@ -527,7 +539,7 @@ __global__ void __launch_bounds__(kThreads) dot_norms_kernel(const float* a, con
             for (int u = 0; u < U; ++u) {
                 const unsigned long long i = t0 + (unsigned long long)u * kThreads + threadIdx.x;
                 x[u] = y[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (i < nvec) { x[u] = ld4(a + 4 * i); y[u] = ld4(b + 4 * i); }
+                if (i < nvec) { x[u] = ld4(a + 4 * i); y[u] = ONE ? x[u] : ld4(b + 4 * i); }
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) acc_vec(acc, x[u], y[u]);
@@ -549,6 +561,15 @@ __global__ void cosine_finalize_kernel(const double* stat, double eps, float* ou
     double den = stat[1] * stat[2];
     if (den < eps * eps) den = eps * eps;
     out[0] = (float)(stat[0] / sqrt(den));
+}
+
+// torch.nn.utils.clip_grad_norm_ of PyTorch v1.8.1 on the fp64 sum of squares:
+// total_norm = sqrt(sumsq) as fp32, clip_coef = max_norm / (total_norm + 1e-6) in fp32.
+__global__ void clip_coef_kernel(const double* sumsq, float max_norm, float* out)
+{
+    const float total = (float)sqrt(sumsq[0]);
+    out[0] = __fdiv_rn(max_norm, __fadd_rn(total, 1e-6f));
+    out[1] = total;
 }
 
 struct RepArgs {
@@ -945,6 +966,7 @@ static int sgd_impl(jabas_ctx_t* ctx, const GradSrc& src, float* const* w, int K
     if (hp->nesterov && (hp->momentum <= 0.0 || hp->dampening != 0.0))
         return fail(JABAS_EINVAL, "nesterov needs momentum > 0 and dampening == 0");
     if (n == 0) return JABAS_OK;
+    a.grad_scale = hp->grad_scale;
     a.c0 = (float)hp->momentum;
     a.c1 = (float)(1.0 - hp->dampening);
     a.flags = (hp->nesterov ? F_NESTEROV : 0u) | (hp->first_step ? F_FIRST : 0u) |
@@ -991,6 +1013,7 @@ static int adam_impl(jabas_ctx_t* ctx, const GradSrc& src, float* const* w, int 
     if (rc) return rc;
     if (!m || !v) return fail(JABAS_EINVAL, "exp_avg and exp_avg_sq buffers are required");
     if (n == 0) return JABAS_OK;
+    a.grad_scale = hp->grad_scale;
     a.c0 = (float)hp->beta1; a.c1 = (float)hp->beta2;
     a.c2 = (float)(1.0 - hp->beta1); a.c3 = (float)(1.0 - hp->beta2);
     a.c4 = (float)hp->eps;
@@ -1039,8 +1062,35 @@ int jabas_dot_norms_f32(jabas_ctx_t* ctx, const float* a, const float* b, uint64
     if ((rc = ws_for(ctx, stream, &ws))) return rc;
     const int vec = (aligned16(a) && aligned16(b)) ? 1 : 0;
     int grid = 0;
-    if ((rc = grid_for(ctx, dot_norms_kernel, vec ? (n + 3) / 4 : n, vec ? kThreads * 4 : kThreads, &grid))) return rc;
-    dot_norms_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(a, b, n, vec, ws, stat3);
+    if ((rc = grid_for(ctx, dot_norms_kernel<false>, vec ? (n + 3) / 4 : n, vec ? kThreads * 4 : kThreads, &grid))) return rc;
+    dot_norms_kernel<false><<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(a, b, n, vec, ws, stat3);
+    JB_CUDA(cudaGetLastError());
+    return JABAS_OK;
+}
+
+int jabas_sumsq_f32(jabas_ctx_t* ctx, const float* x, uint64_t n, double* stat3, void* stream)
+{
+    int rc = ctx_bind(ctx);
+    if (rc) return rc;
+    if (!x || !stat3) return fail(JABAS_EINVAL, "x or stat3 is null");
+    if (n == 0) return JABAS_OK;
+    StatWs ws;
+    if ((rc = ws_for(ctx, stream, &ws))) return rc;
+    const int vec = aligned16(x) ? 1 : 0;
+    int grid = 0;
+    if ((rc = grid_for(ctx, dot_norms_kernel<true>, vec ? (n + 3) / 4 : n, vec ? kThreads * 4 : kThreads, &grid))) return rc;
+    dot_norms_kernel<true><<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, x, n, vec, ws, stat3);
+    JB_CUDA(cudaGetLastError());
+    return JABAS_OK;
+}
+
+int jabas_clip_coef(jabas_ctx_t* ctx, const double* sumsq, double max_norm, float* coef_out, void* stream)
+{
+    int rc = ctx_bind(ctx);
+    if (rc) return rc;
+    if (!sumsq || !coef_out) return fail(JABAS_EINVAL, "sumsq or coef_out is null");
+    if (!(max_norm > 0.0)) return fail(JABAS_EINVAL, "max_norm must be positive");
+    clip_coef_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(sumsq, (float)max_norm, coef_out);
     JB_CUDA(cudaGetLastError());
     return JABAS_OK;
 }
@@ -1142,7 +1192,7 @@ extern "C" int jabas_dot_norms_static_f32(const float* a, const float* b, uint64
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // The array keeps whatever the previous call left: the ticket must start at zero.
     JB_CUDA(cudaMemsetAsync(ws.counter, 0, sizeof(unsigned int), st));
-    dot_norms_kernel<<<(int)grid, kThreads, 0, st>>>(a, b, n, vec, ws, stat3);
+    dot_norms_kernel<false><<<(int)grid, kThreads, 0, st>>>(a, b, n, vec, ws, stat3);
     JB_CUDA(cudaGetLastError());
     return JABAS_OK;
 }

@@ -102,6 +102,11 @@ class GradientPath:
         self.half_divided = set()                    # pair_exchange: buckets whose E is materialised
         self.launches = 0                            # kernels of libjabas_b200 enqueued so far
         self.profile_events: Optional[list] = None   # set to [] to time every kernel with CUDA events
+        nb = layout.num_buckets
+        # gradient-norm clipping: one (sum of squares, coefficient) slot per bucket + one for the model
+        self.clip_stat = torch.zeros(nb + 1, 3, dtype=torch.float64, device=self.device)
+        self.clip_coef = torch.ones(nb + 1, 2, **f32)
+        self._clip_active: Dict[int, bool] = {}
         if optimizer is not None:
             self.set_optimizer(optimizer)
 
@@ -162,6 +167,7 @@ class GradientPath:
     def begin_iteration(self, similarity_step: Optional[bool] = None) -> None:
         self._sim_step = self.similarity if similarity_step is None else (similarity_step and self.similarity)
         self._pending.clear()
+        self._clip_active.clear()
         self.half_divided = set()
         if self._sim_step:
             self.stat.zero_()
@@ -236,6 +242,11 @@ class GradientPath:
                     self.ops.div_(self.ctx, self._sl(self.half, bb), self.T / 2)
                     self.half_divided.add(bb)
                     self.launches += 1
+        nb = self.layout.num_buckets
+        if (nb if b is None else b) in self._clip_active:
+            kw["grad_scale"] = self.clip_coef[nb if b is None else b]
+        elif nb in self._clip_active:
+            kw["grad_scale"] = self.clip_coef[nb]
         g = self.main_grad[begin:end]
         ws = [w[begin:end] for w in self.weights]
         o = self.opt
@@ -251,6 +262,28 @@ class GradientPath:
                           decoupled=(o.kind == "adamw"), **kw)
         self._ev_end("update", b, ev)
         self.launches += 1
+
+    def clip_grad_norm(self, b: Optional[int], max_norm: float) -> torch.Tensor:
+        """L2-norm clipping of the averaged gradient of bucket ``b`` (None: the whole model),
+        as ``clip_grad_norm_for_overlap`` / ``clip_grad_norm_`` do in the reference
+        (examples/gnmt/seq2seq/train/shard_optimizer.py:75-76, seq2seq/train/trainer.py:157-161).
+        One reduction kernel over the gradient (after its allreduce) and a 1-thread kernel
+        produce the coefficient on the device; the following ``update`` multiplies the
+        gradient by it in registers when it is < 1.  Returns the norm (device scalar)."""
+        nb = self.layout.num_buckets
+        slot = nb if b is None else b
+        if b is None:
+            for bb in list(self._pending):
+                self.wait_allreduce(bb)
+        else:
+            self.wait_allreduce(b)
+        st = self.clip_stat[slot]
+        st.zero_()
+        self.ops.sumsq(self.ctx, self._sl(self.main_grad, b), st)
+        self.ops.clip_coef(self.ctx, st, float(max_norm), self.clip_coef[slot])
+        self.launches += 2
+        self._clip_active[slot] = True
+        return self.clip_coef[slot][1]
 
     def can_fuse_local(self) -> bool:
         """One GPU and few enough VSWs: aggregation and update can be one kernel."""

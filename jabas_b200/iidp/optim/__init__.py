@@ -37,6 +37,7 @@ class FusedBinding:
         engine.layout.set_groups([group_of[id(p)] for p in self.params])
         for i, p in enumerate(self.params):
             p.index = i                              # the matching key of ShardOptimizer.step
+            p._jabas_binding = self
         self.kind = self._kind(optimizer)
         engine.set_optimizer(self._spec())
         self._install_state_views()
@@ -88,13 +89,29 @@ class FusedBinding:
         for g, dst in zip(self.optimizer.param_groups, spec.groups):
             dst["lr"], dst["weight_decay"] = float(g["lr"]), float(g.get("weight_decay", 0.0))
 
+    def request_model_clip(self, max_norm: float) -> torch.Tensor:
+        """Whole-model norm clipping for the NEXT whole-model step (sequential mode): the
+        reduction runs inside that step, once every bucket's allreduce has been waited for.
+        Returns the device scalar that will hold the norm."""
+        self.model_clip = float(max_norm)
+        return self.engine.clip_coef[self.engine.layout.num_buckets][1]
+
     def step(self, buckets: Optional[Iterable[int]] = None) -> None:
         self.sync_hyperparams()
         if buckets is None:
+            if getattr(self, "model_clip", None) is not None:
+                self.engine.clip_grad_norm(None, self.model_clip)
+                self.model_clip = None
             self.engine.update(None)
         else:
             for b in buckets:
                 self.engine.update(b)
+
+    def clip(self, buckets: Optional[Iterable[int]], max_norm: float):
+        """Norm clipping of the given buckets' gradients (None: one norm over the model)."""
+        if buckets is None:
+            return self.engine.clip_grad_norm(None, max_norm)
+        return [self.engine.clip_grad_norm(b, max_norm) for b in buckets]
 
     def finish_step(self) -> None:
         """Once per iteration, after every bucket was updated."""
@@ -126,10 +143,16 @@ class _ShardMixin:
         if self._binding is None:
             raise RuntimeError(f"{type(self).__name__} is not bound to the flat gradient storage: "
                                "pass it to IIDPTrainer.prepare_weight_sync_method first")
+        clip = getattr(self, "grad_clip", float("inf"))
         if gradients is None:
+            if clip != float("inf"):
+                self._binding.request_model_clip(clip)
             self._binding.step(None)
         else:
-            self._binding.step(self._binding.buckets_of(gradients))
+            buckets = self._binding.buckets_of(gradients)
+            if clip != float("inf") and len(gradients) > 0:      # shard_optimizer.py:75-76
+                self._binding.clip(buckets, clip)
+            self._binding.step(buckets)
 
 
 class ShardSGD(_ShardMixin, torch.optim.SGD):
@@ -139,9 +162,17 @@ class ShardSGD(_ShardMixin, torch.optim.SGD):
 
 
 class ShardAdam(_ShardMixin, torch.optim.Adam):
-    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0, amsgrad=False):
+    """``grad_clip`` clips the L2 norm of each bucket's gradient before its update, as
+    ``ShardGNMTAdam`` does (examples/gnmt/seq2seq/train/shard_optimizer.py:8-29, 75-76)."""
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0, amsgrad=False,
+                 grad_clip=float("inf")):
         torch.optim.Adam.__init__(self, params, lr=lr, betas=betas, eps=eps,
                                   weight_decay=weight_decay, amsgrad=amsgrad)
+        self.grad_clip = grad_clip
+        if grad_clip != float("inf") and len(self.param_groups) > 1:
+            raise ValueError("Length of self.param_groups must not be > 1 "
+                             "because of applying gradient clipping")
 
 
 class ShardAdamW(_ShardMixin, torch.optim.AdamW):

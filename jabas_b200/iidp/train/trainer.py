@@ -185,6 +185,7 @@ class IIDPTrainer(object):
                 grads = bucket.gradients()
                 for g, i in zip(grads, self.reducer.layout.bucket_indices[bucket.index()]):
                     g.index = i
+                    g._jabas_binding = self.binding
                 with self.reducer.stream_scope():
                     self.main_optimizer.step(grads)
                 return f.value()

@@ -37,6 +37,14 @@ def _stat_ptr(stat: Optional[torch.Tensor], device: torch.device) -> Optional[in
     return stat.data_ptr()
 
 
+def _scale_ptr(t: Optional[torch.Tensor], device: torch.device) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda or t.device != device or t.dtype != torch.float32 or t.numel() < 1:
+        raise JabasError("grad_scale must be a float32 tensor on the context's device")
+    return t.data_ptr()
+
+
 def _ptr_array(ptrs: Sequence[int]):
     return (ctypes.c_void_p * len(ptrs))(*ptrs)
 
@@ -127,9 +135,10 @@ def sgd_momentum(ctx: Context, g: torch.Tensor, weights: Sequence[torch.Tensor],
                  dampening: float = 0.0, nesterov: bool = False, first_step: bool = False,
                  layout: Optional[Layout] = None, base: int = 0,
                  half: Optional[torch.Tensor] = None, half_divisor: float = 1.0,
-                 stat: Optional[torch.Tensor] = None, stream=None) -> None:
+                 stat: Optional[torch.Tensor] = None, grad_scale: Optional[torch.Tensor] = None,
+                 stream=None) -> None:
     """Fused SGD-momentum update of ``weights[0]`` with write-back to every replica."""
-    hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step))
+    hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), _scale_ptr(grad_scale, ctx.device))
     wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
     _lib.check(ctx._lib.jabas_sgd_momentum_f32(
         ctx._h, _dev_f32(g, ctx.device, "g"), wp, len(weights),
@@ -143,9 +152,10 @@ def adam(ctx: Context, g: torch.Tensor, weights: Sequence[torch.Tensor], m: torc
          v: torch.Tensor, groups: Sequence[dict], *, beta1: float, beta2: float, eps: float,
          decoupled: bool, layout: Optional[Layout] = None, base: int = 0,
          half: Optional[torch.Tensor] = None, half_divisor: float = 1.0,
-         stat: Optional[torch.Tensor] = None, stream=None) -> None:
+         stat: Optional[torch.Tensor] = None, grad_scale: Optional[torch.Tensor] = None,
+         stream=None) -> None:
     """Fused Adam (``decoupled=False``) / AdamW (``True``) update with write-back."""
-    hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0)
+    hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0, _scale_ptr(grad_scale, ctx.device))
     wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
     _lib.check(ctx._lib.jabas_adam_f32(
         ctx._h, _dev_f32(g, ctx.device, "g"), wp, len(weights), _dev_f32(m, ctx.device, "m"),
@@ -163,9 +173,10 @@ def vsw_sgd_momentum(ctx: Context, grads: Sequence[torch.Tensor], divisor: float
                      momentum: float = 0.0, dampening: float = 0.0, nesterov: bool = False,
                      first_step: bool = False, layout: Optional[Layout] = None, base: int = 0,
                      grad_out: Optional[torch.Tensor] = None, half_divisor: float = 1.0,
-                     stat: Optional[torch.Tensor] = None, stream=None) -> None:
+                     stat: Optional[torch.Tensor] = None, grad_scale: Optional[torch.Tensor] = None,
+                     stream=None) -> None:
     """Single-GPU path in one launch: aggregate the VSW gradients, update, write back."""
-    hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step))
+    hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), _scale_ptr(grad_scale, ctx.device))
     gp = _ptr_array([_dev_f32(g, ctx.device, "grads[k]") for g in grads])
     wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
     _lib.check(ctx._lib.jabas_vsw_sgd_momentum_f32(
@@ -180,9 +191,10 @@ def vsw_adam(ctx: Context, grads: Sequence[torch.Tensor], divisor: float,
              weights: Sequence[torch.Tensor], m: torch.Tensor, v: torch.Tensor, groups: Sequence[dict], *,
              beta1: float, beta2: float, eps: float, decoupled: bool, layout: Optional[Layout] = None,
              base: int = 0, grad_out: Optional[torch.Tensor] = None, half_divisor: float = 1.0,
-             stat: Optional[torch.Tensor] = None, stream=None) -> None:
+             stat: Optional[torch.Tensor] = None, grad_scale: Optional[torch.Tensor] = None,
+             stream=None) -> None:
     """Adam / AdamW counterpart of :func:`vsw_sgd_momentum`."""
-    hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0)
+    hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0, _scale_ptr(grad_scale, ctx.device))
     gp = _ptr_array([_dev_f32(g, ctx.device, "grads[k]") for g in grads])
     wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
     _lib.check(ctx._lib.jabas_vsw_adam_f32(
@@ -198,6 +210,22 @@ def dot_norms(ctx: Context, a: torch.Tensor, b: torch.Tensor, stat: torch.Tensor
                                             _dev_f32(b, ctx.device, "b"), a.numel(),
                                             _stat_ptr(stat, ctx.device),
                                             _stream_handle(ctx.device, stream)))
+
+
+def sumsq(ctx: Context, x: torch.Tensor, stat: torch.Tensor, *, stream=None) -> None:
+    """stat[0..2] += sum of squares of x (fp64)."""
+    _lib.check(ctx._lib.jabas_sumsq_f32(ctx._h, _dev_f32(x, ctx.device, "x"), x.numel(),
+                                        _stat_ptr(stat, ctx.device), _stream_handle(ctx.device, stream)))
+
+
+def clip_coef(ctx: Context, sumsq_stat: torch.Tensor, max_norm: float, coef_out: torch.Tensor, *,
+              stream=None) -> None:
+    """coef_out[0] = max_norm / (sqrt(sumsq) + 1e-6), coef_out[1] = the norm (fp32, 2 elements)."""
+    if coef_out.numel() < 2:
+        raise JabasError("coef_out needs two float32 elements (coefficient, norm)")
+    _lib.check(ctx._lib.jabas_clip_coef(ctx._h, _stat_ptr(sumsq_stat, ctx.device), max_norm,
+                                        _dev_f32(coef_out, ctx.device, "coef_out"),
+                                        _stream_handle(ctx.device, stream)))
 
 
 STATIC_MAX_ELEMS = 1 << 31
@@ -232,4 +260,4 @@ def replicate(ctx: Context, src: torch.Tensor, dsts: Sequence[torch.Tensor], *, 
 
 
 __all__ = ["Context", "Layout", "JabasError", "MAX_VSW", "MAX_GROUPS", "vsw_aggregate", "div_",
-           "sgd_momentum", "adam", "vsw_sgd_momentum", "vsw_adam", "MAX_FUSED_VSW", "dot_norms", "dot_norms_static", "cosine_finalize", "replicate"]
+           "sgd_momentum", "adam", "vsw_sgd_momentum", "vsw_adam", "MAX_FUSED_VSW", "sumsq", "clip_coef", "dot_norms", "dot_norms_static", "cosine_finalize", "replicate"]

@@ -55,6 +55,8 @@ def _load():
         lib.oracle_replicate_f32.argtypes = [_f32p, pp, ctypes.c_int, sz]
         lib.oracle_sumsq_f32.argtypes = [_f32p, sz]
         lib.oracle_sumsq_f32.restype = ctypes.c_double
+        lib.oracle_clip_grad_norm_f32.argtypes = [_f32p, sz, ctypes.c_double, _f32p]
+        lib.oracle_clip_grad_norm_f32.restype = ctypes.c_float
         for name in ("oracle_vsw_aggregate_f32", "oracle_div_f32", "oracle_dot_norms_f32",
                      "oracle_half_stat_f32", "oracle_vsw_parity_stat_f32",
                      "oracle_sgd_momentum_f32", "oracle_adam_f32", "oracle_replicate_f32"):
@@ -139,6 +141,13 @@ def replicate(src: np.ndarray, dsts: Sequence[np.ndarray]) -> None:
 
 def sumsq(x: np.ndarray) -> float:
     return float(_load().oracle_sumsq_f32(_p(x), x.size))
+
+
+def clip_grad_norm(g: np.ndarray, max_norm: float):
+    """In-place L2-norm clipping of a flat gradient; returns (coefficient, norm)."""
+    norm = ctypes.c_float()
+    coef = _load().oracle_clip_grad_norm_f32(_p(g), g.size, max_norm, ctypes.byref(norm))
+    return float(coef), float(norm.value)
 
 
 def update_segments(kind: str, g, p, m, v, segments, groups, **common) -> None:

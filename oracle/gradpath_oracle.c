@@ -200,3 +200,20 @@ ORACLE_API double oracle_sumsq_f32(const float* x, size_t n)
     for (size_t i = 0; i < n; ++i) s += (double)x[i] * (double)x[i];
     return s;
 }
+
+/* torch.nn.utils.clip_grad_norm_ of PyTorch v1.8.1 (norm_type 2), as reached from
+ * examples/gnmt/seq2seq/train/trainer.py:157-161 and, per bucket, from
+ * clip_grad_norm_for_overlap at examples/gnmt/seq2seq/train/shard_optimizer.py:75-76:
+ *   total_norm = sqrt(sum g^2)  (here from the fp64 sum, rounded to fp32)
+ *   clip_coef  = max_norm / (total_norm + 1e-6)              (fp32)
+ *   if clip_coef < 1:  g = g * clip_coef                      (mul_)
+ * Returns the coefficient; *norm_out (nullable) receives total_norm. */
+ORACLE_API float oracle_clip_grad_norm_f32(float* g, size_t n, double max_norm, float* norm_out)
+{
+    const float total = (float)sqrt(oracle_sumsq_f32(g, n));
+    const float coef = (float)max_norm / (total + 1e-6f);
+    if (norm_out) *norm_out = total;
+    if (coef < 1.0f)
+        for (size_t i = 0; i < n; ++i) g[i] = g[i] * coef;
+    return coef;
+}

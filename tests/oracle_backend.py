@@ -58,9 +58,11 @@ def _replicate(weights):
 
 
 def sgd_momentum(ctx, g, weights, m, groups, *, momentum=0.0, dampening=0.0, nesterov=False,
-                 first_step=False, layout=None, base=0, half=None, half_divisor=1.0, stat=None, stream=None):
+                 first_step=False, layout=None, base=0, half=None, half_divisor=1.0, stat=None, grad_scale=None,
+                 stream=None):
     if stat is not None:
         O.half_stat(_np(g), _np(half), half_divisor, _np(stat))
+    g = _scaled(g, grad_scale)
     mm = _np(m) if m is not None else np.zeros(g.numel(), np.float32)
     O.update_segments("sgd", _np(g), _np(weights[0]), mm, None, _segments(layout, base, g.numel()),
                       [dict(lr=x["lr"], weight_decay=x.get("weight_decay", 0.0)) for x in groups],
@@ -69,13 +71,30 @@ def sgd_momentum(ctx, g, weights, m, groups, *, momentum=0.0, dampening=0.0, nes
 
 
 def adam(ctx, g, weights, m, v, groups, *, beta1, beta2, eps, decoupled, layout=None, base=0,
-         half=None, half_divisor=1.0, stat=None, stream=None):
+         half=None, half_divisor=1.0, stat=None, grad_scale=None, stream=None):
     if stat is not None:
         O.half_stat(_np(g), _np(half), half_divisor, _np(stat))
+    g = _scaled(g, grad_scale)
     O.update_segments("adam", _np(g), _np(weights[0]), _np(m), _np(v), _segments(layout, base, g.numel()),
                       [dict(lr=x["lr"], weight_decay=x.get("weight_decay", 0.0), step=x["step"]) for x in groups],
                       beta1=beta1, beta2=beta2, eps=eps, decoupled=decoupled)
     _replicate(weights)
+
+
+def sumsq(ctx, x, stat, *, stream=None):
+    _np(stat)[:] += O.sumsq(_np(x))
+
+
+def clip_coef(ctx, sumsq_stat, max_norm, coef_out, *, stream=None):
+    total = np.float32(np.sqrt(_np(sumsq_stat)[0]))
+    coef_out[0] = float(np.float32(max_norm) / (total + np.float32(1e-6)))
+    coef_out[1] = float(total)
+
+
+def _scaled(g, grad_scale):
+    if grad_scale is None or float(grad_scale[0]) >= 1.0:
+        return g
+    return (g * grad_scale[0]).to(torch.float32)
 
 
 def dot_norms(ctx, a, b, stat, *, stream=None):

@@ -371,3 +371,39 @@ def test_fused_form_argument_errors(ctx):
     with pytest.raises(JabasError, match="K >= 2"):
         ops.vsw_sgd_momentum(ctx, [x], 1.0, [x.clone()], x.clone(), [dict(lr=0.1)], momentum=0.9,
                              stat=torch.zeros(3, dtype=torch.float64, device="cuda"))
+
+
+@pytest.mark.parametrize("n", [5, 1025, 2 ** 20 + 3])
+@pytest.mark.parametrize("opt", ["sgd", "adam"])
+@pytest.mark.parametrize("max_norm", [0.01, 1e6])
+def test_gradient_norm_clipping(ctx, n, opt, max_norm):
+    """sumsq -> clip_coef -> update(grad_scale): the clip of clip_grad_norm_ (active for the
+    small max_norm, inactive for the large one) folded into the update kernel."""
+    from jabas_b200 import ops
+    rng = np.random.default_rng(n)
+    g, p = _rand(rng, n, 1e-2), _rand(rng, n)
+    m, v = np.zeros(n, np.float32), np.zeros(n, np.float32)
+    dg, w, dm, dv = _dev(g), [_dev(p), torch.empty(n, device="cuda")], _dev(m), _dev(v)
+    st = torch.zeros(3, dtype=torch.float64, device="cuda")
+    coef = torch.zeros(2, device="cuda")
+    ops.sumsq(ctx, dg, st)
+    ops.clip_coef(ctx, st, max_norm, coef)
+    gc = g.copy()
+    coef_o, norm_o = O.clip_grad_norm(gc, max_norm)
+    assert np.allclose(_host(st), O.sumsq(g), rtol=1e-6)
+    assert abs(float(coef[1]) - norm_o) <= 1e-6 * norm_o
+    assert (coef_o < 1.0) == (max_norm < 1.0)
+    if opt == "sgd":
+        O.sgd_momentum(gc, p, m, lr=0.1, weight_decay=1e-4, momentum=0.9, first_step=True)
+        ops.sgd_momentum(ctx, dg, w, dm, [dict(lr=0.1, weight_decay=1e-4)], momentum=0.9, first_step=True,
+                         grad_scale=coef)
+    else:
+        O.adam(gc, p, m, v, lr=1e-3, weight_decay=0.0, beta1=0.9, beta2=0.999, eps=1e-8, step=1, decoupled=False)
+        ops.adam(ctx, dg, w, dm, dv, [dict(lr=1e-3, step=1)], beta1=0.9, beta2=0.999, eps=1e-8,
+                 decoupled=False, grad_scale=coef)
+    if float(coef[0]) == np.float32(coef_o):
+        assert np.array_equal(_host(w[0]), p) and np.array_equal(_host(w[1]), p)
+        assert np.array_equal(_host(dm), m)
+    else:                                               # the two fp64 sums rounded to neighbouring fp32 norms
+        assert np.allclose(_host(w[0]), p, rtol=1e-6, atol=1e-9)
+    assert np.array_equal(_host(dg), g)                 # the gradient buffer itself is not rewritten

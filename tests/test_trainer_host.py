@@ -277,3 +277,49 @@ def test_two_gloo_ranks_match_reference_path(mode, kind, wsm):
         assert w <= 1e-6, (rank, w)          # fp32 weights within 1e-6 relative after the allreduce
         assert c <= 1e-5, (rank, c)          # cosine within 1e-5 absolute
         assert same                          # every rank holds rank 0's value
+
+
+def test_gradient_norm_clipping_sequential_and_overlap():
+    """Whole-model clipping (sequential mode, clip_grad_norm_ between compute and step) and
+    per-bucket clipping (overlap mode, ShardAdam(grad_clip=...)) against the oracle."""
+    from jabas_b200.iidp.optim import ShardAdam
+    from jabas_b200.iidp.utils.clip_grad import clip_grad_norm_
+    from oracle import gradpath as O
+    K, clip = 2, 0.05
+    for wsm in ("sequential", "overlap"):
+        tr = jabas_b200.JABASTrainer("cpu", 8, K, 0, wsm, dict(CFG))
+        tr._backend = oracle_backend
+        tr.prepare_stream_parallel(_model(), torch.nn.CrossEntropyLoss(), bucket_cap_mb=0.01,
+                                   first_bucket_bytes=2048)
+        params = list(tr.main_model.parameters())
+        if wsm == "overlap":
+            opt = ShardAdam(params, lr=1e-2, grad_clip=clip)
+        else:
+            opt = torch.optim.Adam(params, lr=1e-2)
+        tr.prepare_weight_sync_method(opt)
+        lay = tr.reducer.layout
+        ref = ReferencePath(lay, K, dict(kind="adam", groups=[dict(lr=1e-2, weight_decay=0.0)],
+                                         betas=(0.9, 0.999), eps=1e-8),
+                            total_num_decoupled_workers=K, arith="c")
+        for k in range(K):
+            ref.weights[k].copy_(tr.reducer.engine.weights[k])
+        x, y = torch.randn(16, 20), torch.randint(0, 10, (16,))
+        for k, flat in enumerate(_vsw_gradients(tr, x, y)):
+            ref.grads[k].copy_(flat)
+        for b in range(lay.num_buckets):
+            ref.reduce_bucket(b, True)
+        g = ref.grads[0].numpy()
+        if wsm == "overlap":
+            norms = [O.clip_grad_norm(g[bb:be], clip)[1] for bb, be in lay.buckets]
+            assert max(norms) > clip                          # the clip is active
+        else:
+            coef, norm = O.clip_grad_norm(g, clip)
+            assert coef < 1.0
+        ref.optimizer_step(); ref.copy_weights(); ref.compute_cosine_similarity()
+        tr.compute((x, y))
+        if wsm == "sequential":
+            total = clip_grad_norm_(tr.main_model.parameters(), clip)
+        tr.step()
+        assert torch.equal(tr.reducer.engine.weights[K - 1], ref.weights[0]), wsm
+        if wsm == "sequential":
+            assert abs(float(total) - norm) < 1e-6 * norm
