@@ -128,6 +128,26 @@ class GradientPath:
         if self.v is None and optimizer.kind != "sgd":
             self.v = torch.zeros(n, **f32)
 
+    def resize_vsw(self, new_k: int) -> None:
+        """Change the number of VSW replicas at run time (jabas/train/trainer.py:485-575)
+        without touching the buffers that stay: growing appends flat weight / gradient
+        buffers and fills the new weights from the main replica with one kernel; shrinking
+        drops the last ones.  Optimizer state, segment table and bucket layout are unchanged."""
+        new_k = int(new_k)
+        if not 1 <= new_k <= getattr(self.ops, "MAX_VSW", 16):
+            raise ValueError("the number of VSWs must be between 1 and 16")
+        f32 = dict(dtype=torch.float32, device=self.device)
+        if new_k > self.K:
+            fresh = [torch.empty(self.layout.total, **f32) for _ in range(new_k - self.K)]
+            self.ops.replicate(self.ctx, self.weights[0], fresh)
+            self.launches += 1
+            self.weights.extend(fresh)
+            self.grads.extend(torch.zeros(self.layout.total, **f32) for _ in range(new_k - self.K))
+        else:
+            del self.weights[new_k:]
+            del self.grads[new_k:]
+        self.K = new_k
+
     def set_total_workers(self, total_num_decoupled_workers: int) -> None:
         """T changes when VSWs are added or removed at run time
         (jabas/train/trainer.py:543-544, 570-571)."""

@@ -204,6 +204,75 @@ class IIDPTrainer(object):
         for local_model, state, hook in zip(self.local_models, self.states, self.hooks):
             local_model.register_comm_hook(state=state, hook=hook)
 
+    # -- run-time reconfiguration (jabas/train/trainer.py:485-600) ----------------------------
+    def _change_local_trainer_state(self, new_num_models, new_accum_step):
+        """Deltas, as in the reference: ``new_num_models`` VSWs and ``new_accum_step``
+        accumulation steps are ADDED to the current values."""
+        self.prev_num_models = self.num_models
+        if new_num_models != 0:
+            self.num_models = self.prev_num_models + new_num_models
+            assert self.num_models > 0, "self.num_models must be > 0"
+            self.num_local_models = self.num_models
+        if new_accum_step != 0:
+            self.accum_step = self.accum_step + new_accum_step
+            self.is_accum_mode = self.accum_step > 0
+        self.batch_size_per_gpu = self.local_batch_size * self.num_models
+        if getattr(self, "data_loader", None) is not None and hasattr(self.data_loader, "update_local_state"):
+            self.data_loader.update_local_state(self.batch_size_per_gpu, self.num_models, self.accum_step)
+
+    def _change_global_trainer_state(self, solved_iidp_config_map=None):
+        self._get_total_num_decoupled_workers()
+        self.global_batch_size = self.local_batch_size * self.total_num_decoupled_workers
+
+    def _change_local_models_state(self, adjust_num_models_diff):
+        """Add or remove VSWs between two iterations.  The flat buffers of the VSWs that
+        stay are not reallocated; new replicas get their weights from the main replica by
+        one kernel; T reaches the hook states and the kernels' divisors."""
+        K_old, K_new = self.prev_num_models, self.num_models
+        assert K_new == K_old + adjust_num_models_diff
+        if self._cuda:
+            torch.cuda.current_stream(self.device).synchronize()
+        T = self.total_num_decoupled_workers
+        self.reducer.resize(K_new, T)
+        if adjust_num_models_diff > 0:
+            for idx in range(K_old, K_new):
+                self.model_streams.append(torch.cuda.Stream(self.device) if self._cuda else None)
+                copied = copy.deepcopy(self.main_model.module)
+                self.original_local_models.append(copied)
+                wrapper = IndependentIdenticalDataParallel(
+                    copied, device_ids=[self.gpu], output_device=[self.gpu], model_index=idx,
+                    num_local_models=K_new, total_num_models=T, reducer=self.reducer)
+                wrapper.train(self.main_model.training)
+                self.local_models.append(wrapper)
+                self.local_optimizers.append(_ReplicaOptimizer(self.main_optimizer, self.reducer, idx))
+                self.local_schedulers.append(None)
+                self.states.append(None)
+                self.hooks.append(dummy_hook)
+                wrapper.register_comm_hook(state=None, hook=dummy_hook)
+        else:
+            for _ in range(K_new, K_old):
+                for lst in (self.local_models, self.original_local_models, self.local_optimizers,
+                            self.local_schedulers, self.model_streams, self.states, self.hooks):
+                    del lst[-1]
+        assert len(self.local_models) == self.num_models == len(self.local_optimizers)
+        for m in self.local_models:
+            m.reconfigure(self.num_models, T, self._sync_buffer_barrier)
+        if self.states and self.states[0] is not None:
+            self.states[0].total_num_decoupled_workers = T
+            if hasattr(self.states[0], "subgroup_total_num_decoupled_workers"):
+                assert T % 2 == 0
+                self.states[0].subgroup_total_num_decoupled_workers = T / 2
+
+    def change_num_models(self, new_num_models: int, new_accum_step=None):
+        """Convenience over the three reference-named steps: set K (and optionally the
+        accumulation steps) on THIS rank, re-derive T over all ranks, rebuild local state.
+        Collective: every rank must call it (T is all-gathered)."""
+        d_models = int(new_num_models) - self.num_models
+        d_accum = 0 if new_accum_step is None else int(new_accum_step) - self.accum_step
+        self._change_local_trainer_state(d_models, d_accum)
+        self._change_global_trainer_state()
+        self._change_local_models_state(d_models)
+
     # -- per iteration ---------------------------------------------------------------------
     def set_model_train(self):
         for m in self.local_models:

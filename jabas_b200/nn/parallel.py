@@ -158,6 +158,19 @@ class VSWReducer:
         for i, p in enumerate(params):
             p.register_post_accumulate_grad_hook(self._make_hook(k, self.layout.slots[i].bucket))
 
+    def resize(self, new_k: int, total_num_models: int) -> None:
+        """Grow or shrink the set of VSWs.  Wrappers of removed VSWs are dropped here; the
+        caller constructs ``IndependentIdenticalDataParallel`` wrappers for the new indices,
+        whose ``attach`` finds the flat buffers already in place."""
+        self.engine.resize_vsw(new_k)
+        if new_k > self.K:
+            self.wrappers.extend([None] * (new_k - self.K))
+        else:
+            del self.wrappers[new_k:]
+        self.K, self.T = int(new_k), int(total_num_models)
+        self.engine.set_total_workers(total_num_models)
+        self._reset_counters()
+
     def install_grad_views(self, k: int) -> None:
         flat = self.engine.grads[k]
         for p, slot in zip(self.wrappers[k]._params, self.layout.slots):
@@ -305,8 +318,7 @@ class IndependentIdenticalDataParallel(nn.Module):
     def reconfigure(self, num_local_models, total_num_models, sync_buffer_barrier=None) -> None:
         """T changed (jabas/train/trainer.py:526-528); a change of K rebuilds the reducer."""
         if int(num_local_models) != self.reducer.K:
-            raise NotImplementedError("changing the number of VSWs rebuilds the flat storage: "
-                                      "create a new VSWReducer")
+            raise ValueError("resize the shared VSWReducer first (VSWReducer.resize), then reconfigure")
         self.num_local_models, self.total_num_models = int(num_local_models), int(total_num_models)
         self.sync_buffer_barrier = sync_buffer_barrier
         self.reducer.T = int(total_num_models)

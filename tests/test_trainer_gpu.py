@@ -91,3 +91,41 @@ def test_trainer_on_gpu_matches_reference_path(wsm, kind, K):
         for p0, pk in zip(tr.local_models[0].parameters(), tr.local_models[K - 1].parameters()):
             assert torch.equal(p0, pk)
     assert tr.reducer.engine.launches > launches0          # the CUDA library did the work
+
+
+def test_runtime_change_of_vsw_count_on_gpu():
+    """K: 2 -> 4 -> 2 between iterations on the device: surviving flat buffers keep their
+    addresses, new replicas are filled by the replicate kernel, steps keep all replicas equal."""
+    import jabas_b200
+    from jabas_b200.iidp.optim import ShardSGD
+    tr = jabas_b200.JABASTrainer(0, 8, 2, 0, "overlap", dict(CFG))
+    tr.prepare_stream_parallel(_model(), torch.nn.CrossEntropyLoss().cuda(), bucket_cap_mb=0.05,
+                               first_bucket_bytes=4096)
+    tr.prepare_weight_sync_method(ShardSGD(_groups(tr.main_model), lr=0.1, momentum=0.9), None, _groups)
+    tr.set_model_train()
+    eng = tr.reducer.engine
+    g = torch.Generator().manual_seed(2)
+
+    def one_step(K):
+        before = eng.weights[0].clone()
+        x = torch.randn(8 * K, 3, 16, 16, generator=g).cuda()
+        y = torch.randint(0, 10, (8 * K,), generator=g).cuda()
+        tr.compute((x, y))
+        assert tr.step() is True
+        torch.cuda.synchronize()
+        assert not torch.equal(before, eng.weights[0])
+        for k in range(1, K):
+            assert torch.equal(eng.weights[k], eng.weights[0]), k
+        assert -1.0 <= float(tr.cos_placeholder) <= 1.0
+
+    one_step(2)
+    ptrs = (eng.weights[0].data_ptr(), eng.grads[1].data_ptr(), eng.m.data_ptr())
+    tr.change_num_models(4)
+    torch.cuda.synchronize()
+    assert eng.K == 4 and tr.total_num_decoupled_workers == 4
+    assert (eng.weights[0].data_ptr(), eng.grads[1].data_ptr(), eng.m.data_ptr()) == ptrs
+    assert torch.equal(eng.weights[3], eng.weights[0])
+    one_step(4)
+    tr.change_num_models(2)
+    assert eng.K == 2 and eng.weights[0].data_ptr() == ptrs[0]
+    one_step(2)

@@ -323,3 +323,39 @@ def test_gradient_norm_clipping_sequential_and_overlap():
         assert torch.equal(tr.reducer.engine.weights[K - 1], ref.weights[0]), wsm
         if wsm == "sequential":
             assert abs(float(total) - norm) < 1e-6 * norm
+
+
+def test_runtime_change_of_vsw_count():
+    """K: 2 -> 4 -> 2 between iterations: buffers that stay are not reallocated, the new
+    replicas start from the main weights, T reaches the hook state and the kernels."""
+    tr = _make_trainer(2, "overlap", "sgd")
+    eng = tr.reducer.engine
+    g = torch.Generator().manual_seed(9)
+
+    def one_step(K):
+        ref = _reference_for(tr, "sgd")
+        ref.steps = eng.steps
+        ref.m.copy_(eng.m)
+        x, y = torch.randn(8 * K, 20, generator=g), torch.randint(0, 10, (8 * K,), generator=g)
+        for k, flat in enumerate(_vsw_gradients(tr, x, y)):
+            ref.grads[k].copy_(flat)
+        cos_ref = ref.run_iteration()
+        tr.compute((x, y)); tr.step()
+        for k in range(K):
+            assert torch.equal(eng.weights[k], ref.weights[0]), k
+        assert abs(float(tr.cos_placeholder) - cos_ref) < 1e-5
+
+    one_step(2)
+    ptr_w0, ptr_g1, ptr_m = eng.weights[0].data_ptr(), eng.grads[1].data_ptr(), eng.m.data_ptr()
+    tr.change_num_models(4)
+    assert tr.num_models == 4 and eng.K == 4 and len(tr.local_models) == 4 and len(tr.hooks) == 4
+    assert tr.total_num_decoupled_workers == 4 and tr.similarity_state.total_num_decoupled_workers == 4
+    assert tr.similarity_state.subgroup_total_num_decoupled_workers == 2
+    assert tr.batch_size_per_gpu == 32 and tr.global_batch_size == 32
+    assert (eng.weights[0].data_ptr(), eng.grads[1].data_ptr(), eng.m.data_ptr()) == (ptr_w0, ptr_g1, ptr_m)
+    assert torch.equal(eng.weights[3], eng.weights[0])
+    one_step(4)
+    tr.change_num_models(2)
+    assert eng.K == 2 and len(tr.local_models) == 2 and len(tr.model_streams) == 2
+    assert eng.weights[0].data_ptr() == ptr_w0
+    one_step(2)
