@@ -50,6 +50,8 @@ def parse_args():
     ap.add_argument("--no-overlap", action="store_true")
     ap.add_argument("--per-bucket", default="auto", choices=["auto", "yes", "no"],
                     help="walk the DDP buckets (default when N > 1) or launch over the whole flat model")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch every kernel / collective from Python instead of replaying one CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-steps", type=int, default=None)
@@ -88,6 +90,7 @@ def config_dict(args, layout, K, lbs, opt, desc, world):
         "global_batch": world * K * lbs, "optimizer": opt["kind"], "param_groups": len(opt["groups"]),
         "similarity": "every iteration", "similarity_mode": args.similarity_mode if world > 1 else "vsw_parity",
         "overlap": not args.no_overlap,
+        "cuda_graph": (not args.no_graph) and args.impl == "ours",
         "launch_granularity": "bucket" if (args.per_bucket == "yes" or (args.per_bucket == "auto" and world > 1))
                               else "whole flat model",
         "parallelism": f"dp{world} x vsw{K}",
@@ -286,7 +289,9 @@ def run_ours(args):
         eng.grads[k].normal_(0.0, 1e-3, generator=g)
     overlap = not args.no_overlap
     per_bucket = None if args.per_bucket == "auto" else (args.per_bucket == "yes")
-    step_fn = lambda: eng.run_iteration(overlap=overlap, per_bucket=per_bucket)
+    eager_fn = lambda: eng.run_iteration(overlap=overlap, per_bucket=per_bucket)
+    use_graph = not args.no_graph
+    step_fn = eng.replay if use_graph else eager_fn
 
     def barrier():
         if world > 1:
@@ -301,6 +306,8 @@ def run_ours(args):
         return float(t)
 
     # ---- device-resident timing ---------------------------------------------------
+    if use_graph:
+        eng.capture(overlap=overlap, per_bucket=per_bucket, warmup=2)
     for _ in range(max(args.warmup, 3)):
         step_fn()
     barrier()
@@ -308,7 +315,8 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    eng.profile_events = []
+    if not use_graph:
+        eng.profile_events = []
     launches0 = eng.launches
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -319,6 +327,13 @@ def run_ours(args):
     barrier()
     ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
     launches = eng.launches - launches0
+    if use_graph:
+        # kernels inside a replayed graph cannot be bracketed by events: time them in a second
+        # pass of the same number of steps, launched eagerly, right after the timed region
+        eng.profile_events = []
+        for _ in range(args.steps):
+            eager_fn()
+        barrier()
     events, eng.profile_events = eng.profile_events, None
     clocks = sampler.stop() if rank == 0 else None
     cos = float(eng.cos)

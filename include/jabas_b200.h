@@ -46,6 +46,7 @@ extern "C" {
 
 typedef struct jabas_ctx    jabas_ctx_t;
 typedef struct jabas_layout jabas_layout_t;
+typedef struct jabas_dynhp  jabas_dynhp_t;
 
 /* One run of consecutive elements of a flat parameter buffer that belongs to one
  * optimizer param group: the flat form of the group lists the reference builds at
@@ -73,6 +74,8 @@ typedef struct {
     int    first_step;  /* 1: momentum buffer is created from the gradient (m = d)   */
     const float* grad_scale;  /* DEVICE scalar, nullable: when *grad_scale < 1 the gradient is
                                  multiplied by it before the update (jabas_clip_coef)       */
+    const jabas_dynhp_t* dynamic; /* nullable: the kernel reads lr / weight decay / flags from
+                                 this device-resident block (see jabas_dynhp_create)        */
 } jabas_sgd_hp_t;
 
 typedef struct {
@@ -82,6 +85,7 @@ typedef struct {
     int    decoupled;   /* 1: AdamW (p *= 1 - lr*wd); 0: Adam (g += wd*p)            */
     int    reserved;
     const float* grad_scale;  /* as in jabas_sgd_hp_t */
+    const jabas_dynhp_t* dynamic; /* as in jabas_sgd_hp_t */
 } jabas_adam_hp_t;
 
 JABAS_API int         jabas_version(void);
@@ -97,6 +101,21 @@ JABAS_API int jabas_ctx_destroy(jabas_ctx_t* ctx);
 JABAS_API int jabas_layout_create(jabas_ctx_t* ctx, const jabas_seg_t* segs, int nseg, uint64_t total,
                         jabas_layout_t** layout);
 JABAS_API int jabas_layout_destroy(jabas_layout_t* layout);
+
+/* Device-resident hyper-parameters, for update launches that are captured in a CUDA graph.
+ * A graph bakes kernel arguments in, but the reference changes `lr` every iteration
+ * (jabas/train/trainer.py:693-700) and Adam's step count grows.  An update call whose
+ * hp->dynamic is set makes the kernel read those values from this block instead of from
+ * its arguments.  Before every replay, OUTSIDE the graph, call jabas_dynhp_push_*: it
+ * converts the hyper-parameters exactly as the update call would and enqueues a
+ * 288-byte host-to-device copy on `stream` (from a ring of 8 pinned slots; it waits on the
+ * host only if the copy issued 8 pushes ago has not completed).  create allocates. */
+JABAS_API int jabas_dynhp_create(jabas_ctx_t* ctx, jabas_dynhp_t** out);
+JABAS_API int jabas_dynhp_destroy(jabas_dynhp_t* h);
+JABAS_API int jabas_dynhp_push_sgd(jabas_dynhp_t* h, const jabas_group_t* groups, int ngroups,
+                         const jabas_sgd_hp_t* hp, void* stream);
+JABAS_API int jabas_dynhp_push_adam(jabas_dynhp_t* h, const jabas_group_t* groups, int ngroups,
+                          const jabas_adam_hp_t* hp, void* stream);
 
 /* Local aggregation of the K VSW gradient buckets of one GPU.
  *   sum      = g[0] + g[1] + ... + g[K-1]       (fp32, ascending k: order is fixed)

@@ -262,6 +262,15 @@ struct GroupDev {
     float s2;      // SGD: unused          Adam: sqrt(1 - beta2^t)
 };
 
+// Everything an update kernel needs that may change from one iteration to the next.
+struct UpdHp {
+    GroupDev grp[JABAS_MAX_GROUPS];
+    unsigned int flags;
+    unsigned int wd_mask;     // bit i: group i has weight_decay != 0
+    float c0, c1, c2, c3, c4; // SGD: mu, 1-dampening | Adam: b1, b2, 1-b1, 1-b2, eps
+    float pad;
+};
+
 enum { OPT_SGD = 0, OPT_ADAM = 1 };
 enum { F_NESTEROV = 1, F_FIRST = 2, F_MOMENTUM = 4, F_DECOUPLED = 8 };
 
@@ -282,11 +291,9 @@ struct UpdArgs {
     unsigned long long n, base;
     int nseg;
     int K;
-    unsigned int flags;
-    unsigned int wd_mask;     // bit i: group i has weight_decay != 0
-    float c0, c1, c2, c3, c4; // SGD: mu, 1-dampening | Adam: b1, b2, 1-b1, 1-b2, eps
     float half_divisor;
-    GroupDev grp[JABAS_MAX_GROUPS];
+    const UpdHp* dyn;         // nullable: hyper-parameters live in device memory (CUDA-graph replay)
+    UpdHp hp;                 // ... otherwise they travel in the argument block
 };
 
 // index of the segment that holds element `idx` (segments are contiguous and sorted)
@@ -301,7 +308,7 @@ __device__ __forceinline__ int seg_find(const SegDev* segs, int nseg, unsigned l
 }
 
 template <int OPT>
-__device__ __forceinline__ void upd_math(const UpdArgs& a, const GroupDev& h, bool has_wd, float g,
+__device__ __forceinline__ void upd_math(const UpdHp& a, const GroupDev& h, bool has_wd, float g,
                                          float& p, float& m, float& v)
 {
     if (OPT == OPT_SGD) {
@@ -326,7 +333,7 @@ __device__ __forceinline__ void upd_math(const UpdArgs& a, const GroupDev& h, bo
 }
 
 template <int OPT>
-__device__ __forceinline__ void upd_math4(const UpdArgs& a, const GroupDev& h, bool has_wd, float4 g,
+__device__ __forceinline__ void upd_math4(const UpdHp& a, const GroupDev& h, bool has_wd, float4 g,
                                           float4& p, float4& m, float4& v)
 {
     upd_math<OPT>(a, h, has_wd, g.x, p.x, m.x, v.x);
@@ -347,7 +354,8 @@ __device__ __forceinline__ void half_stat4(const UpdArgs& a, float4 g, float4 hs
 
 // Per-element form (tail, unaligned path, tiles that straddle a segment boundary).
 template <int OPT, bool STAT>
-__device__ __forceinline__ void upd_elem(const UpdArgs& a, unsigned long long i, int seg, Acc3& acc)
+__device__ __forceinline__ void upd_elem(const UpdArgs& a, const UpdHp& H, unsigned long long i, int seg,
+                                         Acc3& acc)
 {
     int gi = 0;
     if (a.segs) {
@@ -376,11 +384,11 @@ __device__ __forceinline__ void upd_elem(const UpdArgs& a, unsigned long long i,
         if (gs < 1.0f) g = __fmul_rn(g, gs);
     }
     float p = a.w[0][i];
-    float m = (OPT == OPT_ADAM || ((a.flags & F_MOMENTUM) && !(a.flags & F_FIRST))) ? a.m[i] : 0.0f;
+    float m = (OPT == OPT_ADAM || ((H.flags & F_MOMENTUM) && !(H.flags & F_FIRST))) ? a.m[i] : 0.0f;
     float v = OPT == OPT_ADAM ? a.v[i] : 0.0f;
-    upd_math<OPT>(a, a.grp[gi], (a.wd_mask >> gi) & 1u, g, p, m, v);
+    upd_math<OPT>(H, H.grp[gi], (H.wd_mask >> gi) & 1u, g, p, m, v);
     for (int k = 0; k < a.K; ++k) a.w[k][i] = p;
-    if (OPT == OPT_ADAM || (a.flags & F_MOMENTUM)) a.m[i] = m;
+    if (OPT == OPT_ADAM || (H.flags & F_MOMENTUM)) a.m[i] = m;
     if (OPT == OPT_ADAM) a.v[i] = v;
     if (STAT) {
         if (a.kagg > 0) {
@@ -390,6 +398,20 @@ __device__ __forceinline__ void upd_elem(const UpdArgs& a, unsigned long long i,
             acc_one(acc, e, __fmaf_rn(2.0f, g_unclipped, -e));
         }
     }
+}
+
+// Hyper-parameters of this launch into shared memory: from the argument block, or from the
+// device-resident block when the launch is part of a replayed CUDA graph.
+__device__ __forceinline__ void load_hp(const UpdArgs& a, UpdHp& H)
+{
+    if (a.dyn) {
+        const unsigned int* src = reinterpret_cast<const unsigned int*>(a.dyn);
+        unsigned int* dst = reinterpret_cast<unsigned int*>(&H);
+        for (unsigned int i = threadIdx.x; i < sizeof(UpdHp) / 4; i += blockDim.x) dst[i] = __ldg(src + i);
+    } else if (threadIdx.x == 0) {
+        H = a.hp;
+    }
+    __syncthreads();
 }
 
 // KAGG = 0: g is read from a.g.  KAGG > 0 (single-GPU form): the KAGG VSW gradients are
@@ -404,8 +426,10 @@ __global__ void __launch_bounds__(kThreads) upd_vec_kernel(const UpdArgs a)
     const bool clip = gscale < 1.0f;
     const unsigned long long nvec = a.n >> 2;
     const unsigned long long tile = (unsigned long long)kThreads * U;
-    const bool use_m = OPT == OPT_ADAM || (a.flags & F_MOMENTUM);
-    const bool load_m = OPT == OPT_ADAM || ((a.flags & F_MOMENTUM) && !(a.flags & F_FIRST));
+    __shared__ UpdHp H;
+    load_hp(a, H);
+    const bool use_m = OPT == OPT_ADAM || (H.flags & F_MOMENTUM);
+    const bool load_m = OPT == OPT_ADAM || ((H.flags & F_MOMENTUM) && !(H.flags & F_FIRST));
     Acc3 acc = {0.0, 0.0, 0.0};
     for (unsigned long long t0 = (unsigned long long)blockIdx.x * tile; t0 < nvec;
          t0 += (unsigned long long)gridDim.x * tile) {
@@ -469,13 +493,13 @@ __global__ void __launch_bounds__(kThreads) upd_vec_kernel(const UpdArgs a)
                 g[u] = make_float4(__fmul_rn(g[u].x, gscale), __fmul_rn(g[u].y, gscale),
                                    __fmul_rn(g[u].z, gscale), __fmul_rn(g[u].w, gscale));
             if (uniform) {
-                upd_math4<OPT>(a, a.grp[gi0], (a.wd_mask >> gi0) & 1u, g[u], p[u], m[u], v[u]);
+                upd_math4<OPT>(H, H.grp[gi0], (H.wd_mask >> gi0) & 1u, g[u], p[u], m[u], v[u]);
             } else {
                 int s = seg0;
                 auto one = [&](int c, float gx, float& px, float& mx, float& vx) {
                     while (__ldg(&a.segs[s].end) <= a.base + 4 * x + c) ++s;
                     const int gi = (int)__ldg(&a.segs[s].group);
-                    upd_math<OPT>(a, a.grp[gi], (a.wd_mask >> gi) & 1u, gx, px, mx, vx);
+                    upd_math<OPT>(H, H.grp[gi], (H.wd_mask >> gi) & 1u, gx, px, mx, vx);
                 };
                 one(0, g[u].x, p[u].x, m[u].x, v[u].x);
                 one(1, g[u].y, p[u].y, m[u].y, v[u].y);
@@ -490,7 +514,7 @@ __global__ void __launch_bounds__(kThreads) upd_vec_kernel(const UpdArgs a)
     const unsigned int rem = (unsigned int)(a.n & 3ull);
     if (blockIdx.x == 0 && threadIdx.x < rem) {
         const unsigned long long i = (nvec << 2) + threadIdx.x;
-        upd_elem<OPT, STAT>(a, i, a.segs ? seg_find(a.segs, a.nseg, a.base + i) : 0, acc);
+        upd_elem<OPT, STAT>(a, H, i, a.segs ? seg_find(a.segs, a.nseg, a.base + i) : 0, acc);
     }
     if (STAT) stat_finish(acc, a.ws, a.stat);
 }
@@ -498,10 +522,12 @@ __global__ void __launch_bounds__(kThreads) upd_vec_kernel(const UpdArgs a)
 template <int OPT, bool STAT>
 __global__ void __launch_bounds__(kThreads) upd_scalar_kernel(const UpdArgs a)
 {
+    __shared__ UpdHp H;
+    load_hp(a, H);
     Acc3 acc = {0.0, 0.0, 0.0};
     for (unsigned long long i = (unsigned long long)blockIdx.x * kThreads + threadIdx.x; i < a.n;
          i += (unsigned long long)gridDim.x * kThreads)
-        upd_elem<OPT, STAT>(a, i, a.segs ? seg_find(a.segs, a.nseg, a.base + i) : 0, acc);
+        upd_elem<OPT, STAT>(a, H, i, a.segs ? seg_find(a.segs, a.nseg, a.base + i) : 0, acc);
     if (STAT) stat_finish(acc, a.ws, a.stat);
 }
 
@@ -634,6 +660,21 @@ struct jabas_layout {
     int nseg = 0;
     unsigned long long total = 0;
     SegDev* dsegs = nullptr;
+};
+
+// Device-resident hyper-parameter block.  A captured CUDA graph bakes kernel arguments in;
+// what changes every iteration (lr, Adam step, first-step flag) therefore lives in device
+// memory and is refreshed by a small stream-ordered copy BEFORE each replay, outside the
+// graph, from a ring of pinned slots (a slot is reused only after its copy has completed).
+struct jabas_dynhp {
+    static constexpr int kSlots = 8;
+    int device = 0;
+    int kind = -1;                  // OPT_SGD / OPT_ADAM once pushed
+    UpdHp* dev = nullptr;
+    UpdHp* pinned = nullptr;        // kSlots entries
+    cudaEvent_t done[kSlots] = {};
+    int next = 0;
+    std::mutex mu;
 };
 
 namespace {
@@ -951,6 +992,42 @@ int jabas_div_f32(jabas_ctx_t* ctx, float* x, uint64_t n, float divisor, void* s
     return JABAS_OK;
 }
 
+// Host -> kernel form of the hyper-parameters: fp64 scalars rounded to fp32 once.
+static int fill_sgd_hp(UpdHp& h, const jabas_group_t* groups, int ngroups, const jabas_sgd_hp_t* hp)
+{
+    std::memset(&h, 0, sizeof(h));
+    h.c0 = (float)hp->momentum;
+    h.c1 = (float)(1.0 - hp->dampening);
+    h.flags = (hp->nesterov ? F_NESTEROV : 0u) | (hp->first_step ? F_FIRST : 0u) |
+              (hp->momentum != 0.0 ? F_MOMENTUM : 0u);
+    for (int i = 0; i < ngroups; ++i) {
+        h.grp[i].wd = (float)groups[i].weight_decay;
+        h.grp[i].s0 = (float)(-groups[i].lr);
+        if (groups[i].weight_decay != 0.0) h.wd_mask |= 1u << i;
+    }
+    return JABAS_OK;
+}
+
+static int fill_adam_hp(UpdHp& h, const jabas_group_t* groups, int ngroups, const jabas_adam_hp_t* hp)
+{
+    std::memset(&h, 0, sizeof(h));
+    h.c0 = (float)hp->beta1; h.c1 = (float)hp->beta2;
+    h.c2 = (float)(1.0 - hp->beta1); h.c3 = (float)(1.0 - hp->beta2);
+    h.c4 = (float)hp->eps;
+    h.flags = hp->decoupled ? F_DECOUPLED : 0u;
+    for (int i = 0; i < ngroups; ++i) {
+        if (groups[i].step < 1) return fail(JABAS_EINVAL, "Adam step must be >= 1");
+        const double bc1 = 1.0 - std::pow(hp->beta1, (double)groups[i].step);
+        const double bc2 = 1.0 - std::pow(hp->beta2, (double)groups[i].step);
+        h.grp[i].wd = (float)groups[i].weight_decay;
+        h.grp[i].s0 = (float)(1.0 - groups[i].lr * groups[i].weight_decay);
+        h.grp[i].s1 = (float)(-(groups[i].lr / bc1));
+        h.grp[i].s2 = (float)std::sqrt(bc2);
+        if (groups[i].weight_decay != 0.0) h.wd_mask |= 1u << i;
+    }
+    return JABAS_OK;
+}
+
 static int sgd_impl(jabas_ctx_t* ctx, const GradSrc& src, float* const* w, int K, float* m,
                     uint64_t n, uint64_t base, const jabas_layout_t* layout,
                     const jabas_group_t* groups, int ngroups, const jabas_sgd_hp_t* hp,
@@ -967,14 +1044,10 @@ static int sgd_impl(jabas_ctx_t* ctx, const GradSrc& src, float* const* w, int K
         return fail(JABAS_EINVAL, "nesterov needs momentum > 0 and dampening == 0");
     if (n == 0) return JABAS_OK;
     a.grad_scale = hp->grad_scale;
-    a.c0 = (float)hp->momentum;
-    a.c1 = (float)(1.0 - hp->dampening);
-    a.flags = (hp->nesterov ? F_NESTEROV : 0u) | (hp->first_step ? F_FIRST : 0u) |
-              (hp->momentum != 0.0 ? F_MOMENTUM : 0u);
-    for (int i = 0; i < ngroups; ++i) {
-        a.grp[i].wd = (float)groups[i].weight_decay;
-        a.grp[i].s0 = (float)(-groups[i].lr);
-        if (groups[i].weight_decay != 0.0) a.wd_mask |= 1u << i;
+    if ((rc = fill_sgd_hp(a.hp, groups, ngroups, hp))) return rc;
+    if (hp->dynamic) {
+        if (hp->dynamic->kind != OPT_SGD) return fail(JABAS_EINVAL, "the dynamic block holds Adam hyper-parameters");
+        a.dyn = hp->dynamic->dev;
     }
     return upd_launch<OPT_SGD>(ctx, a, vec, static_cast<cudaStream_t>(stream));
 }
@@ -1014,19 +1087,10 @@ static int adam_impl(jabas_ctx_t* ctx, const GradSrc& src, float* const* w, int 
     if (!m || !v) return fail(JABAS_EINVAL, "exp_avg and exp_avg_sq buffers are required");
     if (n == 0) return JABAS_OK;
     a.grad_scale = hp->grad_scale;
-    a.c0 = (float)hp->beta1; a.c1 = (float)hp->beta2;
-    a.c2 = (float)(1.0 - hp->beta1); a.c3 = (float)(1.0 - hp->beta2);
-    a.c4 = (float)hp->eps;
-    a.flags = hp->decoupled ? F_DECOUPLED : 0u;
-    for (int i = 0; i < ngroups; ++i) {
-        if (groups[i].step < 1) return fail(JABAS_EINVAL, "Adam step must be >= 1");
-        const double bc1 = 1.0 - std::pow(hp->beta1, (double)groups[i].step);
-        const double bc2 = 1.0 - std::pow(hp->beta2, (double)groups[i].step);
-        a.grp[i].wd = (float)groups[i].weight_decay;
-        a.grp[i].s0 = (float)(1.0 - groups[i].lr * groups[i].weight_decay);
-        a.grp[i].s1 = (float)(-(groups[i].lr / bc1));
-        a.grp[i].s2 = (float)std::sqrt(bc2);
-        if (groups[i].weight_decay != 0.0) a.wd_mask |= 1u << i;
+    if ((rc = fill_adam_hp(a.hp, groups, ngroups, hp))) return rc;
+    if (hp->dynamic) {
+        if (hp->dynamic->kind != OPT_ADAM) return fail(JABAS_EINVAL, "the dynamic block holds SGD hyper-parameters");
+        a.dyn = hp->dynamic->dev;
     }
     return upd_launch<OPT_ADAM>(ctx, a, vec, static_cast<cudaStream_t>(stream));
 }
@@ -1049,6 +1113,78 @@ int jabas_vsw_adam_f32(jabas_ctx_t* ctx, const float* const* grads, int Kg, floa
     if (!grads) return fail(JABAS_EINVAL, "grads is null");
     const GradSrc src = {nullptr, grads, Kg, divisor, grad_out};
     return adam_impl(ctx, src, w, K, m, v, n, base, layout, groups, ngroups, hp, nullptr, half_divisor, stat3, stream);
+}
+
+int jabas_dynhp_create(jabas_ctx_t* ctx, jabas_dynhp_t** out)
+{
+    int rc = ctx_bind(ctx);
+    if (rc) return rc;
+    if (!out) return fail(JABAS_EINVAL, "dynhp out pointer is null");
+    *out = nullptr;
+    jabas_dynhp_t* h = new (std::nothrow) jabas_dynhp_t();
+    if (!h) return fail(JABAS_ENOMEM, "out of host memory");
+    h->device = ctx->device;
+    cudaError_t e = cudaMalloc(&h->dev, sizeof(UpdHp));
+    if (e == cudaSuccess) e = cudaMemset(h->dev, 0, sizeof(UpdHp));
+    if (e == cudaSuccess) e = cudaMallocHost(&h->pinned, sizeof(UpdHp) * jabas_dynhp::kSlots);
+    for (int i = 0; e == cudaSuccess && i < jabas_dynhp::kSlots; ++i)
+        e = cudaEventCreateWithFlags(&h->done[i], cudaEventDisableTiming);
+    if (e != cudaSuccess) {
+        jabas_dynhp_destroy(h);
+        return fail(JABAS_ECUDA, cudaGetErrorString(e));
+    }
+    *out = h;
+    return JABAS_OK;
+}
+
+int jabas_dynhp_destroy(jabas_dynhp_t* h)
+{
+    if (!h) return JABAS_OK;
+    int cur = -1;
+    if (cudaGetDevice(&cur) == cudaSuccess && cur != h->device) cudaSetDevice(h->device);
+    for (int i = 0; i < jabas_dynhp::kSlots; ++i)
+        if (h->done[i]) cudaEventDestroy(h->done[i]);
+    if (h->pinned) cudaFreeHost(h->pinned);
+    if (h->dev) cudaFree(h->dev);
+    delete h;
+    return JABAS_OK;
+}
+
+static int dynhp_push(jabas_dynhp_t* h, const UpdHp& v, int kind, void* stream)
+{
+    std::lock_guard<std::mutex> lk(h->mu);
+    int cur = -1;
+    JB_CUDA(cudaGetDevice(&cur));
+    if (cur != h->device) JB_CUDA(cudaSetDevice(h->device));
+    const int slot = h->next;
+    h->next = (slot + 1) % jabas_dynhp::kSlots;
+    JB_CUDA(cudaEventSynchronize(h->done[slot]));      // the copy that last used this slot is over
+    h->pinned[slot] = v;
+    h->kind = kind;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    JB_CUDA(cudaMemcpyAsync(h->dev, h->pinned + slot, sizeof(UpdHp), cudaMemcpyHostToDevice, st));
+    JB_CUDA(cudaEventRecord(h->done[slot], st));
+    return JABAS_OK;
+}
+
+int jabas_dynhp_push_sgd(jabas_dynhp_t* h, const jabas_group_t* groups, int ngroups,
+                         const jabas_sgd_hp_t* hp, void* stream)
+{
+    if (!h || !groups || !hp) return fail(JABAS_EINVAL, "null argument");
+    if (ngroups < 1 || ngroups > JABAS_MAX_GROUPS) return fail(JABAS_EINVAL, "ngroups must be in [1, JABAS_MAX_GROUPS]");
+    UpdHp v;
+    int rc = fill_sgd_hp(v, groups, ngroups, hp);
+    return rc ? rc : dynhp_push(h, v, OPT_SGD, stream);
+}
+
+int jabas_dynhp_push_adam(jabas_dynhp_t* h, const jabas_group_t* groups, int ngroups,
+                          const jabas_adam_hp_t* hp, void* stream)
+{
+    if (!h || !groups || !hp) return fail(JABAS_EINVAL, "null argument");
+    if (ngroups < 1 || ngroups > JABAS_MAX_GROUPS) return fail(JABAS_EINVAL, "ngroups must be in [1, JABAS_MAX_GROUPS]");
+    UpdHp v;
+    int rc = fill_adam_hp(v, groups, ngroups, hp);
+    return rc ? rc : dynhp_push(h, v, OPT_ADAM, stream);
 }
 
 int jabas_dot_norms_f32(jabas_ctx_t* ctx, const float* a, const float* b, uint64_t n, double* stat3,

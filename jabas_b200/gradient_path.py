@@ -107,6 +107,9 @@ class GradientPath:
         self.clip_stat = torch.zeros(nb + 1, 3, dtype=torch.float64, device=self.device)
         self.clip_coef = torch.ones(nb + 1, 2, **f32)
         self._clip_active: Dict[int, bool] = {}
+        self._dyn = None                             # device-resident hyper-parameters (graph mode)
+        self._graph = None
+        self._graph_stream = None
         if optimizer is not None:
             self.set_optimizer(optimizer)
 
@@ -267,6 +270,8 @@ class GradientPath:
             kw["grad_scale"] = self.clip_coef[nb if b is None else b]
         elif nb in self._clip_active:
             kw["grad_scale"] = self.clip_coef[nb]
+        if self._dyn is not None:
+            kw["dynamic"] = self._dyn
         g = self.main_grad[begin:end]
         ws = [w[begin:end] for w in self.weights]
         o = self.opt
@@ -325,6 +330,8 @@ class GradientPath:
         kw = dict(layout=self.dev_layout, base=begin, grad_out=gs[0] if keep_grad else None)
         if self._sim_step:
             kw.update(half_divisor=self.T / 2, stat=self.stat)
+        if self._dyn is not None:
+            kw["dynamic"] = self._dyn
         o = self.opt
         ev = self._ev_begin()
         if o.kind == "sgd":
@@ -369,6 +376,13 @@ class GradientPath:
         """One pass of the path.  ``per_bucket`` (default: only when there are collectives
         to overlap) walks the DDP buckets as the comm hooks do during backward; otherwise
         the whole flat model goes through each kernel in one launch."""
+        if self._dyn is not None:                      # kernels read the device-resident block
+            self.push_hyperparams()
+        cos = self._iteration_body(similarity_step, overlap, per_bucket, fuse_local)
+        self.end_iteration()
+        return cos
+
+    def _iteration_body(self, similarity_step, overlap, per_bucket, fuse_local):
         self.begin_iteration(similarity_step)
         nb = self.layout.num_buckets
         if per_bucket is None:
@@ -394,9 +408,54 @@ class GradientPath:
                 self.aggregate(b)
                 self.allreduce(b)
             self.update(None)
-        cos = self.finish_similarity()
+        return self.finish_similarity()
+
+    # -- CUDA-graph mode: the whole iteration (kernels and collectives) is one graph launch ----
+    def push_hyperparams(self) -> None:
+        """Refresh the device-resident hyper-parameter block with this iteration's values
+        (lr and weight decay of every group, first-step flag, Adam step)."""
+        o = self.opt
+        if o.kind == "sgd":
+            self._dyn.push_sgd(o.groups, momentum=o.momentum, dampening=o.dampening, nesterov=o.nesterov,
+                               first_step=(self.steps == 0))
+        else:
+            self._dyn.push_adam([dict(gr, step=self.steps + 1) for gr in o.groups], beta1=o.betas[0],
+                                beta2=o.betas[1], eps=o.eps, decoupled=(o.kind == "adamw"))
+
+    def capture(self, similarity_step: Optional[bool] = None, overlap: bool = True,
+                per_bucket: Optional[bool] = None, fuse_local: Optional[bool] = None, warmup: int = 2) -> None:
+        """Capture one iteration into a CUDA graph.  ``warmup`` real iterations run first on
+        the capture stream (they allocate the per-stream reduction workspace and bring up the
+        NCCL communicators, neither of which may happen during capture).  Afterwards call
+        :meth:`replay` once per iteration; what varies between iterations is read by the
+        kernels from a device block that ``replay`` refreshes before the graph launch."""
+        if self.profile_events is not None:
+            raise RuntimeError("per-kernel event timing cannot be captured: unset profile_events")
+        self._dyn = self.ops.DynHp(self.ctx)
+        s = torch.cuda.Stream(self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            for _ in range(max(1, warmup)):
+                self.push_hyperparams()
+                self._iteration_body(similarity_step, overlap, per_bucket, fuse_local)
+                self.end_iteration()
+        s.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = self.launches
+        with torch.cuda.graph(graph, stream=s):
+            self._iteration_body(similarity_step, overlap, per_bucket, fuse_local)
+        self._graph, self._graph_stream = graph, s
+        self.launches_per_replay = self.launches - before
+        self.launches = before
+        torch.cuda.current_stream(self.device).wait_stream(s)
+
+    def replay(self) -> Optional[torch.Tensor]:
+        """One iteration: a 288-byte hyper-parameter copy, then one graph launch."""
+        self.push_hyperparams()
+        self._graph.replay()
+        self.launches += self.launches_per_replay
         self.end_iteration()
-        return cos
+        return self.cos if self._sim_step else None
 
     # -- bookkeeping for roofline reports ----------------------------------------------
     def algorithmic_bytes(self, similarity_step: bool = True) -> Dict[str, int]:

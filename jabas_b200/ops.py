@@ -45,6 +45,10 @@ def _scale_ptr(t: Optional[torch.Tensor], device: torch.device) -> Optional[int]
     return t.data_ptr()
 
 
+def _dyn_ptr(d) -> Optional[int]:
+    return None if d is None else d._h
+
+
 def _ptr_array(ptrs: Sequence[int]):
     return (ctypes.c_void_p * len(ptrs))(*ptrs)
 
@@ -101,6 +105,41 @@ class Layout:
             pass
 
 
+class DynHp:
+    """Device-resident hyper-parameters for update launches captured in a CUDA graph: pass
+    it as ``dynamic=`` when capturing, then call ``push_sgd`` / ``push_adam`` before every
+    replay (outside the graph) with the values of that iteration."""
+
+    def __init__(self, ctx: Context):
+        self.ctx = ctx
+        h = ctypes.c_void_p()
+        _lib.check(ctx._lib.jabas_dynhp_create(ctx._h, ctypes.byref(h)))
+        self._h = h
+
+    def push_sgd(self, groups: Sequence[dict], *, momentum: float = 0.0, dampening: float = 0.0,
+                 nesterov: bool = False, first_step: bool = False, stream=None) -> None:
+        hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), None, None)
+        _lib.check(self.ctx._lib.jabas_dynhp_push_sgd(self._h, _groups_array(groups), len(groups),
+                                                      ctypes.byref(hp), _stream_handle(self.ctx.device, stream)))
+
+    def push_adam(self, groups: Sequence[dict], *, beta1: float, beta2: float, eps: float,
+                  decoupled: bool, stream=None) -> None:
+        hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0, None, None)
+        _lib.check(self.ctx._lib.jabas_dynhp_push_adam(self._h, _groups_array(groups), len(groups),
+                                                       ctypes.byref(hp), _stream_handle(self.ctx.device, stream)))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self.ctx._lib.jabas_dynhp_destroy(self._h)
+            self._h = None
+
+    def __del__(self):  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def _groups_array(groups: Sequence[dict]):
     if not 1 <= len(groups) <= MAX_GROUPS:
         raise JabasError(f"between 1 and {MAX_GROUPS} param groups per launch")
@@ -136,9 +175,9 @@ def sgd_momentum(ctx: Context, g: torch.Tensor, weights: Sequence[torch.Tensor],
                  layout: Optional[Layout] = None, base: int = 0,
                  half: Optional[torch.Tensor] = None, half_divisor: float = 1.0,
                  stat: Optional[torch.Tensor] = None, grad_scale: Optional[torch.Tensor] = None,
-                 stream=None) -> None:
+                 dynamic: Optional["DynHp"] = None, stream=None) -> None:
     """Fused SGD-momentum update of ``weights[0]`` with write-back to every replica."""
-    hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), _scale_ptr(grad_scale, ctx.device))
+    hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic))
     wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
     _lib.check(ctx._lib.jabas_sgd_momentum_f32(
         ctx._h, _dev_f32(g, ctx.device, "g"), wp, len(weights),
@@ -153,9 +192,9 @@ def adam(ctx: Context, g: torch.Tensor, weights: Sequence[torch.Tensor], m: torc
          decoupled: bool, layout: Optional[Layout] = None, base: int = 0,
          half: Optional[torch.Tensor] = None, half_divisor: float = 1.0,
          stat: Optional[torch.Tensor] = None, grad_scale: Optional[torch.Tensor] = None,
-         stream=None) -> None:
+         dynamic: Optional["DynHp"] = None, stream=None) -> None:
     """Fused Adam (``decoupled=False``) / AdamW (``True``) update with write-back."""
-    hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0, _scale_ptr(grad_scale, ctx.device))
+    hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0, _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic))
     wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
     _lib.check(ctx._lib.jabas_adam_f32(
         ctx._h, _dev_f32(g, ctx.device, "g"), wp, len(weights), _dev_f32(m, ctx.device, "m"),
@@ -174,9 +213,9 @@ def vsw_sgd_momentum(ctx: Context, grads: Sequence[torch.Tensor], divisor: float
                      first_step: bool = False, layout: Optional[Layout] = None, base: int = 0,
                      grad_out: Optional[torch.Tensor] = None, half_divisor: float = 1.0,
                      stat: Optional[torch.Tensor] = None, grad_scale: Optional[torch.Tensor] = None,
-                     stream=None) -> None:
+                     dynamic: Optional["DynHp"] = None, stream=None) -> None:
     """Single-GPU path in one launch: aggregate the VSW gradients, update, write back."""
-    hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), _scale_ptr(grad_scale, ctx.device))
+    hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic))
     gp = _ptr_array([_dev_f32(g, ctx.device, "grads[k]") for g in grads])
     wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
     _lib.check(ctx._lib.jabas_vsw_sgd_momentum_f32(
@@ -192,9 +231,9 @@ def vsw_adam(ctx: Context, grads: Sequence[torch.Tensor], divisor: float,
              beta1: float, beta2: float, eps: float, decoupled: bool, layout: Optional[Layout] = None,
              base: int = 0, grad_out: Optional[torch.Tensor] = None, half_divisor: float = 1.0,
              stat: Optional[torch.Tensor] = None, grad_scale: Optional[torch.Tensor] = None,
-             stream=None) -> None:
+             dynamic: Optional["DynHp"] = None, stream=None) -> None:
     """Adam / AdamW counterpart of :func:`vsw_sgd_momentum`."""
-    hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0, _scale_ptr(grad_scale, ctx.device))
+    hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0, _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic))
     gp = _ptr_array([_dev_f32(g, ctx.device, "grads[k]") for g in grads])
     wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
     _lib.check(ctx._lib.jabas_vsw_adam_f32(
@@ -259,5 +298,5 @@ def replicate(ctx: Context, src: torch.Tensor, dsts: Sequence[torch.Tensor], *, 
                                             src.numel(), _stream_handle(ctx.device, stream)))
 
 
-__all__ = ["Context", "Layout", "JabasError", "MAX_VSW", "MAX_GROUPS", "vsw_aggregate", "div_",
+__all__ = ["Context", "Layout", "DynHp", "JabasError", "MAX_VSW", "MAX_GROUPS", "vsw_aggregate", "div_",
            "sgd_momentum", "adam", "vsw_sgd_momentum", "vsw_adam", "MAX_FUSED_VSW", "sumsq", "clip_coef", "dot_norms", "dot_norms_static", "cosine_finalize", "replicate"]

@@ -59,7 +59,7 @@ def _replicate(weights):
 
 def sgd_momentum(ctx, g, weights, m, groups, *, momentum=0.0, dampening=0.0, nesterov=False,
                  first_step=False, layout=None, base=0, half=None, half_divisor=1.0, stat=None, grad_scale=None,
-                 stream=None):
+                 dynamic=None, stream=None):
     if stat is not None:
         O.half_stat(_np(g), _np(half), half_divisor, _np(stat))
     g = _scaled(g, grad_scale)
@@ -71,7 +71,7 @@ def sgd_momentum(ctx, g, weights, m, groups, *, momentum=0.0, dampening=0.0, nes
 
 
 def adam(ctx, g, weights, m, v, groups, *, beta1, beta2, eps, decoupled, layout=None, base=0,
-         half=None, half_divisor=1.0, stat=None, grad_scale=None, stream=None):
+         half=None, half_divisor=1.0, stat=None, grad_scale=None, dynamic=None, stream=None):
     if stat is not None:
         O.half_stat(_np(g), _np(half), half_divisor, _np(stat))
     g = _scaled(g, grad_scale)
