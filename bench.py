@@ -33,6 +33,7 @@ WORKLOADS = {
     # name: (model, K, local batch per VSW, optimizer kind)
     "resnet50": ("resnet50", 4, 64, "sgd"),
     "vit_b_16": ("vit_b_16", 8, 32, "adamw"),
+    "gnmt8": ("gnmt8", 2, 128, "adam"),
 }
 
 
@@ -43,13 +44,13 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="resnet50",
-                    help="resnet50 | vit_b_16 | flat<log2 elements> (e.g. flat27)")
+                    help="resnet50 | vit_b_16 | gnmt8 | flat<log2 elements> (e.g. flat27)")
     ap.add_argument("--vsw", type=int, default=None, help="override K (VSWs per GPU)")
     ap.add_argument("--optimizer", default=None, choices=[None, "sgd", "adam", "adamw"])
     ap.add_argument("--similarity-mode", default="fused", choices=["fused", "pair_exchange"])
     ap.add_argument("--no-overlap", action="store_true")
     ap.add_argument("--per-bucket", default="auto", choices=["auto", "yes", "no"],
-                    help="walk the DDP buckets (default when N > 1) or launch over the whole flat model")
+                    help="yes: walk the DDP buckets as the comm hooks do; no / auto: the whole flat model per launch")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch every kernel / collective from Python instead of replaying one CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
@@ -91,7 +92,7 @@ def config_dict(args, layout, K, lbs, opt, desc, world):
         "similarity": "every iteration", "similarity_mode": args.similarity_mode if world > 1 else "vsw_parity",
         "overlap": not args.no_overlap,
         "cuda_graph": (not args.no_graph) and args.impl == "ours",
-        "launch_granularity": "bucket" if (args.per_bucket == "yes" or (args.per_bucket == "auto" and world > 1))
+        "launch_granularity": "bucket" if args.per_bucket == "yes"
                               else "whole flat model",
         "parallelism": f"dp{world} x vsw{K}",
         "l2": "inputs larger than L2: %.0f MB of gradients, weights and state per GPU vs 126 MB"
@@ -268,6 +269,8 @@ def run_ours(args):
     sub_group = pair_group = None
     if world > 1:
         import datetime
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"       # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
         idx = [[r for r in range(world) if r % 2 == p] for p in (0, 1)]
         groups = [dist.new_group(ix) for ix in idx]
@@ -383,9 +386,7 @@ def run_ours(args):
                "api": "GradientPath.run_iteration over the C ABI; gradients from pinned host memory"}
 
     if rank != 0:
-        if world > 1:
-            dist.barrier()
-            dist.destroy_process_group()
+        _finish(world)
         return
 
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -422,9 +423,22 @@ def run_ours(args):
             "sample": f"{cpu_steps} iterations of this workload at one rank (K={K}) after 2 warm-up, "
                       f"stock torch CPU ops, {threads} threads"}
     print(json.dumps(line), flush=True)
+    _finish(world)
+
+
+def _finish(world):
+    """Leave a multi-rank run: last barrier, then exit without tearing the NCCL communicators
+    down one by one (communicator teardown at interpreter exit was seen to block for minutes
+    after the result line had been printed; the driver reclaims everything at process exit)."""
     if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def measure_allreduce(eng, layout, world, dev):

@@ -234,7 +234,7 @@ class GradientPath:
         if self.world == 1:
             return
         works = []
-        if self._sim_step:
+        if self._sim_step and dist.get_world_size(self.sub_group) > 1:     # a one-rank sub-group owns its sum
             works.append(dist.all_reduce(self._sl(self.half, b), group=self.sub_group, async_op=True))
         works.append(dist.all_reduce(self._sl(self.main_grad, b), group=self.pg, async_op=True))
         self._pending[b] = works
@@ -373,9 +373,10 @@ class GradientPath:
     # -- whole iteration, buckets in ready order (used by the benchmark and by tests) ---
     def run_iteration(self, similarity_step: Optional[bool] = None, overlap: bool = True,
                       per_bucket: Optional[bool] = None, fuse_local: Optional[bool] = None):
-        """One pass of the path.  ``per_bucket`` (default: only when there are collectives
-        to overlap) walks the DDP buckets as the comm hooks do during backward; otherwise
-        the whole flat model goes through each kernel in one launch."""
+        """One pass of the path.  ``per_bucket=True`` walks the DDP buckets as the comm hooks do
+        during backward (update of bucket b overlapping the collectives of bucket b+1); the
+        default sends the whole flat model through each kernel and each collective in one
+        call, which is faster when there is no backward pass to hide behind."""
         if self._dyn is not None:                      # kernels read the device-resident block
             self.push_hyperparams()
         cos = self._iteration_body(similarity_step, overlap, per_bucket, fuse_local)
@@ -386,7 +387,7 @@ class GradientPath:
         self.begin_iteration(similarity_step)
         nb = self.layout.num_buckets
         if per_bucket is None:
-            per_bucket = self.world > 1
+            per_bucket = False
         if fuse_local is None:
             fuse_local = self.can_fuse_local() and not per_bucket
         if fuse_local:

@@ -156,6 +156,8 @@ def model_zoo_shapes(model: str):
     puts every parameter whose name contains "bn" in a weight-decay-free group
     (examples/resnet50/main.py:340-349); ViT puts 1-D tensors and biases there
     (examples/vit/main.py:405-423); GNMT uses one group."""
+    if model == "gnmt8":
+        return _gnmt_shapes(vocab=32000, hidden=1024, layers=8)
     import torch
     with torch.device("meta"):
         if model == "resnet50":
@@ -171,3 +173,35 @@ def model_zoo_shapes(model: str):
     named = list(net.named_parameters())
     return ([n for n, _ in named], [tuple(p.shape) for _, p in named],
             [rule(n, p) for n, p in named])
+
+
+def _gnmt_shapes(vocab: int, hidden: int, layers: int):
+    """Parameter shapes of a GNMT-v2 seq2seq model in ``named_parameters()`` order, as built
+    by examples/gnmt/seq2seq/models/gnmt.py:34 with a shared embedding: a residual LSTM
+    encoder (first layer bidirectional, second layer fed with 2*hidden), the shared
+    embedding, a decoder whose first LSTM drives a normalised Bahdanau attention, further
+    decoder LSTMs fed with [hidden, context], and a biased classifier.  One param group
+    (the reference's GNMT optimizer refuses more, shard_optimizer.py:26-29)."""
+    names, shapes = [], []
+
+    def lstm(prefix, inp, suffixes=("",)):
+        for sfx in suffixes:
+            for nm, shp in (("weight_ih_l0", (4 * hidden, inp)), ("weight_hh_l0", (4 * hidden, hidden)),
+                            ("bias_ih_l0", (4 * hidden,)), ("bias_hh_l0", (4 * hidden,))):
+                names.append(f"{prefix}.{nm}{sfx}")
+                shapes.append(shp)
+
+    lstm("encoder.rnn_layers.0", hidden, ("", "_reverse"))
+    lstm("encoder.rnn_layers.1", 2 * hidden)
+    for i in range(2, layers):
+        lstm(f"encoder.rnn_layers.{i}", hidden)
+    names.append("encoder.embedder.weight"); shapes.append((vocab, hidden))
+    lstm("decoder.att_rnn.rnn", hidden)
+    for nm, shp in (("linear_att", (hidden,)), ("normalize_scalar", (1,)), ("normalize_bias", (hidden,)),
+                    ("linear_q.weight", (hidden, hidden)), ("linear_k.weight", (hidden, hidden))):
+        names.append(f"decoder.att_rnn.attn.{nm}"); shapes.append(shp)
+    for i in range(layers - 1):
+        lstm(f"decoder.rnn_layers.{i}", 2 * hidden)
+    names.append("decoder.classifier.classifier.weight"); shapes.append((vocab, hidden))
+    names.append("decoder.classifier.classifier.bias"); shapes.append((vocab,))
+    return names, shapes, [0] * len(names)

@@ -129,3 +129,50 @@ def test_runtime_change_of_vsw_count_on_gpu():
     tr.change_num_models(2)
     assert eng.K == 2 and eng.weights[0].data_ptr() == ptrs[0]
     one_step(2)
+
+
+def test_resnet50_two_vsws_five_iterations():
+    """The CPU-runnable configuration of the reference (ResNet-50, 2 VSWs, local batch 8,
+    SGD momentum 0.9 lr 0.1 wd 1e-4, 25 MB buckets, 5 iterations, statistic every iteration)
+    on one GPU through the trainer mirror; bit-exact against the reference-path restatement
+    fed with the gradients captured from the run."""
+    import torchvision
+    import jabas_b200
+    from jabas_b200.iidp.optim import ShardSGD
+    from oracle.reference_path import ReferencePath
+    torch.manual_seed(0)
+    model = torchvision.models.resnet50().cuda()
+    K = 2
+    tr = jabas_b200.JABASTrainer(0, 8, K, 0, "overlap", dict(CFG))
+    tr.prepare_stream_parallel(model, torch.nn.CrossEntropyLoss().cuda())
+    lay = tr.reducer.layout
+    assert lay.num_params == 25557032 and lay.bucket_sizes_mib() == [7.82, 30.04, 25.04, 25.32, 9.27]
+
+    def groups(m):
+        named = list(m.named_parameters())
+        return [{"params": [p for n, p in named if "bn" in n], "weight_decay": 0},
+                {"params": [p for n, p in named if "bn" not in n], "weight_decay": 1e-4}]
+    tr.prepare_weight_sync_method(ShardSGD(groups(tr.main_model), 0.1, momentum=0.9, weight_decay=1e-4),
+                                  None, groups)
+    assert len(lay.segments) == 99
+    tr.set_model_train()
+    opt = dict(kind="sgd", groups=[dict(lr=0.1, weight_decay=0.0), dict(lr=0.1, weight_decay=1e-4)], momentum=0.9)
+    ref = ReferencePath(lay, K, opt, total_num_decoupled_workers=K, arith="c")
+    for k in range(K):
+        ref.weights[k].copy_(tr.reducer.engine.weights[k].cpu())
+    captured = _capture_vsw_gradients(tr)
+    for it in range(5):
+        g = torch.Generator().manual_seed(10 * it)
+        x = torch.randn(8 * K, 3, 224, 224, generator=g).cuda()
+        y = torch.randint(0, 1000, (8 * K,), generator=g).cuda()
+        tr.compute((x, y))
+        assert tr.step() is True
+        torch.cuda.synchronize()
+        for (k, b), t in captured.items():
+            ref.grads[k][lay.buckets[b][0]:lay.buckets[b][1]].copy_(t.cpu())
+        captured.clear()
+        cos_ref = ref.run_iteration()
+        assert abs(float(tr.cos_placeholder) - cos_ref) < 1e-5, it
+        for k in range(K):
+            assert torch.equal(tr.reducer.engine.weights[k].cpu(), ref.weights[0]), (it, k)
+        assert torch.isfinite(tr.losses[0]).item()
