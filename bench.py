@@ -40,7 +40,7 @@ WORKLOADS = {
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="resnet50",
@@ -48,6 +48,8 @@ def parse_args():
     ap.add_argument("--vsw", type=int, default=None, help="override K (VSWs per GPU)")
     ap.add_argument("--optimizer", default=None, choices=[None, "sgd", "adam", "adamw"])
     ap.add_argument("--similarity-mode", default="fused", choices=["fused", "pair_exchange"])
+    ap.add_argument("--no-similarity", action="store_true",
+                    help="skip the two-half statistic (forced when T is odd, e.g. one GPU with one VSW)")
     ap.add_argument("--no-overlap", action="store_true")
     ap.add_argument("--per-bucket", default="auto", choices=["auto", "yes", "no"],
                     help="yes: walk the DDP buckets as the comm hooks do; no / auto: the whole flat model per launch")
@@ -118,7 +120,7 @@ class ClockSampler:
             os.close(fd)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
@@ -244,7 +246,7 @@ def run_reference(args):
 def _alg_bytes(layout, K, opt, world):
     n = layout.num_params
     multi = world > 1
-    agg = 4 * n * (K + 1) + (4 * n if multi else 0)
+    agg = (4 * n * (K + 1) if (K > 1 or multi) else 0) + (4 * n if multi else 0)
     per = (K + 4) if opt["kind"] == "sgd" else (K + 6)
     upd = 4 * n * per + (4 * n if multi else 0)
     return {"aggregate": agg, "update": upd, "total": agg + upd}
@@ -280,8 +282,9 @@ def run_ours(args):
     layout, K, lbs, opt, desc = make_workload(args)
     spec = OptimizerSpec(kind=opt["kind"], groups=opt["groups"], momentum=opt.get("momentum", 0.0),
                          betas=opt.get("betas", (0.9, 0.999)), eps=opt.get("eps", 1e-8))
+    similarity = not args.no_similarity and (world * K) % 2 == 0 and (world > 1 or K % 2 == 0)
     eng = GradientPath(layout, K, dev, spec, total_num_decoupled_workers=world * K,
-                       sub_group=sub_group, pair_group=pair_group, similarity=True,
+                       sub_group=sub_group, pair_group=pair_group, similarity=similarity,
                        similarity_mode=args.similarity_mode)
     gen = torch.Generator(device=dev).manual_seed(7)
     eng.weights[0].normal_(generator=gen)
@@ -346,7 +349,7 @@ def run_ours(args):
         d = per_kernel.setdefault(kind, [0.0, 0])
         d[0] += a.elapsed_time(z)
         d[1] += 1
-    alg = eng.algorithmic_bytes(True)
+    alg = eng.algorithmic_bytes(similarity)
 
     # ---- collectives alone (N > 1), outside the timed region ------------------------
     bus = None
@@ -366,13 +369,13 @@ def run_ours(args):
             for k in range(K):
                 eng.grads[k].copy_(host[k], non_blocking=True)
             c = step_fn()
-            cos_host.copy_(c, non_blocking=True)
+            cos_host.copy_(c if c is not None else eng.cos, non_blocking=True)
             torch.cuda.current_stream().synchronize()      # the caller reads the statistic
 
         for _ in range(3):
             e2e_step()
         barrier()
-        n_e2e = max(5, min(args.steps, 20))
+        n_e2e = max(5, min(args.steps, 30))
         a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for _ in range(n_e2e):
@@ -403,7 +406,8 @@ def run_ours(args):
         "metric": "samples/sec", "value": world * K * lbs / (ms_step / 1e3), "unit": "samples/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": config_dict(args, layout, K, lbs, opt, desc, world),
+        "data": "synthetic", "config": dict(config_dict(args, layout, K, lbs, opt, desc, world),
+                                            similarity="every iteration" if similarity else "off"),
         "gradient_path_gbs_per_gpu": alg["total"] / (ms_step / 1e3) / 1e9,
         "gradient_path_frac_of_hbm_peak": alg["total"] / (ms_step / 1e3) / 1e9 / peak,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",

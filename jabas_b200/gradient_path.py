@@ -463,7 +463,8 @@ class GradientPath:
         """Bytes each stage must move per iteration on this GPU (fp32 = 4 B)."""
         n, K = self.layout.num_params, self.K
         multi = self.world > 1
-        agg = 4 * n * (K + 1) + (4 * n if (similarity_step and multi) else 0)
+        # K = 1 with nothing to clone: the division by T folds into the update's read of g
+        agg = (4 * n * (K + 1) if (K > 1 or multi) else 0) + (4 * n if (similarity_step and multi) else 0)
         per_elem = (K + 4) if self.opt.kind == "sgd" else (K + 6)
         if self.opt.kind == "sgd" and self.opt.momentum == 0:
             per_elem = K + 2
