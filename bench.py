@@ -48,6 +48,8 @@ def parse_args():
     ap.add_argument("--vsw", type=int, default=None, help="override K (VSWs per GPU)")
     ap.add_argument("--optimizer", default=None, choices=[None, "sgd", "adam", "adamw"])
     ap.add_argument("--similarity-mode", default="fused", choices=["fused", "pair_exchange"])
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: cross-GPU exchange by this library's kernels over NVLink peer memory, or by NCCL")
     ap.add_argument("--no-similarity", action="store_true",
                     help="skip the two-half statistic (forced when T is odd, e.g. one GPU with one VSW)")
     ap.add_argument("--no-overlap", action="store_true")
@@ -94,6 +96,8 @@ def config_dict(args, layout, K, lbs, opt, desc, world):
         "similarity": "every iteration", "similarity_mode": args.similarity_mode if world > 1 else "vsw_parity",
         "overlap": not args.no_overlap,
         "cuda_graph": (not args.no_graph) and args.impl == "ours",
+        "collective": ("peer-memory kernels over NVLink" if args.collective == "peer" else "NCCL allreduce")
+                      if world > 1 else "none",
         "launch_granularity": "bucket" if args.per_bucket == "yes"
                               else "whole flat model",
         "parallelism": f"dp{world} x vsw{K}",
@@ -285,7 +289,7 @@ def run_ours(args):
     similarity = not args.no_similarity and (world * K) % 2 == 0 and (world > 1 or K % 2 == 0)
     eng = GradientPath(layout, K, dev, spec, total_num_decoupled_workers=world * K,
                        sub_group=sub_group, pair_group=pair_group, similarity=similarity,
-                       similarity_mode=args.similarity_mode)
+                       similarity_mode=args.similarity_mode, collective=args.collective)
     gen = torch.Generator(device=dev).manual_seed(7)
     eng.weights[0].normal_(generator=gen)
     for k in range(1, K):

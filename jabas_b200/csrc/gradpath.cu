@@ -281,6 +281,8 @@ struct UpdArgs {
     float divisor;                      // fused form: T
     int kagg;                           // 0: two-kernel form
     const float* grad_scale;            // nullable device scalar: g *= *grad_scale when it is < 1 (norm clipping)
+    int npeer;                          // > 0: element i of g is read from gk[i / shard_len][i] (peer memory)
+    unsigned long long shard_len;
     float* w[JABAS_MAX_VSW];
     float* m;
     float* v;
@@ -295,6 +297,17 @@ struct UpdArgs {
     const UpdHp* dyn;         // nullable: hyper-parameters live in device memory (CUDA-graph replay)
     UpdHp hp;                 // ... otherwise they travel in the argument block
 };
+
+// Base pointer of the rank that owns element `idx` of the reduced gradient (shards in rank order).
+__device__ __forceinline__ const float* peer_base(const UpdArgs& a, unsigned long long idx)
+{
+    unsigned long long owner = idx / a.shard_len;
+    const float* gp = a.gk[0];
+#pragma unroll
+    for (int r = 1; r < JABAS_MAX_VSW; ++r)
+        if (owner >= (unsigned long long)r && r < a.npeer) gp = a.gk[r];
+    return gp;
+}
 
 // index of the segment that holds element `idx` (segments are contiguous and sorted)
 __device__ __forceinline__ int seg_find(const SegDev* segs, int nseg, unsigned long long idx)
@@ -375,6 +388,8 @@ __device__ __forceinline__ void upd_elem(const UpdArgs& a, const UpdHp& H, unsig
         }
         g = __fdiv_rn(s, a.divisor);
         if (a.gout) a.gout[i] = g;
+    } else if (a.npeer > 0) {
+        g = peer_base(a, a.base + i)[a.base + i];
     } else {
         g = a.g[i];
     }
@@ -443,6 +458,8 @@ __global__ void __launch_bounds__(kThreads) upd_vec_kernel(const UpdArgs a)
                 if (KAGG > 0) {
 #pragma unroll
                     for (int k = 0; k < KX; ++k) xk[u][k] = ld4(a.gk[k] + 4 * x);
+                } else if (a.npeer > 0) {
+                    g[u] = ld4(peer_base(a, a.base + 4 * x) + a.base + 4 * x);
                 } else {
                     g[u] = ld4(a.g + 4 * x);
                 }
@@ -596,6 +613,71 @@ __global__ void clip_coef_kernel(const double* sumsq, float max_norm, float* out
     const float total = (float)sqrt(sumsq[0]);
     out[0] = __fdiv_rn(max_norm, __fadd_rn(total, 1e-6f));
     out[1] = total;
+}
+
+// Reduce-scatter over peer memory: this rank's shard [lo, hi) of the world-averaged gradient,
+// read straight from every rank's locally aggregated buffer over NVLink (plain loads, no
+// collective library).  Per element, in rank order:  g = sum_r fl(S_r / T)  — the reference's
+// div_(T) before the SUM allreduce — and the two halves E = sum over even ranks, O = sum over
+// odd ranks, divided by T/2, feed the cosine sums exactly as the pair exchange of
+// jabas/train/trainer.py:470-483 would.  Callers order this kernel after every rank's
+// aggregation with a collective barrier; nothing here waits on another GPU.
+struct PeerArgs {
+    const float* x[JABAS_MAX_VSW];      // one locally aggregated buffer per rank, rank order
+    float* gout;                        // this rank's reduced-gradient buffer (full-length base)
+    double* stat;
+    StatWs ws;
+    unsigned long long lo, hi;          // element range of this rank's shard, lo % 4 == 0
+    float divisor, half_divisor;
+    int n;
+};
+
+template <int NR, bool STAT>           // NR = 0: runtime rank count
+__global__ void __launch_bounds__(kThreads) peer_reduce_kernel(const PeerArgs a)
+{
+    const int n = NR > 0 ? NR : a.n;
+    const unsigned long long len = a.hi - a.lo, nvec = len >> 2;
+    Acc3 acc = {0.0, 0.0, 0.0};
+    for (unsigned long long v = (unsigned long long)blockIdx.x * kThreads + threadIdx.x; v < nvec;
+         v += (unsigned long long)gridDim.x * kThreads) {
+        const unsigned long long off = a.lo + 4 * v;
+        float4 x[NR > 0 ? NR : 1];
+        float4 g, e, o = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (NR > 0) {
+#pragma unroll
+            for (int r = 0; r < NR; ++r) x[r] = ld4(a.x[r] + off);
+            e = x[0];
+            g = div4(x[0], a.divisor);
+#pragma unroll
+            for (int r = 1; r < NR; ++r) {
+                g = add4(g, div4(x[r], a.divisor));
+                if (r == 1) o = x[1]; else if (r & 1) o = add4(o, x[r]); else e = add4(e, x[r]);
+            }
+        } else {
+            x[0] = ld4(a.x[0] + off);
+            e = x[0];
+            g = div4(x[0], a.divisor);
+            for (int r = 1; r < n; ++r) {
+                const float4 y = ld4(a.x[r] + off);
+                g = add4(g, div4(y, a.divisor));
+                if (r == 1) o = y; else if (r & 1) o = add4(o, y); else e = add4(e, y);
+            }
+        }
+        st4(a.gout + off, g);
+        if (STAT) acc_vec(acc, div4(e, a.half_divisor), div4(o, a.half_divisor));
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (len & 3ull)) {       // ragged end of the last shard
+        const unsigned long long i = a.lo + (nvec << 2) + threadIdx.x;
+        float g = __fdiv_rn(a.x[0][i], a.divisor), e = a.x[0][i], o = 0.0f;
+        for (int r = 1; r < n; ++r) {
+            const float y = a.x[r][i];
+            g = __fadd_rn(g, __fdiv_rn(y, a.divisor));
+            if (r == 1) o = y; else if (r & 1) o = __fadd_rn(o, y); else e = __fadd_rn(e, y);
+        }
+        a.gout[i] = g;
+        if (STAT) acc_one(acc, __fdiv_rn(e, a.half_divisor), __fdiv_rn(o, a.half_divisor));
+    }
+    if (STAT) stat_finish(acc, a.ws, a.stat);
 }
 
 struct RepArgs {
@@ -817,7 +899,7 @@ int upd_prepare(jabas_ctx_t* ctx, UpdArgs& a, bool* vec, const GradSrc& src, flo
     if (!w) return fail(JABAS_EINVAL, "w is null");
     if (K < 1 || K > JABAS_MAX_VSW) return fail(JABAS_EINVAL, "K must be in [1, JABAS_MAX_VSW]");
     const bool fused = src.grads != nullptr;
-    if (!fused && !src.g) return fail(JABAS_EINVAL, "g is null");
+    // (a null g is legal when the gradient comes from peer shards; checked by the callers)
     if (fused) {
         if (src.kg < 1 || src.kg > kMaxFusedVsw)
             return fail(JABAS_EINVAL, "fused aggregate+update supports 1..8 VSW gradients");
@@ -844,7 +926,7 @@ int upd_prepare(jabas_ctx_t* ctx, UpdArgs& a, bool* vec, const GradSrc& src, flo
             *vec = *vec && aligned16(src.grads[k]);
         }
     } else {
-        *vec = *vec && aligned16(src.g);
+        *vec = *vec && (!src.g || aligned16(src.g));
     }
     for (int k = 0; k < K; ++k) {
         if (!w[k]) return fail(JABAS_EINVAL, "w[k] is null");
@@ -992,6 +1074,24 @@ int jabas_div_f32(jabas_ctx_t* ctx, float* x, uint64_t n, float divisor, void* s
     return JABAS_OK;
 }
 
+// Gradient read from the reduced shards that live in the ranks' peer-mapped buffers.
+static int set_peer_src(UpdArgs& a, const jabas_peer_src_t* ps, bool* vec)
+{
+    if (!ps) return JABAS_OK;
+    if (a.kagg > 0) return fail(JABAS_EINVAL, "peer_grad cannot be combined with the fused single-GPU form");
+    if (!ps->bufs || ps->n < 1 || ps->n > JABAS_MAX_VSW) return fail(JABAS_EINVAL, "peer_grad: 1..16 buffers");
+    if (ps->shard_len == 0 || (ps->shard_len & 3ull)) return fail(JABAS_EINVAL, "peer_grad: shard_len must be a positive multiple of 4");
+    a.npeer = ps->n;
+    a.shard_len = ps->shard_len;
+    for (int r = 0; r < ps->n; ++r) {
+        if (!ps->bufs[r]) return fail(JABAS_EINVAL, "peer_grad: null buffer");
+        a.gk[r] = ps->bufs[r];
+        *vec = *vec && aligned16(ps->bufs[r]);
+    }
+    *vec = *vec && ((a.base & 3ull) == 0);
+    return JABAS_OK;
+}
+
 // Host -> kernel form of the hyper-parameters: fp64 scalars rounded to fp32 once.
 static int fill_sgd_hp(UpdHp& h, const jabas_group_t* groups, int ngroups, const jabas_sgd_hp_t* hp)
 {
@@ -1044,6 +1144,7 @@ static int sgd_impl(jabas_ctx_t* ctx, const GradSrc& src, float* const* w, int K
         return fail(JABAS_EINVAL, "nesterov needs momentum > 0 and dampening == 0");
     if (n == 0) return JABAS_OK;
     a.grad_scale = hp->grad_scale;
+    if ((rc = set_peer_src(a, hp->peer_grad, &vec))) return rc;
     if ((rc = fill_sgd_hp(a.hp, groups, ngroups, hp))) return rc;
     if (hp->dynamic) {
         if (hp->dynamic->kind != OPT_SGD) return fail(JABAS_EINVAL, "the dynamic block holds Adam hyper-parameters");
@@ -1058,7 +1159,7 @@ int jabas_sgd_momentum_f32(jabas_ctx_t* ctx, const float* g, float* const* w, in
                            const float* half, float half_divisor, double* stat3, void* stream)
 {
     const GradSrc src = {g, nullptr, 0, 1.0f, nullptr};
-    if (!g) return fail(JABAS_EINVAL, "g is null");
+    if (!g && !(hp && hp->peer_grad)) return fail(JABAS_EINVAL, "g is null");
     return sgd_impl(ctx, src, w, K, m, n, base, layout, groups, ngroups, hp, half, half_divisor, stat3, stream);
 }
 
@@ -1087,6 +1188,7 @@ static int adam_impl(jabas_ctx_t* ctx, const GradSrc& src, float* const* w, int 
     if (!m || !v) return fail(JABAS_EINVAL, "exp_avg and exp_avg_sq buffers are required");
     if (n == 0) return JABAS_OK;
     a.grad_scale = hp->grad_scale;
+    if ((rc = set_peer_src(a, hp->peer_grad, &vec))) return rc;
     if ((rc = fill_adam_hp(a.hp, groups, ngroups, hp))) return rc;
     if (hp->dynamic) {
         if (hp->dynamic->kind != OPT_ADAM) return fail(JABAS_EINVAL, "the dynamic block holds SGD hyper-parameters");
@@ -1101,7 +1203,7 @@ int jabas_adam_f32(jabas_ctx_t* ctx, const float* g, float* const* w, int K, flo
                    const float* half, float half_divisor, double* stat3, void* stream)
 {
     const GradSrc src = {g, nullptr, 0, 1.0f, nullptr};
-    if (!g) return fail(JABAS_EINVAL, "g is null");
+    if (!g && !(hp && hp->peer_grad)) return fail(JABAS_EINVAL, "g is null");
     return adam_impl(ctx, src, w, K, m, v, n, base, layout, groups, ngroups, hp, half, half_divisor, stat3, stream);
 }
 
@@ -1200,6 +1302,48 @@ int jabas_dot_norms_f32(jabas_ctx_t* ctx, const float* a, const float* b, uint64
     int grid = 0;
     if ((rc = grid_for(ctx, dot_norms_kernel<false>, vec ? (n + 3) / 4 : n, vec ? kThreads * 4 : kThreads, &grid))) return rc;
     dot_norms_kernel<false><<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(a, b, n, vec, ws, stat3);
+    JB_CUDA(cudaGetLastError());
+    return JABAS_OK;
+}
+
+int jabas_peer_reduce_f32(jabas_ctx_t* ctx, const float* const* xs, int n, float* g_out, uint64_t lo,
+                          uint64_t hi, float divisor, float half_divisor, double* stat3, void* stream)
+{
+    int rc = ctx_bind(ctx);
+    if (rc) return rc;
+    if (!xs || !g_out) return fail(JABAS_EINVAL, "xs or g_out is null");
+    if (n < 1 || n > JABAS_MAX_VSW) return fail(JABAS_EINVAL, "n must be in [1, 16]");
+    if (hi < lo || (lo & 3ull)) return fail(JABAS_EINVAL, "shard must start on a multiple of 4 elements");
+    if (!(divisor != 0.0f)) return fail(JABAS_EINVAL, "divisor must be non-zero");
+    if (stat3 && (n < 2 || !(half_divisor != 0.0f)))
+        return fail(JABAS_EINVAL, "the two-half statistic needs n >= 2 and a non-zero half_divisor");
+    if (hi == lo) return JABAS_OK;
+    PeerArgs a;
+    std::memset(&a, 0, sizeof(a));
+    if (!aligned16(g_out)) return fail(JABAS_EINVAL, "peer buffers must be 16-byte aligned");
+    for (int r = 0; r < n; ++r) {
+        if (!xs[r] || !aligned16(xs[r])) return fail(JABAS_EINVAL, "peer buffers must be non-null and 16-byte aligned");
+        a.x[r] = xs[r];
+    }
+    a.gout = g_out; a.stat = stat3; a.lo = lo; a.hi = hi; a.divisor = divisor;
+    a.half_divisor = half_divisor; a.n = n;
+    if (stat3 && (rc = ws_for(ctx, stream, &a.ws))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int grid = 0;
+    const unsigned long long nvec = ((hi - lo) >> 2) + 1;
+#define JB_PEER_LAUNCH(NR, ST)                                                                     \
+    do {                                                                                           \
+        if ((rc = grid_for(ctx, peer_reduce_kernel<NR, ST>, nvec, kThreads, &grid))) return rc;     \
+        peer_reduce_kernel<NR, ST><<<grid, kThreads, 0, st>>>(a);                                   \
+    } while (0)
+    if (stat3) {
+        if (n == 2) JB_PEER_LAUNCH(2, true); else if (n == 4) JB_PEER_LAUNCH(4, true);
+        else if (n == 8) JB_PEER_LAUNCH(8, true); else JB_PEER_LAUNCH(0, true);
+    } else {
+        if (n == 2) JB_PEER_LAUNCH(2, false); else if (n == 4) JB_PEER_LAUNCH(4, false);
+        else if (n == 8) JB_PEER_LAUNCH(8, false); else JB_PEER_LAUNCH(0, false);
+    }
+#undef JB_PEER_LAUNCH
     JB_CUDA(cudaGetLastError());
     return JABAS_OK;
 }

@@ -59,7 +59,8 @@ class GradientPath:
     def __init__(self, layout: FlatLayout, num_vsw: int, device, optimizer: Optional[OptimizerSpec] = None, *,
                  total_num_decoupled_workers: int, process_group=None, sub_group=None,
                  pair_group=None, first_subgroup_src_rank: int = 0, second_subgroup_src_rank: int = 1,
-                 similarity: bool = True, similarity_mode: str = "fused", backend=None):
+                 similarity: bool = True, similarity_mode: str = "fused", backend=None,
+                 collective: str = "nccl"):
         if backend is None:
             from . import ops as backend          # the CUDA library; raises without a GPU
         self.ops = backend
@@ -93,7 +94,13 @@ class GradientPath:
         f32 = dict(dtype=torch.float32, device=self.device)
         self.weights = [torch.zeros(n, **f32) for _ in range(self.K)]
         self.grads = [torch.zeros(n, **f32) for _ in range(self.K)]
-        self.half = torch.zeros(n, **f32) if (self.similarity and self.world > 1) else None
+        if collective not in ("nccl", "peer"):
+            raise ValueError("collective must be 'nccl' or 'peer'")
+        self.collective = collective if self.world > 1 else "nccl"
+        self.half = torch.zeros(n, **f32) if (self.similarity and self.world > 1
+                                              and self.collective == "nccl") else None
+        if self.collective == "peer":
+            self._setup_peer_exchange()
         self.stat = torch.zeros(3, dtype=torch.float64, device=self.device)
         self.cos = torch.zeros(1, **f32)
         self.steps = 0                               # completed optimizer steps
@@ -112,6 +119,50 @@ class GradientPath:
         self._graph_stream = None
         if optimizer is not None:
             self.set_optimizer(optimizer)
+
+    def _setup_peer_exchange(self) -> None:
+        """Peer-memory exchange: two symmetric buffers per rank, mapped into every rank's
+        address space over NVLink (torch symmetric memory does the allocation and the handle
+        exchange; the data path is this library's kernels).  ``px`` receives the local sum of
+        the K VSW gradients, ``pg`` this rank's shard of the world-averaged gradient."""
+        import torch.distributed._symmetric_memory as symm_mem
+        n, world = self.layout.total, self.world
+        group = self.pg if self.pg is not None else dist.group.WORLD
+        self.px = symm_mem.empty(n, dtype=torch.float32, device=self.device)
+        self.pgrad = symm_mem.empty(n, dtype=torch.float32, device=self.device)
+        self.px.zero_(); self.pgrad.zero_()
+        self._px_h = symm_mem.rendezvous(self.px, group)
+        self._pg_h = symm_mem.rendezvous(self.pgrad, group)
+        self.px_ptrs = [int(p) for p in self._px_h.buffer_ptrs]
+        self.pg_ptrs = [int(p) for p in self._pg_h.buffer_ptrs]
+        shard = -(-n // world)
+        self.shard_len = -(-shard // 32) * 32                       # 128-byte aligned shards
+        self.shard_lo = min(self.rank * self.shard_len, n)
+        self.shard_hi = min(self.shard_lo + self.shard_len, n)
+        self._peer_grad = self.ops.PeerGrad(self.pg_ptrs, self.shard_len)
+        self._tok = torch.zeros(1, dtype=torch.float32, device=self.device)
+
+    def _peer_iteration(self) -> Optional[torch.Tensor]:
+        """Whole flat model through the peer-memory exchange:
+        aggregate -> barrier -> reduce-scatter kernel over NVLink -> barrier (carrying the
+        3-double statistic) -> update kernel that gathers the gradient shards over NVLink."""
+        sim = self._sim_step
+        ev = self._ev_begin()
+        self.ops.vsw_aggregate(self.ctx, self.grads, self.px, 1.0)                 # undivided local sum
+        self._ev_end("aggregate", None, ev)
+        dist.all_reduce(self._tok, group=self.pg)                                  # every rank's sum is in place
+        ev = self._ev_begin()
+        self.ops.peer_reduce(self.ctx, self.px_ptrs, self.pgrad.data_ptr(), self.shard_lo, self.shard_hi,
+                             float(self.T), half_divisor=self.T / 2, stat=self.stat if sim else None)
+        self._ev_end("peer_reduce", None, ev)
+        dist.all_reduce(self.stat if sim else self._tok, group=self.pg)            # barrier + global sums
+        self.launches += 2
+        self.update(None)
+        if sim:
+            self.ops.cosine_finalize(self.ctx, self.stat, self.cos)                # identical on every rank
+            self.launches += 1
+            return self.cos
+        return None
 
     def set_optimizer(self, optimizer: OptimizerSpec) -> None:
         """Bind the fused update: uploads the param-group segment table of the layout and
@@ -256,8 +307,11 @@ class GradientPath:
         if end == begin:
             return
         kw = dict(layout=self.dev_layout, base=begin)
-        fused_stat = self._sim_step and self.world > 1 and self.similarity_mode == "fused"
-        if fused_stat:
+        peer = self.collective == "peer"
+        fused_stat = self._sim_step and self.world > 1 and self.similarity_mode == "fused" and not peer
+        if peer:
+            pass                                       # the statistic came from the reduce-scatter kernel
+        elif fused_stat:
             kw.update(half=self.half[begin:end], half_divisor=self.T / 2, stat=self.stat)
         elif self._sim_step and self.world > 1:
             for bb in (range(self.layout.num_buckets) if b is None else (b,)):
@@ -273,6 +327,9 @@ class GradientPath:
         if self._dyn is not None:
             kw["dynamic"] = self._dyn
         g = self.main_grad[begin:end]
+        if self.collective == "peer":
+            g, kw["peer_grad"] = None, self._peer_grad
+            kw.pop("half", None); kw.pop("half_divisor", None); kw.pop("stat", None)
         ws = [w[begin:end] for w in self.weights]
         o = self.opt
         ev = self._ev_begin()
@@ -390,6 +447,8 @@ class GradientPath:
             per_bucket = False
         if fuse_local is None:
             fuse_local = self.can_fuse_local() and not per_bucket
+        if self.collective == "peer":
+            return self._peer_iteration()
         if fuse_local:
             self.fused_local_step(None)
         elif not per_bucket:

@@ -49,6 +49,23 @@ def _dyn_ptr(d) -> Optional[int]:
     return None if d is None else d._h
 
 
+class PeerGrad:
+    """The world-averaged gradient as it lies after :func:`peer_reduce`: shard ``r`` of the
+    flat buffer lives in rank ``r``'s buffer ``ptrs[r]`` (device pointers valid on this GPU)."""
+
+    def __init__(self, ptrs: Sequence[int], shard_len: int):
+        self.ptrs, self.shard_len = [int(p) for p in ptrs], int(shard_len)
+        self._arr = (ctypes.c_void_p * len(self.ptrs))(*self.ptrs)
+        self._struct = _lib.PeerSrc(self._arr, len(self.ptrs), 0, self.shard_len)
+
+    def ref(self):
+        return ctypes.pointer(self._struct)
+
+
+def _peer_ref(p: Optional[PeerGrad]):
+    return None if p is None else p.ref()
+
+
 def _ptr_array(ptrs: Sequence[int]):
     return (ctypes.c_void_p * len(ptrs))(*ptrs)
 
@@ -175,13 +192,13 @@ def sgd_momentum(ctx: Context, g: torch.Tensor, weights: Sequence[torch.Tensor],
                  layout: Optional[Layout] = None, base: int = 0,
                  half: Optional[torch.Tensor] = None, half_divisor: float = 1.0,
                  stat: Optional[torch.Tensor] = None, grad_scale: Optional[torch.Tensor] = None,
-                 dynamic: Optional["DynHp"] = None, stream=None) -> None:
+                 dynamic: Optional["DynHp"] = None, peer_grad: Optional[PeerGrad] = None, stream=None) -> None:
     """Fused SGD-momentum update of ``weights[0]`` with write-back to every replica."""
-    hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic))
+    hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic), _peer_ref(peer_grad))
     wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
     _lib.check(ctx._lib.jabas_sgd_momentum_f32(
-        ctx._h, _dev_f32(g, ctx.device, "g"), wp, len(weights),
-        None if m is None else _dev_f32(m, ctx.device, "m"), g.numel(), base,
+        ctx._h, None if g is None else _dev_f32(g, ctx.device, "g"), wp, len(weights),
+        None if m is None else _dev_f32(m, ctx.device, "m"), weights[0].numel(), base,
         None if layout is None else layout._h, _groups_array(groups), len(groups), ctypes.byref(hp),
         None if half is None else _dev_f32(half, ctx.device, "half"), half_divisor,
         _stat_ptr(stat, ctx.device), _stream_handle(ctx.device, stream)))
@@ -192,13 +209,14 @@ def adam(ctx: Context, g: torch.Tensor, weights: Sequence[torch.Tensor], m: torc
          decoupled: bool, layout: Optional[Layout] = None, base: int = 0,
          half: Optional[torch.Tensor] = None, half_divisor: float = 1.0,
          stat: Optional[torch.Tensor] = None, grad_scale: Optional[torch.Tensor] = None,
-         dynamic: Optional["DynHp"] = None, stream=None) -> None:
+         dynamic: Optional["DynHp"] = None, peer_grad: Optional[PeerGrad] = None, stream=None) -> None:
     """Fused Adam (``decoupled=False``) / AdamW (``True``) update with write-back."""
-    hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0, _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic))
+    hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0, _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic), _peer_ref(peer_grad))
     wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
     _lib.check(ctx._lib.jabas_adam_f32(
-        ctx._h, _dev_f32(g, ctx.device, "g"), wp, len(weights), _dev_f32(m, ctx.device, "m"),
-        _dev_f32(v, ctx.device, "v"), g.numel(), base, None if layout is None else layout._h,
+        ctx._h, None if g is None else _dev_f32(g, ctx.device, "g"), wp, len(weights),
+        _dev_f32(m, ctx.device, "m"), _dev_f32(v, ctx.device, "v"), weights[0].numel(), base,
+        None if layout is None else layout._h,
         _groups_array(groups), len(groups), ctypes.byref(hp),
         None if half is None else _dev_f32(half, ctx.device, "half"), half_divisor,
         _stat_ptr(stat, ctx.device), _stream_handle(ctx.device, stream)))
@@ -215,7 +233,7 @@ def vsw_sgd_momentum(ctx: Context, grads: Sequence[torch.Tensor], divisor: float
                      stat: Optional[torch.Tensor] = None, grad_scale: Optional[torch.Tensor] = None,
                      dynamic: Optional["DynHp"] = None, stream=None) -> None:
     """Single-GPU path in one launch: aggregate the VSW gradients, update, write back."""
-    hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic))
+    hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic), None)
     gp = _ptr_array([_dev_f32(g, ctx.device, "grads[k]") for g in grads])
     wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
     _lib.check(ctx._lib.jabas_vsw_sgd_momentum_f32(
@@ -233,7 +251,7 @@ def vsw_adam(ctx: Context, grads: Sequence[torch.Tensor], divisor: float,
              stat: Optional[torch.Tensor] = None, grad_scale: Optional[torch.Tensor] = None,
              dynamic: Optional["DynHp"] = None, stream=None) -> None:
     """Adam / AdamW counterpart of :func:`vsw_sgd_momentum`."""
-    hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0, _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic))
+    hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0, _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic), None)
     gp = _ptr_array([_dev_f32(g, ctx.device, "grads[k]") for g in grads])
     wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
     _lib.check(ctx._lib.jabas_vsw_adam_f32(
@@ -249,6 +267,16 @@ def dot_norms(ctx: Context, a: torch.Tensor, b: torch.Tensor, stat: torch.Tensor
                                             _dev_f32(b, ctx.device, "b"), a.numel(),
                                             _stat_ptr(stat, ctx.device),
                                             _stream_handle(ctx.device, stream)))
+
+
+def peer_reduce(ctx: Context, peer_ptrs: Sequence[int], g_out_ptr: int, lo: int, hi: int, divisor: float, *,
+                half_divisor: float = 1.0, stat: Optional[torch.Tensor] = None, stream=None) -> None:
+    """This rank's shard ``[lo, hi)`` of the world-averaged gradient, read from every rank's
+    locally aggregated buffer over NVLink peer mappings (raw device pointers, rank order)."""
+    arr = _ptr_array([int(p) for p in peer_ptrs])
+    _lib.check(ctx._lib.jabas_peer_reduce_f32(ctx._h, arr, len(peer_ptrs), int(g_out_ptr), lo, hi, divisor,
+                                              half_divisor, _stat_ptr(stat, ctx.device),
+                                              _stream_handle(ctx.device, stream)))
 
 
 def sumsq(ctx: Context, x: torch.Tensor, stat: torch.Tensor, *, stream=None) -> None:
@@ -298,5 +326,5 @@ def replicate(ctx: Context, src: torch.Tensor, dsts: Sequence[torch.Tensor], *, 
                                             src.numel(), _stream_handle(ctx.device, stream)))
 
 
-__all__ = ["Context", "Layout", "DynHp", "JabasError", "MAX_VSW", "MAX_GROUPS", "vsw_aggregate", "div_",
+__all__ = ["Context", "Layout", "DynHp", "PeerGrad", "peer_reduce", "JabasError", "MAX_VSW", "MAX_GROUPS", "vsw_aggregate", "div_",
            "sgd_momentum", "adam", "vsw_sgd_momentum", "vsw_adam", "MAX_FUSED_VSW", "sumsq", "clip_coef", "dot_norms", "dot_norms_static", "cosine_finalize", "replicate"]

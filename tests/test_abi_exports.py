@@ -33,8 +33,8 @@ def test_struct_sizes_match_header():
     from jabas_b200 import _lib
     assert ctypes.sizeof(_lib.Seg) == 24
     assert ctypes.sizeof(_lib.Group) == 32
-    assert ctypes.sizeof(_lib.SgdHp) == 40
-    assert ctypes.sizeof(_lib.AdamHp) == 48
+    assert ctypes.sizeof(_lib.SgdHp) == 48
+    assert ctypes.sizeof(_lib.AdamHp) == 56
 
 
 def test_no_cpu_fallback():

@@ -86,3 +86,95 @@ def test_two_nccl_ranks_match_reference_path(mode, kind, wsm):
         assert w <= 1e-6, (rank, w)
         assert c <= 1e-5, (rank, c)
         assert launches > 0
+
+
+def _engine_rank(rank, world, port, collective, kind, K, q):
+    try:
+        sys.path.insert(0, os.path.dirname(HERE))
+        import datetime
+        import numpy as np
+        import torch.distributed as dist
+        from jabas_b200.gradient_path import GradientPath, OptimizerSpec
+        from jabas_b200.layout import build_layout
+        from oracle.reference_path import ReferencePath
+        torch.cuda.set_device(rank)
+        dist.init_process_group("cpu:gloo,cuda:nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank,
+                                world_size=world, timeout=datetime.timedelta(seconds=120))
+        shapes = [(64, 3, 7, 7), (64,), (64,), (256, 64, 3, 3), (1000, 257), (1000,), (333,)]
+        names = ["c1.w", "bn1.w", "bn1.b", "c2.w", "fc.w", "fc.b", "odd"]
+        layout = build_layout(names, shapes, [1, 0, 0, 1, 1, 1, 0], bucket_cap_mb=0.5, first_bucket_bytes=64 * 1024)
+        if kind == "sgd":
+            opt = dict(kind="sgd", groups=[dict(lr=0.1, weight_decay=0.0), dict(lr=0.1, weight_decay=1e-4)], momentum=0.9)
+        else:
+            opt = dict(kind="adamw", groups=[dict(lr=1e-3, weight_decay=0.0), dict(lr=1e-3, weight_decay=0.05)],
+                       betas=(0.9, 0.999), eps=1e-8)
+        spec = OptimizerSpec(opt["kind"], opt["groups"], momentum=opt.get("momentum", 0.0))
+        idx = [[r for r in range(world) if r % 2 == p] for p in (0, 1)]
+        groups = [dist.new_group(ix) for ix in idx]
+        pair = dist.new_group([idx[0][0], idx[1][0]])
+        T = world * K
+        eng = GradientPath(layout, K, torch.device("cuda", rank), spec, total_num_decoupled_workers=T,
+                           sub_group=groups[rank % 2], pair_group=pair, collective=collective)
+        ref = ReferencePath(layout, K, opt, total_num_decoupled_workers=T, arith="c")
+        rng = np.random.default_rng(5)
+        w0 = rng.standard_normal(layout.total).astype(np.float32)
+        pads = list(zip([0] + [x[1] for x in layout.buckets], [x[0] for x in layout.buckets] + [layout.total]))
+        for b, e in pads:
+            w0[b:e] = 0
+        for k in range(K):
+            eng.weights[k].copy_(torch.from_numpy(w0)); ref.weights[k].copy_(torch.from_numpy(w0))
+        worst_w = worst_c = 0.0
+        graph = collective == "peer"
+        for it in range(4):
+            rg = np.random.default_rng(1000 * rank + it)
+            for k in range(K):
+                g = (rg.standard_normal(layout.total) * 1e-3).astype(np.float32)
+                for b, e in pads:
+                    g[b:e] = 0
+                eng.grads[k].copy_(torch.from_numpy(g)); ref.grads[k].copy_(torch.from_numpy(g))
+            if graph and it == 2:
+                eng.capture(warmup=1)                      # iteration 2 is the warm-up, 3 is replayed
+                cos = float(eng.cos)
+            elif graph and it == 3:
+                cos = float(eng.replay())
+            else:
+                cos = float(eng.run_iteration())
+            torch.cuda.synchronize()
+            cos_ref = ref.run_iteration()
+            wr = ref.weights[0]
+            for k in range(K):
+                w = eng.weights[k].cpu()
+                worst_w = max(worst_w, float(((w - wr).abs() / wr.abs().clamp_min(1e-3)).max()))
+            worst_c = max(worst_c, abs(cos - cos_ref))
+        q.put((rank, worst_w, worst_c, eng.launches))
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
+    except Exception:  # pragma: no cover
+        import traceback
+        q.put((rank, "error", traceback.format_exc(), 0))
+
+
+@pytest.mark.parametrize("collective,kind,K", [("peer", "sgd", 4), ("peer", "adamw", 1), ("nccl", "sgd", 2)])
+def test_engine_exchange_modes_match_reference_path(collective, kind, K):
+    """The gradient path at engine level on every visible pair of GPUs: the peer-memory
+    exchange (reduce-scatter kernel + gathering update kernel, eager and as a replayed CUDA
+    graph) and the NCCL exchange against the reference path over gloo."""
+    world = 2 if torch.cuda.device_count() < 4 else 4
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() + hash((collective, kind, K))) % 400
+    procs = [ctx.Process(target=_engine_rank, args=(r, world, port, collective, kind, K, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, w, c, launches in res:
+        assert w != "error", c
+        assert w <= 1e-6, (rank, w)
+        assert c <= 1e-5, (rank, c)
+        assert launches > 0
