@@ -151,6 +151,18 @@ class GradientPath:
         self.ops.vsw_aggregate(self.ctx, self.grads, self.px, 1.0)                 # undivided local sum
         self._ev_end("aggregate", None, ev)
         dist.all_reduce(self._tok, group=self.pg)                                  # every rank's sum is in place
+        if self.world == 2:
+            # Two GPUs: the update kernel itself reads both ranks' sums (the remote one over
+            # NVLink, hidden under its own HBM traffic), averages, takes the statistic from
+            # the two ranks = the two halves, and updates: no reduce-scatter pass at all.
+            self.fused_local_step(None, sources=self.px_ptrs)
+            dist.all_reduce(self._tok, group=self.pg)      # nobody overwrites its sum while a peer still reads it
+            self.launches += 1
+            if sim:
+                self.ops.cosine_finalize(self.ctx, self.stat, self.cos)            # same bits on both ranks
+                self.launches += 1
+                return self.cos
+            return None
         ev = self._ev_begin()
         self.ops.peer_reduce(self.ctx, self.px_ptrs, self.pgrad.data_ptr(), self.shard_lo, self.shard_hi,
                              float(self.T), half_divisor=self.T / 2, stat=self.stat if sim else None)
@@ -371,7 +383,7 @@ class GradientPath:
         """One GPU and few enough VSWs: aggregation and update can be one kernel."""
         return self.world == 1 and self.K <= getattr(self.ops, "MAX_FUSED_VSW", 0)
 
-    def fused_local_step(self, b: Optional[int] = None, keep_grad: bool = False) -> None:
+    def fused_local_step(self, b: Optional[int] = None, keep_grad: bool = False, sources=None) -> None:
         """Single-GPU path in ONE launch over bucket ``b`` (None: the whole flat model):
         sum the K VSW gradients in registers, divide by T, update, write the new weights to
         all K replicas, accumulate the VSW-parity statistic.  The averaged gradient is only
@@ -382,7 +394,11 @@ class GradientPath:
             begin, end = self.layout.buckets[b]
         if end == begin:
             return
-        gs = [g[begin:end] for g in self.grads]
+        if sources is not None:              # raw device pointers of whole flat buffers (peer mappings)
+            assert b is None and not keep_grad
+            gs = list(sources)
+        else:
+            gs = [g[begin:end] for g in self.grads]
         ws = [w[begin:end] for w in self.weights]
         kw = dict(layout=self.dev_layout, base=begin, grad_out=gs[0] if keep_grad else None)
         if self._sim_step:
@@ -529,7 +545,21 @@ class GradientPath:
             per_elem = K + 2
         upd = 4 * n * per_elem + (4 * n if (similarity_step and multi) else 0)
         fused = 4 * n * (K + per_elem - 1)          # the averaged gradient stays in registers
-        return {"aggregate": agg, "update": upd, "total": agg + upd, "fused_step": fused}
+        out = {"aggregate": agg, "update": upd, "total": agg + upd, "fused_step": fused}
+        if self.collective == "peer":
+            # what the kernels of the peer exchange move through THIS GPU's HBM: the aggregate
+            # writes no copy for the sub-group, the reduce-scatter kernel reads every rank's
+            # shard once (one buffer's worth in total per GPU) and writes its own shard
+            out["aggregate"] = 4 * n * (K + 1)
+            out["peer_reduce"] = 4 * n + 4 * n // self.world
+            out["update"] = 4 * n * per_elem
+            out["nvlink_in"] = 2 * 4 * n * (self.world - 1) // self.world
+            if self.world == 2:
+                # direct form: this GPU's sum is read once by its own update kernel and once by
+                # the peer's; the remote sum arrives over NVLink (4n bytes in)
+                out["fused_step"] = 4 * n * (per_elem + 1)
+                out["nvlink_in"] = 4 * n
+        return out
 
     def close(self) -> None:
         if self.dev_layout is not None:

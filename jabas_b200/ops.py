@@ -20,7 +20,11 @@ def _stream_handle(device: torch.device, stream: Optional[torch.cuda.Stream]) ->
     return s.cuda_stream
 
 
-def _dev_f32(t: torch.Tensor, device: torch.device, name: str) -> int:
+def _dev_f32(t, device: torch.device, name: str) -> int:
+    if isinstance(t, int):            # a raw device pointer (e.g. a peer mapping of another rank's buffer)
+        if t == 0:
+            raise JabasError(f"{name} is a null pointer")
+        return t
     if not t.is_cuda or t.device != device:
         raise JabasError(f"{name} must live on {device} (got {t.device}); there is no CPU path")
     if t.dtype != torch.float32 or not t.is_contiguous():
