@@ -99,6 +99,8 @@ class GradientPath:
         self.collective = collective if self.world > 1 else "nccl"
         self.half = torch.zeros(n, **f32) if (self.similarity and self.world > 1
                                               and self.collective == "nccl") else None
+        #: two ranks: the update kernel reads both sums itself; more ranks: reduce-scatter kernel first
+        self.peer_direct = self.world == 2
         if self.collective == "peer":
             self._setup_peer_exchange()
         self.stat = torch.zeros(3, dtype=torch.float64, device=self.device)
@@ -151,7 +153,7 @@ class GradientPath:
         self.ops.vsw_aggregate(self.ctx, self.grads, self.px, 1.0)                 # undivided local sum
         self._ev_end("aggregate", None, ev)
         dist.all_reduce(self._tok, group=self.pg)                                  # every rank's sum is in place
-        if self.world == 2:
+        if self.peer_direct and self.world <= getattr(self.ops, "MAX_FUSED_VSW", 0):
             # Two GPUs: the update kernel itself reads both ranks' sums (the remote one over
             # NVLink, hidden under its own HBM traffic), averages, takes the statistic from
             # the two ranks = the two halves, and updates: no reduce-scatter pass at all.
@@ -554,7 +556,7 @@ class GradientPath:
             out["peer_reduce"] = 4 * n + 4 * n // self.world
             out["update"] = 4 * n * per_elem
             out["nvlink_in"] = 2 * 4 * n * (self.world - 1) // self.world
-            if self.world == 2:
+            if self.peer_direct:
                 # direct form: this GPU's sum is read once by its own update kernel and once by
                 # the peer's; the remote sum arrives over NVLink (4n bytes in)
                 out["fused_step"] = 4 * n * (per_elem + 1)

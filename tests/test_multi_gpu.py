@@ -88,7 +88,7 @@ def test_two_nccl_ranks_match_reference_path(mode, kind, wsm):
         assert launches > 0
 
 
-def _engine_rank(rank, world, port, collective, kind, K, q):
+def _engine_rank(rank, world, port, collective, kind, K, q, direct=None):
     try:
         sys.path.insert(0, os.path.dirname(HERE))
         import datetime
@@ -115,6 +115,8 @@ def _engine_rank(rank, world, port, collective, kind, K, q):
         T = world * K
         eng = GradientPath(layout, K, torch.device("cuda", rank), spec, total_num_decoupled_workers=T,
                            sub_group=groups[rank % 2], pair_group=pair, collective=collective)
+        if direct is not None:
+            eng.peer_direct = direct
         ref = ReferencePath(layout, K, opt, total_num_decoupled_workers=T, arith="c")
         rng = np.random.default_rng(5)
         w0 = rng.standard_normal(layout.total).astype(np.float32)
@@ -155,11 +157,13 @@ def _engine_rank(rank, world, port, collective, kind, K, q):
         q.put((rank, "error", traceback.format_exc(), 0))
 
 
-@pytest.mark.parametrize("collective,kind,K", [("peer", "sgd", 4), ("peer", "adamw", 1), ("nccl", "sgd", 2)])
-def test_engine_exchange_modes_match_reference_path(collective, kind, K):
-    """The gradient path at engine level on every visible pair of GPUs: the peer-memory
-    exchange (reduce-scatter kernel + gathering update kernel, eager and as a replayed CUDA
-    graph) and the NCCL exchange against the reference path over gloo."""
+@pytest.mark.parametrize("collective,kind,K,direct", [("peer", "sgd", 4, None), ("peer", "adamw", 1, False),
+                                                      ("peer", "sgd", 2, False), ("nccl", "sgd", 2, None)])
+def test_engine_exchange_modes_match_reference_path(collective, kind, K, direct):
+    """The gradient path at engine level on 2 (or, when visible, 4) GPUs: the peer-memory
+    exchange in both forms (``direct``: the update kernel reads both ranks' sums; otherwise
+    reduce-scatter kernel + gathering update kernel), eager and as a replayed CUDA graph, and
+    the NCCL exchange, against the reference path over gloo."""
     world = 2 if torch.cuda.device_count() < 4 else 4
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -167,7 +171,8 @@ def test_engine_exchange_modes_match_reference_path(collective, kind, K):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = 29500 + (os.getpid() + hash((collective, kind, K))) % 400
-    procs = [ctx.Process(target=_engine_rank, args=(r, world, port, collective, kind, K, q)) for r in range(world)]
+    procs = [ctx.Process(target=_engine_rank, args=(r, world, port, collective, kind, K, q, direct))
+             for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=300) for _ in procs]
