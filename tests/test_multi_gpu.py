@@ -130,7 +130,11 @@ def _engine_rank(rank, world, port, collective, kind, K, q, direct=None):
         for it in range(4):
             rg = np.random.default_rng(1000 * rank + it)
             for k in range(K):
-                g = (rg.standard_normal(layout.total) * 1e-3).astype(np.float32)
+                # mean-shifted so that the sum over ranks never cancels to ~0: with more than two
+                # ranks the summation order of an allreduce is not fixed, and Adam's
+                # g / (|g| + eps) turns an order-dependent last bit of a near-zero gradient into
+                # a visible weight difference (in the reference just as here)
+                g = ((rg.standard_normal(layout.total) + 3.0) * 1e-3).astype(np.float32)
                 for b, e in pads:
                     g[b:e] = 0
                 eng.grads[k].copy_(torch.from_numpy(g)); ref.grads[k].copy_(torch.from_numpy(g))
