@@ -422,6 +422,14 @@ def run_ours(args):
     }
     if bus is not None:
         line["allreduce"] = bus
+    if world > 1 and eng.collective == "peer":
+        kms = sum(v[0] for k, v in per_kernel.items() if k in ("peer_reduce", "update", "fused_step")) / args.steps
+        line["exchange"] = {
+            "kind": "peer-memory kernels (plain NVLink loads inside the reduce-scatter and update kernels)",
+            "form": "direct (2 ranks)" if eng.peer_direct else "reduce-scatter + gathering update",
+            "nvlink_in_bytes_per_step": alg["nvlink_in"], "kernels_ms_per_step": kms,
+            "nvlink_in_gbs_while_kernels_run": alg["nvlink_in"] / (kms / 1e3) / 1e9,
+            "nccl_barriers_per_step": 2, "bus_peak_gbs": 900.0}
     if not args.no_cpu_baseline and world == 1:      # the CPU baseline is reported at N = 1 only
         cpu_steps = args.cpu_steps or 10
         dt, cores, threads = run_cpu_path(layout, K, opt, 1, cpu_steps, 2)
