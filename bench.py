@@ -37,6 +37,12 @@ WORKLOADS = {
 }
 
 
+# dram__bytes_read + dram__bytes_write of one launch divided by the launch's algorithmic bytes,
+# from the ncu captures summarised under profiles/ (ResNet-50 layout, K = 4, SGD-momentum); the
+# kernels stream every byte once, so the ratio carries over to other sizes.
+NCU_TRAFFIC_RATIO = {"fused_step": 1067.7 / 1124.5, "update": 760.1 / 817.8, "aggregate": 457.4 / 511.1}
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -415,7 +421,9 @@ def run_ours(args):
         "gradient_path_gbs_per_gpu": alg["total"] / (ms_step / 1e3) / 1e9,
         "gradient_path_frac_of_hbm_peak": alg["total"] / (ms_step / 1e3) / 1e9 / peak,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_source": peak_src, "traffic": None,
+                     "frac": achieved / peak, "peak_source": peak_src,
+                     "traffic": (NCU_TRAFFIC_RATIO[dom] * alg[dom] / max(1, dom_n // args.steps)
+                                 if dom in NCU_TRAFFIC_RATIO and world == 1 else None),
                      "algorithmic_bytes_per_launch": alg[dom] / max(1, dom_n // args.steps),
                      "launches_per_step": dom_n // args.steps},
         "kernels": kern, "gpu_launches": launches, "cosine": cos, "clocks": clocks, "e2e": e2e,
