@@ -116,6 +116,10 @@ class GradientPath:
         self.clip_stat = torch.zeros(nb + 1, 3, dtype=torch.float64, device=self.device)
         self.clip_coef = torch.ones(nb + 1, 2, **f32)
         self._clip_active: Dict[int, bool] = {}
+        #: one GPU: hooks may leave a bucket's aggregation to the update, which then runs as ONE
+        #: kernel (aggregate + update + write-back + statistic); set by the trainer
+        self.defer_local = False
+        self._deferred = set()
         self._dyn = None                             # device-resident hyper-parameters (graph mode)
         self._graph = None
         self._graph_stream = None
@@ -255,6 +259,7 @@ class GradientPath:
     def begin_iteration(self, similarity_step: Optional[bool] = None) -> None:
         self._sim_step = self.similarity if similarity_step is None else (similarity_step and self.similarity)
         self._pending.clear()
+        self._deferred.clear()
         self._clip_active.clear()
         self.half_divided = set()
         if self._sim_step:
@@ -359,6 +364,40 @@ class GradientPath:
         self._ev_end("update", b, ev)
         self.launches += 1
 
+    def defer(self, b: int, similarity: bool) -> None:
+        """A comm hook hands bucket ``b`` over without aggregating it (see ``defer_local``)."""
+        if similarity and not self._sim_step:
+            self._sim_step = True
+            self.stat.zero_()
+        self._deferred.add(b)
+
+    def materialize(self, b: Optional[int] = None) -> None:
+        """Run the aggregation of deferred buckets after all (someone needs the averaged
+        gradient itself, e.g. norm clipping)."""
+        for bb in sorted(self._deferred if b is None else ({b} & self._deferred)):
+            self._deferred.discard(bb)
+            self.aggregate(bb, divide=True, similarity=self._sim_step)
+
+    def step_buckets(self, buckets=None) -> None:
+        """Optimizer update of the given buckets (None: the whole model), as one fused
+        aggregate+update kernel where the aggregation was deferred."""
+        nb = self.layout.num_buckets
+        if buckets is None:
+            if len(self._deferred) == nb:
+                self._deferred.clear()
+                self.fused_local_step(None)
+                return
+            if not self._deferred:
+                self.update(None)
+                return
+            buckets = range(nb)
+        for b in buckets:
+            if b in self._deferred:
+                self._deferred.discard(b)
+                self.fused_local_step(b)
+            else:
+                self.update(b)
+
     def clip_grad_norm(self, b: Optional[int], max_norm: float) -> torch.Tensor:
         """L2-norm clipping of the averaged gradient of bucket ``b`` (None: the whole model),
         as ``clip_grad_norm_for_overlap`` / ``clip_grad_norm_`` do in the reference
@@ -368,6 +407,7 @@ class GradientPath:
         gradient by it in registers when it is < 1.  Returns the norm (device scalar)."""
         nb = self.layout.num_buckets
         slot = nb if b is None else b
+        self.materialize(b)
         if b is None:
             for bb in list(self._pending):
                 self.wait_allreduce(bb)

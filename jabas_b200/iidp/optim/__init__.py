@@ -102,10 +102,9 @@ class FusedBinding:
             if getattr(self, "model_clip", None) is not None:
                 self.engine.clip_grad_norm(None, self.model_clip)
                 self.model_clip = None
-            self.engine.update(None)
+            self.engine.step_buckets(None)
         else:
-            for b in buckets:
-                self.engine.update(b)
+            self.engine.step_buckets(buckets)
 
     def clip(self, buckets: Optional[Iterable[int]], max_norm: float):
         """Norm clipping of the given buckets' gradients (None: one norm over the model)."""

@@ -143,6 +143,8 @@ class IIDPTrainer(object):
         self.param_groups_func = param_groups_func
         self.main_optimizer = optimizer
         self.binding = FusedBinding(optimizer, self.reducer.engine, self.main_model._params)
+        # one GPU: let the update kernel aggregate the VSW gradients itself (one launch per bucket)
+        self.reducer.engine.defer_local = self.reducer.engine.can_fuse_local()
         if hasattr(optimizer, "bind"):
             optimizer.bind(self.binding)
         self.local_optimizers = [optimizer] + [_ReplicaOptimizer(optimizer, self.reducer, k)

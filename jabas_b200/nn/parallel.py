@@ -72,6 +72,11 @@ class VSWGradBucket:
             return
         eng = self.engine
         eng.set_total_workers(total_num_decoupled_workers)
+        if eng.defer_local and not self._summed:
+            with self._scope():
+                eng.defer(self._index, similarity=False)
+            self._averaged = True
+            return
         with self._scope():
             if self._summed:
                 eng.ops.div_(eng.ctx, self.buffer(materialize=False), float(total_num_decoupled_workers))
@@ -88,6 +93,11 @@ class VSWGradBucket:
         eng.set_total_workers(total_num_decoupled_workers)
         if self._summed or self._averaged:
             raise RuntimeError("the bucket was already aggregated by an earlier hook")
+        if eng.defer_local:
+            with self._scope():
+                eng.defer(self._index, similarity=True)
+            self._averaged = True
+            return eng.stat
         with self._scope():
             eng.aggregate(self._index, divide=True, similarity=True)
         self._averaged = True
