@@ -119,6 +119,42 @@ class FusedBinding:
             for p in self.params:
                 self.optimizer.state[p]["step"] = torch.tensor(float(self.engine.steps))
 
+    def load_state_dict(self, sd: dict, sync_step: Optional[int] = None) -> None:
+        """Load a ``torch.optim.Optimizer.state_dict()`` (per-parameter ``momentum_buffer`` /
+        ``exp_avg`` / ``exp_avg_sq`` / ``step``, as the reference checkpoints hold it,
+        jabas/train/trainer.py:764,783) into the flat state buffers, and the groups'
+        hyper-parameters into ``param_groups``."""
+        eng, lay = self.engine, self.engine.layout
+        id_map = {}
+        for sg, cg in zip(sd["param_groups"], self.optimizer.param_groups):
+            if len(sg["params"]) != len(cg["params"]):
+                raise ValueError("the checkpoint's param groups do not match this optimizer")
+            for pid, p in zip(sg["params"], cg["params"]):
+                id_map[pid] = p
+            for k, v in sg.items():
+                if k != "params":
+                    cg[k] = v
+        adam_step, has_state = None, False
+        with torch.no_grad():
+            for pid, st in sd["state"].items():
+                slot = lay.slots[id_map[pid].index]
+                sl = slice(slot.offset, slot.offset + slot.numel)
+                if st.get("momentum_buffer") is not None:
+                    eng.m[sl].copy_(st["momentum_buffer"].reshape(-1))
+                    has_state = True
+                if "exp_avg" in st:
+                    eng.m[sl].copy_(st["exp_avg"].reshape(-1))
+                    eng.v[sl].copy_(st["exp_avg_sq"].reshape(-1))
+                    adam_step = int(st["step"])
+        if self.kind == "sgd":
+            eng.steps = int(sync_step) if sync_step is not None else (1 if has_state else 0)
+            if not has_state:
+                eng.steps = 0                      # the momentum buffers are created by the next step
+        else:
+            eng.steps = adam_step or 0
+        self._install_state_views()
+        self.sync_hyperparams()
+
     def buckets_of(self, gradients: Sequence[torch.Tensor]) -> List[int]:
         """Buckets covered by a list of gradient tensors carrying ``.index``."""
         lay = self.engine.layout

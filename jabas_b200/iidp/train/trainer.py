@@ -345,6 +345,60 @@ class IIDPTrainer(object):
             yield self.epoch
             self.epoch += 1
 
+    # -- checkpoints (keys of jabas/train/trainer.py:747-799) -----------------------------------
+    CHECKPOINT_FILE_NAME = "checkpoint.pth"
+
+    def _state_dict_for_ckpt_based_restart(self):
+        sched = self.main_scheduler.state_dict() if self.main_scheduler is not None else None
+        sd = {"epoch": self.epoch, "total_epoch_time": self.total_epoch_time, "step": self.sync_step,
+              "model": self.main_model.module.state_dict(), "optimizer": self.main_optimizer.state_dict(),
+              "scheduler": sched}
+        loader = getattr(self, "data_loader", None)
+        if loader is not None and hasattr(loader, "state_dict"):
+            sd["data"] = loader.state_dict()
+        return sd
+
+    def _load_state_dict_for_ckpt_based_restart(self, state_dict):
+        if self._cuda:
+            torch.cuda.current_stream(self.device).synchronize()
+        for local_model in self.local_models:              # in place: the parameters stay views of the flat buffers
+            local_model.module.load_state_dict(state_dict["model"])
+        self.binding.load_state_dict(state_dict["optimizer"], sync_step=state_dict.get("step"))
+        if self.main_scheduler is not None and state_dict.get("scheduler") is not None:
+            self.main_scheduler.load_state_dict(state_dict["scheduler"])
+        loader = getattr(self, "data_loader", None)
+        if loader is not None and "data" in state_dict and hasattr(loader, "load_state_dict"):
+            loader.load_state_dict(state_dict["data"])
+        self.epoch = state_dict["epoch"]
+        self.total_epoch_time = state_dict["total_epoch_time"]
+        self.sync_step = state_dict["step"]
+
+    def _checkpoint_file(self, checkpoint_path, create=False):
+        import os
+        if os.path.isdir(checkpoint_path) or not os.path.splitext(checkpoint_path)[1]:
+            if create:
+                os.makedirs(checkpoint_path, exist_ok=True)
+            return os.path.join(checkpoint_path, self.CHECKPOINT_FILE_NAME)
+        return checkpoint_path
+
+    def save(self, checkpoint_path):
+        sd = self._state_dict_for_ckpt_based_restart()
+        sd["global_batch_size"], sd["local_batch_size"] = self.global_batch_size, self.local_batch_size
+        path = self._checkpoint_file(checkpoint_path, create=True)
+        torch.save(sd, path)
+        return path
+
+    def load(self, checkpoint_path, restrict_saved_config=False):
+        import os
+        if not os.path.exists(checkpoint_path):
+            raise FileExistsError(f"Checkpoint path: {checkpoint_path} does not exist")
+        sd = torch.load(self._checkpoint_file(checkpoint_path), map_location=self.device, weights_only=False)
+        self._load_state_dict_for_ckpt_based_restart(sd)
+        if restrict_saved_config:
+            assert self.global_batch_size == sd["global_batch_size"], \
+                f"self.global_batch_size: {self.global_batch_size} | state_dict['global_batch_size']: {sd['global_batch_size']}"
+            assert self.local_batch_size == sd["local_batch_size"]
+
     # -- profiling entry points (examples/resnet50/profiler/comp/comp_profiler.py:61-62) ------
     def profile_parallel_compute(self, scatter_inputs, scatter_targets):
         """(forward+backward ms, 0.0): the two phases are not separated here."""

@@ -222,6 +222,23 @@ class JABASTrainer(IIDPTrainer):
             self.last_decision = ("keep", self.global_batch_size)
         self.global_batch_size_trajectory.append([self.similarity_state.step, self.global_batch_size])
 
+    def _state_dict_for_ckpt_based_restart(self):                  # jabas/train/trainer.py:747-776
+        sd = super()._state_dict_for_ckpt_based_restart()
+        sd["total_epoch_cost"] = getattr(self, "total_epoch_cost", 0)
+        sd["gbs_trajectory"] = self.global_batch_size_trajectory
+        if self.config_params["metric"] == "similarity":
+            sd["similarity_step"] = self.similarity_state.step
+            sd["global_lr_modifier"] = self.config_params["global_lr_modifier"]
+        return sd
+
+    def _load_state_dict_for_ckpt_based_restart(self, state_dict):  # jabas/train/trainer.py:778-799
+        super()._load_state_dict_for_ckpt_based_restart(state_dict)
+        self.total_epoch_cost = state_dict.get("total_epoch_cost", 0)
+        self.global_batch_size_trajectory = state_dict.get("gbs_trajectory", [])
+        if self.config_params["metric"] == "similarity" and "similarity_step" in state_dict:
+            self.similarity_state.step = state_dict["similarity_step"]
+            self.config_params["global_lr_modifier"] = state_dict["global_lr_modifier"]
+
     def _scale_lr(self, new_global_batch_size):                    # square-root scaling, :676-691
         initial = max(self.config_params["original_batch_size"], self.config_params["batch_size_lower_bound"])
         self.config_params["global_lr_modifier"] = math.sqrt(new_global_batch_size / initial)

@@ -359,3 +359,38 @@ def test_runtime_change_of_vsw_count():
     assert eng.K == 2 and len(tr.local_models) == 2 and len(tr.model_streams) == 2
     assert eng.weights[0].data_ptr() == ptr_w0
     one_step(2)
+
+
+@pytest.mark.parametrize("kind", ["sgd", "adamw"])
+def test_checkpoint_round_trip(kind, tmp_path):
+    """save -> new trainer -> load -> both take the same next step (weights, optimizer state,
+    step counters, similarity step); the keys are those of the reference's checkpoints."""
+    a = _make_trainer(2, "sequential", kind)
+    g = torch.Generator().manual_seed(21)
+    batches = [(torch.randn(16, 20, generator=g), torch.randint(0, 10, (16,), generator=g)) for _ in range(3)]
+    for x, y in batches[:2]:
+        a.compute((x, y)); a.step()
+    path = a.save(str(tmp_path))
+    sd = torch.load(path, weights_only=False)
+    for key in ("epoch", "total_epoch_time", "step", "model", "optimizer", "scheduler", "gbs_trajectory",
+                "similarity_step", "global_lr_modifier", "global_batch_size", "local_batch_size"):
+        assert key in sd, key
+    assert len(sd["optimizer"]["state"]) == len(list(a.main_model.parameters()))
+    b = _make_trainer(2, "sequential", kind)
+    b.load(str(tmp_path), restrict_saved_config=True)
+    assert b.sync_step == 2 and b.similarity_state.step == a.similarity_state.step
+    assert b.reducer.engine.steps == a.reducer.engine.steps
+    for k in range(2):
+        assert torch.equal(b.reducer.engine.weights[k], a.reducer.engine.weights[0])
+    assert torch.equal(b.reducer.engine.m, a.reducer.engine.m)
+    x, y = batches[2]
+    a.compute((x, y)); a.step()
+    b.compute((x, y)); b.step()
+    assert torch.equal(b.reducer.engine.weights[1], a.reducer.engine.weights[0])
+    # a stock torch optimizer can read the same optimizer state (it is per parameter)
+    params = [torch.nn.Parameter(p.detach().clone()) for p in a.main_model.parameters()]
+    named = list(zip([n for n, _ in a.main_model.named_parameters()], params))
+    groups = [{"params": [p for n, p in named if p.dim() == 1], "weight_decay": 0.0},
+              {"params": [p for n, p in named if p.dim() != 1], "weight_decay": 1e-2}]
+    stock = torch.optim.SGD(groups, lr=0.1, momentum=0.9) if kind == "sgd" else torch.optim.AdamW(groups, lr=1e-2)
+    stock.load_state_dict(a.main_optimizer.state_dict())
