@@ -172,7 +172,7 @@ class ClockSampler:
 # CPU restatement (cpu_baseline leg and --impl reference)
 # --------------------------------------------------------------------------------------
 
-def _cpu_worker(rank, world, port, layout, K, opt, steps, warmup, threads, q):
+def _cpu_worker(rank, world, port, layout, K, opt, steps, warmup, threads, q, budget_s=60.0):
     import torch
     import torch.distributed as dist
     from oracle.reference_path import ReferencePath
@@ -188,23 +188,32 @@ def _cpu_worker(rank, world, port, layout, K, opt, steps, warmup, threads, q):
     for k in range(K):
         g = torch.Generator().manual_seed(1000 * rank + k)
         ref.grads[k].normal_(0.0, 1e-3, generator=g)
-    for _ in range(warmup):
+    for _ in range(max(1, min(warmup, 3))):
         ref.run_iteration()
     if world > 1:
         dist.barrier()
+    # Bounded sample: at most `steps` iterations, and no more than `budget_s` seconds of them.
+    stop = torch.zeros(1, dtype=torch.int32)
+    done = 0
     t0 = time.perf_counter()
-    for _ in range(steps):
+    while done < steps:
         ref.run_iteration()
+        done += 1
+        stop[0] = 1 if (time.perf_counter() - t0) > budget_s else 0
+        if world > 1:
+            dist.all_reduce(stop, op=dist.ReduceOp.MAX)
+        if int(stop[0]):
+            break
     if world > 1:
         dist.barrier()
-    dt = time.perf_counter() - t0
+    dt = (time.perf_counter() - t0) / done * steps          # seconds for `steps` iterations at the sampled rate
     if rank == 0:
-        q.put(dt)
+        q.put((dt, done))
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_cpu_path(layout, K, opt, world, steps, warmup):
+def run_cpu_path(layout, K, opt, world, steps, warmup, budget_s=60.0):
     """Seconds for `steps` iterations of the CPU/gloo restatement with `world` ranks that
     share this host's cores."""
     import torch.multiprocessing as mp
@@ -216,16 +225,17 @@ def run_cpu_path(layout, K, opt, world, steps, warmup):
     if world == 1:
         import queue
         qq = queue.Queue()
-        _cpu_worker(0, 1, port, layout, K, opt, steps, warmup, threads, qq)
-        return qq.get(), cores, threads
-    procs = [ctx.Process(target=_cpu_worker, args=(r, world, port, layout, K, opt, steps, warmup, threads, q))
-             for r in range(world)]
+        _cpu_worker(0, 1, port, layout, K, opt, steps, warmup, threads, qq, budget_s)
+        dt, done = qq.get()
+        return dt, cores, threads, done
+    procs = [ctx.Process(target=_cpu_worker, args=(r, world, port, layout, K, opt, steps, warmup, threads, q,
+                                                   budget_s)) for r in range(world)]
     for p in procs:
         p.start()
-    dt = q.get(timeout=1800)
+    dt, done = q.get(timeout=1800)
     for p in procs:
         p.join()
-    return dt, cores, threads
+    return dt, cores, threads, done
 
 
 def run_reference(args):
@@ -234,13 +244,13 @@ def run_reference(args):
         return
     layout, K, lbs, opt, desc = make_workload(args)
     world = args.gpus
-    dt, cores, threads = run_cpu_path(layout, K, opt, world, args.steps, args.warmup)
+    dt, cores, threads, done = run_cpu_path(layout, K, opt, world, args.steps, args.warmup, budget_s=90.0)
     ms = dt / args.steps * 1e3
     value = world * K * lbs / (ms / 1e3)
     cfg = config_dict(args, layout, K, lbs, opt, desc, world)
     cfg["similarity_mode"] = "pair_exchange" if world > 1 else "vsw_parity"
-    sample = (f"{args.steps} full iterations of the workload after {args.warmup} warm-up, "
-              f"{world} gloo rank(s) x {threads} torch threads on {cores} host cores")
+    sample = (f"{done} full iterations of the workload (of {args.steps} asked; at most 90 s are sampled) after "
+              f"{max(1, min(args.warmup, 3))} warm-up, {world} gloo rank(s) x {threads} torch threads on {cores} host cores")
     line = {
         "impl": "reference", "metric": "samples/sec", "value": value, "unit": "samples/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
@@ -440,11 +450,11 @@ def run_ours(args):
             "nccl_barriers_per_step": 2, "bus_peak_gbs": 900.0}
     if not args.no_cpu_baseline and world == 1:      # the CPU baseline is reported at N = 1 only
         cpu_steps = args.cpu_steps or 10
-        dt, cores, threads = run_cpu_path(layout, K, opt, 1, cpu_steps, 2)
+        dt, cores, threads, done = run_cpu_path(layout, K, opt, 1, cpu_steps, 2, budget_s=30.0)
         line["cpu_baseline"] = {
             "value": K * lbs / (dt / cpu_steps), "unit": "samples/s", "cores": cores, "kind": "port",
             "ms_per_step": dt / cpu_steps * 1e3,
-            "sample": f"{cpu_steps} iterations of this workload at one rank (K={K}) after 2 warm-up, "
+            "sample": f"{done} iterations of this workload at one rank (K={K}) after 2 warm-up, "
                       f"stock torch CPU ops, {threads} threads"}
     print(json.dumps(line), flush=True)
     _finish(world)
