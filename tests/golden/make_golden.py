@@ -152,7 +152,9 @@ def _worker(rank, ref_root, port, q):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/reference-checkout")
+    ref_root = sys.argv[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_worker, args=(r, ref_root, 29871, q)) for r in range(WORLD)]
