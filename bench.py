@@ -506,7 +506,8 @@ def measure_training_iteration(K, lbs, dev, world, iters=8):
     cfg = dict(similarity_target=0.1, batch_size_adjust_interval=1, enable_adjust=False)
     tr = jabas_b200.JABASTrainer(dev.index, lbs, K, 0, "overlap", cfg)
     torch.manual_seed(0)
-    tr.prepare_stream_parallel(torchvision.models.resnet50().to(dev), torch.nn.CrossEntropyLoss().to(dev))
+    tr.prepare_stream_parallel(torchvision.models.resnet50().to(dev), torch.nn.CrossEntropyLoss().to(dev),
+                               gradient_as_bucket_view=True)
 
     def groups(m):
         named = list(m.named_parameters())
