@@ -61,6 +61,8 @@ def parse_args():
     ap.add_argument("--no-overlap", action="store_true")
     ap.add_argument("--per-bucket", default="auto", choices=["auto", "yes", "no"],
                     help="yes: walk the DDP buckets as the comm hooks do; no / auto: the whole flat model per launch")
+    ap.add_argument("--share-weights", action="store_true",
+                    help="the K replicas alias one weight buffer (no write-back to K-1 replicas); not the default")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch every kernel / collective from Python instead of replaying one CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
@@ -104,6 +106,7 @@ def config_dict(args, layout, K, lbs, opt, desc, world):
         "similarity": "every iteration", "similarity_mode": args.similarity_mode if world > 1 else "vsw_parity",
         "overlap": not args.no_overlap,
         "cuda_graph": (not args.no_graph) and args.impl == "ours",
+        "replica_weights": "one shared buffer" if getattr(args, "share_weights", False) else "K separate buffers",
         "collective": ("peer-memory kernels over NVLink" if args.collective == "peer" else "NCCL allreduce")
                       if world > 1 else "none",
         "launch_granularity": "bucket" if args.per_bucket == "yes"
@@ -307,11 +310,13 @@ def run_ours(args):
     similarity = not args.no_similarity and (world * K) % 2 == 0 and (world > 1 or K % 2 == 0)
     eng = GradientPath(layout, K, dev, spec, total_num_decoupled_workers=world * K,
                        sub_group=sub_group, pair_group=pair_group, similarity=similarity,
-                       similarity_mode=args.similarity_mode, collective=args.collective)
+                       similarity_mode=args.similarity_mode, collective=args.collective,
+                       share_weights=args.share_weights)
     gen = torch.Generator(device=dev).manual_seed(7)
     eng.weights[0].normal_(generator=gen)
-    for k in range(1, K):
-        eng.weights[k].copy_(eng.weights[0])
+    if not args.share_weights:
+        for k in range(1, K):
+            eng.weights[k].copy_(eng.weights[0])
     for k in range(K):
         g = torch.Generator(device=dev).manual_seed(1000 * rank + k)
         eng.grads[k].normal_(0.0, 1e-3, generator=g)

@@ -60,7 +60,7 @@ class GradientPath:
                  total_num_decoupled_workers: int, process_group=None, sub_group=None,
                  pair_group=None, first_subgroup_src_rank: int = 0, second_subgroup_src_rank: int = 1,
                  similarity: bool = True, similarity_mode: str = "fused", backend=None,
-                 collective: str = "nccl"):
+                 collective: str = "nccl", share_weights: bool = False):
         if backend is None:
             from . import ops as backend          # the CUDA library; raises without a GPU
         self.ops = backend
@@ -92,7 +92,15 @@ class GradientPath:
         self.dev_layout = None
         n = layout.total
         f32 = dict(dtype=torch.float32, device=self.device)
-        self.weights = [torch.zeros(n, **f32) for _ in range(self.K)]
+        #: K replicas may alias ONE weight buffer: forward/backward only read the weights, and a
+        #: bucket is updated only after every VSW has finished with it, so the write-back to the
+        #: other K-1 replicas (4(K-1) bytes per element and iteration) has nothing left to do
+        self.share_weights = bool(share_weights)
+        if self.share_weights:
+            w0 = torch.zeros(n, **f32)
+            self.weights = [w0] * self.K
+        else:
+            self.weights = [torch.zeros(n, **f32) for _ in range(self.K)]
         self.grads = [torch.zeros(n, **f32) for _ in range(self.K)]
         if collective not in ("nccl", "peer"):
             raise ValueError("collective must be 'nccl' or 'peer'")
@@ -209,7 +217,10 @@ class GradientPath:
         if not 1 <= new_k <= getattr(self.ops, "MAX_VSW", 16):
             raise ValueError("the number of VSWs must be between 1 and 16")
         f32 = dict(dtype=torch.float32, device=self.device)
-        if new_k > self.K:
+        if new_k > self.K and self.share_weights:
+            self.weights.extend([self.weights[0]] * (new_k - self.K))
+            self.grads.extend(torch.zeros(self.layout.total, **f32) for _ in range(new_k - self.K))
+        elif new_k > self.K:
             fresh = [torch.empty(self.layout.total, **f32) for _ in range(new_k - self.K)]
             self.ops.replicate(self.ctx, self.weights[0], fresh)
             self.launches += 1
@@ -240,6 +251,11 @@ class GradientPath:
     @property
     def main_grad(self) -> torch.Tensor:
         return self.grads[0]
+
+    def _replicas(self, begin: int, end: int):
+        """Weight buffers an update has to write: all K replicas, or the one they share."""
+        ws = self.weights[:1] if self.share_weights else self.weights
+        return [w[begin:end] for w in ws]
 
     def _ev_begin(self):
         if self.profile_events is None:
@@ -349,7 +365,7 @@ class GradientPath:
         if self.collective == "peer":
             g, kw["peer_grad"] = None, self._peer_grad
             kw.pop("half", None); kw.pop("half_divisor", None); kw.pop("stat", None)
-        ws = [w[begin:end] for w in self.weights]
+        ws = self._replicas(begin, end)
         o = self.opt
         ev = self._ev_begin()
         if o.kind == "sgd":
@@ -441,7 +457,7 @@ class GradientPath:
             gs = list(sources)
         else:
             gs = [g[begin:end] for g in self.grads]
-        ws = [w[begin:end] for w in self.weights]
+        ws = self._replicas(begin, end)
         kw = dict(layout=self.dev_layout, base=begin, grad_out=gs[0] if keep_grad else None)
         if self._sim_step:
             kw.update(half_divisor=self.T / 2, stat=self.stat)
@@ -580,11 +596,12 @@ class GradientPath:
         """Bytes each stage must move per iteration on this GPU (fp32 = 4 B)."""
         n, K = self.layout.num_params, self.K
         multi = self.world > 1
+        Kw = 1 if self.share_weights else K          # weight buffers written by the update
         # K = 1 with nothing to clone: the division by T folds into the update's read of g
         agg = (4 * n * (K + 1) if (K > 1 or multi) else 0) + (4 * n if (similarity_step and multi) else 0)
-        per_elem = (K + 4) if self.opt.kind == "sgd" else (K + 6)
+        per_elem = (Kw + 4) if self.opt.kind == "sgd" else (Kw + 6)
         if self.opt.kind == "sgd" and self.opt.momentum == 0:
-            per_elem = K + 2
+            per_elem = Kw + 2
         upd = 4 * n * per_elem + (4 * n if (similarity_step and multi) else 0)
         fused = 4 * n * (K + per_elem - 1)          # the averaged gradient stays in registers
         out = {"aggregate": agg, "update": upd, "total": agg + upd, "fused_step": fused}

@@ -115,6 +115,9 @@ class IIDPTrainer(object):
         kwargs.setdefault("gradient_as_bucket_view", True)
         bucket_cap_mb = kwargs.pop("bucket_cap_mb", 25)
         first_bucket_bytes = kwargs.pop("first_bucket_bytes", None)
+        # share_weights=True: the K replicas' parameters are views of ONE flat weight buffer
+        # (they are only read between updates), which removes the write-back to K-1 replicas
+        share_weights = kwargs.pop("share_weights", False)
         self.criterion = criterion
         K = self.num_models
         self.model_streams = [torch.cuda.Stream(self.device) if self._cuda else None for _ in range(K)]
@@ -123,7 +126,7 @@ class IIDPTrainer(object):
         self.reducer = VSWReducer(self.device, K, self.total_num_decoupled_workers, bucket_cap_mb,
                                   similarity=self._similarity_enabled(),
                                   similarity_mode=self._similarity_mode(), backend=self._backend,
-                                  first_bucket_bytes=first_bucket_bytes)
+                                  first_bucket_bytes=first_bucket_bytes, share_weights=share_weights)
         self._sync_buffer_barrier = [None, None]
         self.local_models = [
             IndependentIdenticalDataParallel(

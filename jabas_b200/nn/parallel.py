@@ -123,12 +123,13 @@ class VSWReducer:
     def __init__(self, device, num_local_models: int, total_num_models: int,
                  bucket_cap_mb: float = DEFAULT_BUCKET_CAP_MB, similarity: bool = False,
                  similarity_mode: str = "fused", process_group=None, backend=None,
-                 first_bucket_bytes: Optional[int] = None):
+                 first_bucket_bytes: Optional[int] = None, share_weights: bool = False):
         self.device = torch.device(device)
         self.K = int(num_local_models)
         self.T = int(total_num_models)
         self.bucket_cap_mb = bucket_cap_mb
         self.first_bucket_bytes = first_bucket_bytes
+        self.share_weights = share_weights
         self.similarity, self.similarity_mode = similarity, similarity_mode
         self.process_group, self.backend = process_group, backend
         self.engine: Optional[GradientPath] = None
@@ -149,7 +150,7 @@ class VSWReducer:
             self.engine = GradientPath(self.layout, self.K, self.device, None,
                                        total_num_decoupled_workers=self.T, process_group=self.process_group,
                                        similarity=self.similarity, similarity_mode=self.similarity_mode,
-                                       backend=self.backend)
+                                       backend=self.backend, share_weights=self.share_weights)
             if self.device.type == "cuda":
                 self.path_stream = torch.cuda.Stream(self.device)
         self.wrappers[k] = wrapper

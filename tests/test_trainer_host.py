@@ -394,3 +394,33 @@ def test_checkpoint_round_trip(kind, tmp_path):
               {"params": [p for n, p in named if p.dim() != 1], "weight_decay": 1e-2}]
     stock = torch.optim.SGD(groups, lr=0.1, momentum=0.9) if kind == "sgd" else torch.optim.AdamW(groups, lr=1e-2)
     stock.load_state_dict(a.main_optimizer.state_dict())
+
+
+@pytest.mark.parametrize("wsm", ["sequential", "overlap"])
+def test_replicas_may_share_one_weight_buffer(wsm):
+    """share_weights=True: every replica's parameters are views of the same flat buffer, the
+    update writes it once, and results are those of K separate replicas."""
+    K = 4
+    tr = jabas_b200.JABASTrainer("cpu", 8, K, 0, wsm, dict(CFG))
+    tr._backend = oracle_backend
+    tr.prepare_stream_parallel(_model(), torch.nn.CrossEntropyLoss(), bucket_cap_mb=0.01,
+                               first_bucket_bytes=2048, share_weights=True)
+    groups = _groups(tr.main_model)
+    opt = (ShardSGD if wsm == "overlap" else torch.optim.SGD)(groups, lr=0.1, momentum=0.9)
+    tr.prepare_weight_sync_method(opt, None, _groups)
+    eng = tr.reducer.engine
+    assert all(w.data_ptr() == eng.weights[0].data_ptr() for w in eng.weights)
+    p0 = next(tr.local_models[0].parameters()); p3 = next(tr.local_models[3].parameters())
+    assert p0.data_ptr() == p3.data_ptr() and p0 is not p3
+    ref = _reference_for(tr, "sgd")
+    g = torch.Generator().manual_seed(1)
+    for it in range(3):
+        x, y = torch.randn(8 * K, 20, generator=g), torch.randint(0, 10, (8 * K,), generator=g)
+        for k, flat in enumerate(_vsw_gradients(tr, x, y)):
+            ref.grads[k].copy_(flat)
+        cos_ref = ref.run_iteration()
+        tr.compute((x, y)); tr.step()
+        assert torch.equal(eng.weights[0], ref.weights[0])
+        assert abs(float(tr.cos_placeholder) - cos_ref) < 1e-5
+    tr.change_num_models(2); tr.change_num_models(4)
+    assert eng.weights[3].data_ptr() == eng.weights[0].data_ptr()
