@@ -144,6 +144,17 @@ JABAS_API int jabas_vsw_aggregate_f32(jabas_ctx_t* ctx, const float* const* grad
                             float* half_out, uint64_t n, float divisor, float half_divisor,
                             double* stat3, void* stream);
 
+/* Local aggregation whose result is scattered, shard by shard, into the ranks that will
+ * reduce it: element i of  (g[0] + ... + g[K-1]) / divisor  is stored to
+ * slots[i / shard_len][i % shard_len].  slots[j] is this rank's staging slot inside rank j's
+ * peer-mapped buffer, so the reduce-scatter traffic crosses NVLink as plain stores while the
+ * kernel streams the K local gradients from HBM; the owner then reduces its n slots locally
+ * (jabas_peer_reduce_f32 with local pointers).  First stage of the cross-GPU exchange that
+ * replaces the allreduces of jabas/ddp_comm_hooks/similarity_allreduce.py:30,42. */
+JABAS_API int jabas_vsw_aggregate_scatter_f32(jabas_ctx_t* ctx, const float* const* grads, int K,
+                                    float* const* slots, int nranks, uint64_t shard_len, uint64_t n,
+                                    float divisor, void* stream);
+
 /* x /= divisor in place.  Replaces `div_(T/2)` at
  * jabas/ddp_comm_hooks/similarity_allreduce.py:32. */
 JABAS_API int jabas_div_f32(jabas_ctx_t* ctx, float* x, uint64_t n, float divisor, void* stream);

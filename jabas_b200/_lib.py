@@ -21,7 +21,7 @@ EXPORTS = (
     "jabas_sgd_momentum_f32", "jabas_adam_f32", "jabas_dot_norms_f32", "jabas_cosine_finalize",
     "jabas_replicate_f32", "jabas_dot_norms_static_f32", "jabas_vsw_sgd_momentum_f32",
     "jabas_vsw_adam_f32", "jabas_sumsq_f32", "jabas_clip_coef", "jabas_dynhp_create",
-    "jabas_dynhp_destroy", "jabas_dynhp_push_sgd", "jabas_dynhp_push_adam", "jabas_peer_reduce_f32",
+    "jabas_dynhp_destroy", "jabas_dynhp_push_sgd", "jabas_dynhp_push_adam", "jabas_peer_reduce_f32", "jabas_vsw_aggregate_scatter_f32",
 )
 
 
@@ -99,6 +99,7 @@ def load() -> ctypes.CDLL:
     lib.jabas_dynhp_destroy.argtypes = [vp]
     lib.jabas_dynhp_push_sgd.argtypes = [vp, ctypes.POINTER(Group), i32, ctypes.POINTER(SgdHp), vp]
     lib.jabas_dynhp_push_adam.argtypes = [vp, ctypes.POINTER(Group), i32, ctypes.POINTER(AdamHp), vp]
+    lib.jabas_vsw_aggregate_scatter_f32.argtypes = [vp, pvp, i32, pvp, i32, u64, u64, f32, vp]
     lib.jabas_peer_reduce_f32.argtypes = [vp, pvp, i32, vp, u64, u64, f32, f32, vp, vp]
     lib.jabas_sumsq_f32.argtypes = [vp, vp, u64, vp, vp]
     lib.jabas_clip_coef.argtypes = [vp, vp, f64, vp, vp]

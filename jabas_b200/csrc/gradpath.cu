@@ -158,7 +158,25 @@ struct AggArgs {
     float divisor;
     float half_divisor;
     int K;
+    // scatter mode (nscatter > 0): element i goes to scatter[i / shard_len][i % shard_len] — the
+    // staging slot this rank owns inside the buffer of the rank that reduces that shard (peer
+    // memory, written over NVLink while the K local gradients stream in from HBM)
+    int nscatter;
+    unsigned long long shard_len;
+    float* scatter[JABAS_MAX_VSW];
 };
+
+__device__ __forceinline__ float* agg_dst(const AggArgs& a, unsigned long long idx)
+{
+    if (a.nscatter == 0) return a.out + idx;
+    const unsigned long long owner = idx / a.shard_len;
+    float* p = a.scatter[0];
+#pragma unroll
+    for (int r = 1; r < JABAS_MAX_VSW; ++r)
+        if (owner >= (unsigned long long)r && r < a.nscatter) p = a.scatter[r];
+    const unsigned long long o = owner < (unsigned long long)a.nscatter ? owner : (unsigned long long)(a.nscatter - 1);
+    return p + (idx - o * a.shard_len);
+}
 
 __host__ __device__ constexpr int agg_unroll(int K) { return K <= 2 ? 4 : (K <= 4 ? 2 : 1); }
 
@@ -187,7 +205,7 @@ __device__ __forceinline__ void agg_elem(const AggArgs& a, unsigned long long i,
         }
     }
     if (a.half) a.half[i] = s;
-    a.out[i] = __fdiv_rn(s, a.divisor);
+    *agg_dst(a, i) = __fdiv_rn(s, a.divisor);
     if (STAT) acc_one(acc, __fdiv_rn(e, a.half_divisor), __fdiv_rn(o, a.half_divisor));
 }
 
@@ -218,7 +236,7 @@ __global__ void __launch_bounds__(kThreads) agg_vec_kernel(const AggArgs a)
 #pragma unroll
                 for (int k = 1; k < K; ++k) s = add4(s, x[u][k]);
                 if (a.half) st4(a.half + 4 * v, s);
-                st4(a.out + 4 * v, div4(s, a.divisor));
+                st4(agg_dst(a, 4 * v), div4(s, a.divisor));
                 if (STAT) {
                     float4 e = x[u][0];
                     float4 o = K > 1 ? x[u][K > 1 ? 1 : 0] : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -1059,6 +1077,45 @@ int jabas_vsw_aggregate_f32(jabas_ctx_t* ctx, const float* const* grads, int K, 
             if ((rc = grid_for(ctx, agg_scalar_kernel<false>, n, kThreads, &grid))) return rc;
             agg_scalar_kernel<false><<<grid, kThreads, 0, st>>>(a);
         }
+    }
+    JB_CUDA(cudaGetLastError());
+    return JABAS_OK;
+}
+
+int jabas_vsw_aggregate_scatter_f32(jabas_ctx_t* ctx, const float* const* grads, int K,
+                                    float* const* slots, int nranks, uint64_t shard_len, uint64_t n,
+                                    float divisor, void* stream)
+{
+    int rc = ctx_bind(ctx);
+    if (rc) return rc;
+    if (!grads || !slots) return fail(JABAS_EINVAL, "grads or slots is null");
+    if (K < 1 || K > JABAS_MAX_VSW) return fail(JABAS_EINVAL, "K must be in [1, JABAS_MAX_VSW]");
+    if (nranks < 1 || nranks > JABAS_MAX_VSW) return fail(JABAS_EINVAL, "nranks must be in [1, 16]");
+    if (shard_len == 0 || (shard_len & 3ull)) return fail(JABAS_EINVAL, "shard_len must be a positive multiple of 4");
+    if ((uint64_t)nranks * shard_len < n) return fail(JABAS_EINVAL, "nranks * shard_len must cover n");
+    if (!(divisor != 0.0f)) return fail(JABAS_EINVAL, "divisor must be non-zero");
+    if (n == 0) return JABAS_OK;
+    AggArgs a;
+    std::memset(&a, 0, sizeof(a));
+    bool vec = true;
+    for (int k = 0; k < K; ++k) {
+        if (!grads[k]) return fail(JABAS_EINVAL, "grads[k] is null");
+        a.g[k] = grads[k];
+        vec = vec && aligned16(grads[k]);
+    }
+    for (int r = 0; r < nranks; ++r) {
+        if (!slots[r]) return fail(JABAS_EINVAL, "slots[r] is null");
+        a.scatter[r] = slots[r];
+        vec = vec && aligned16(slots[r]);
+    }
+    a.nscatter = nranks; a.shard_len = shard_len; a.n = n; a.divisor = divisor; a.half_divisor = 1.0f; a.K = K;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (vec) {
+        if ((rc = agg_dispatch<1>(ctx, a, st))) return rc;
+    } else {
+        int grid = 0;
+        if ((rc = grid_for(ctx, agg_scalar_kernel<false>, n, kThreads, &grid))) return rc;
+        agg_scalar_kernel<false><<<grid, kThreads, 0, st>>>(a);
     }
     JB_CUDA(cudaGetLastError());
     return JABAS_OK;

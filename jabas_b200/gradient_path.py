@@ -142,30 +142,43 @@ class GradientPath:
         import torch.distributed._symmetric_memory as symm_mem
         n, world = self.layout.total, self.world
         group = self.pg if self.pg is not None else dist.group.WORLD
-        self.px = symm_mem.empty(n, dtype=torch.float32, device=self.device)
+        shard = -(-n // world)
+        self.shard_len = -(-shard // 32) * 32                       # 128-byte aligned shards
+        self.shard_lo = min(self.rank * self.shard_len, n)
+        self.shard_hi = min(self.shard_lo + self.shard_len, n)
+        # px: `world` staging slots of one shard each (slot r = rank r's contribution to the
+        # shard this rank reduces); the two-rank direct form uses it as one full-length buffer
+        self.px = symm_mem.empty(world * self.shard_len, dtype=torch.float32, device=self.device)
         self.pgrad = symm_mem.empty(n, dtype=torch.float32, device=self.device)
         self.px.zero_(); self.pgrad.zero_()
         self._px_h = symm_mem.rendezvous(self.px, group)
         self._pg_h = symm_mem.rendezvous(self.pgrad, group)
         self.px_ptrs = [int(p) for p in self._px_h.buffer_ptrs]
         self.pg_ptrs = [int(p) for p in self._pg_h.buffer_ptrs]
-        shard = -(-n // world)
-        self.shard_len = -(-shard // 32) * 32                       # 128-byte aligned shards
-        self.shard_lo = min(self.rank * self.shard_len, n)
-        self.shard_hi = min(self.shard_lo + self.shard_len, n)
+        # where this rank's partial sums go: its slot inside every owner's staging buffer
+        self._scatter_ptrs = [p + 4 * self.rank * self.shard_len for p in self.px_ptrs]
+        # the `world` local slots, addressed so that slot r holds elements [shard_lo, shard_hi)
+        self._slot_ptrs = [self.px.data_ptr() + 4 * (r * self.shard_len - self.shard_lo) for r in range(world)]
         self._peer_grad = self.ops.PeerGrad(self.pg_ptrs, self.shard_len)
         self._tok = torch.zeros(1, dtype=torch.float32, device=self.device)
 
     def _peer_iteration(self) -> Optional[torch.Tensor]:
-        """Whole flat model through the peer-memory exchange:
-        aggregate -> barrier -> reduce-scatter kernel over NVLink -> barrier (carrying the
-        3-double statistic) -> update kernel that gathers the gradient shards over NVLink."""
+        """Whole flat model through the peer-memory exchange.  More than two ranks:
+        aggregate kernel that scatters its sums, shard by shard, into the owners' staging
+        slots (NVLink stores, hidden under the K-way HBM read) -> barrier -> local reduce of
+        the n slots (+ statistic from the exact even/odd-rank halves) -> barrier carrying the
+        3-double statistic -> update kernel that gathers the gradient shards over NVLink."""
         sim = self._sim_step
+        n = self.layout.total
+        direct = self.peer_direct and self.world <= getattr(self.ops, "MAX_FUSED_VSW", 0)
         ev = self._ev_begin()
-        self.ops.vsw_aggregate(self.ctx, self.grads, self.px, 1.0)                 # undivided local sum
+        if direct:
+            self.ops.vsw_aggregate(self.ctx, self.grads, self.px[:n], 1.0)         # undivided local sum
+        else:
+            self.ops.vsw_aggregate_scatter(self.ctx, self.grads, self._scatter_ptrs, self.shard_len, n, 1.0)
         self._ev_end("aggregate", None, ev)
-        dist.all_reduce(self._tok, group=self.pg)                                  # every rank's sum is in place
-        if self.peer_direct and self.world <= getattr(self.ops, "MAX_FUSED_VSW", 0):
+        dist.all_reduce(self._tok, group=self.pg)                                  # every rank's sums are in place
+        if direct:
             # Two GPUs: the update kernel itself reads both ranks' sums (the remote one over
             # NVLink, hidden under its own HBM traffic), averages, takes the statistic from
             # the two ranks = the two halves, and updates: no reduce-scatter pass at all.
@@ -178,7 +191,7 @@ class GradientPath:
                 return self.cos
             return None
         ev = self._ev_begin()
-        self.ops.peer_reduce(self.ctx, self.px_ptrs, self.pgrad.data_ptr(), self.shard_lo, self.shard_hi,
+        self.ops.peer_reduce(self.ctx, self._slot_ptrs, self.pgrad.data_ptr(), self.shard_lo, self.shard_hi,
                              float(self.T), half_divisor=self.T / 2, stat=self.stat if sim else None)
         self._ev_end("peer_reduce", None, ev)
         dist.all_reduce(self.stat if sim else self._tok, group=self.pg)            # barrier + global sums
@@ -607,8 +620,9 @@ class GradientPath:
         out = {"aggregate": agg, "update": upd, "total": agg + upd, "fused_step": fused}
         if self.collective == "peer":
             # what the kernels of the peer exchange move through THIS GPU's HBM: the aggregate
-            # writes no copy for the sub-group, the reduce-scatter kernel reads every rank's
-            # shard once (one buffer's worth in total per GPU) and writes its own shard
+            # reads K gradients and writes one buffer's worth of partial sums (1/n of it locally,
+            # the rest into peers, whose stores land here in turn), the reduce kernel reads the
+            # n local slots and writes its shard
             out["aggregate"] = 4 * n * (K + 1)
             out["peer_reduce"] = 4 * n + 4 * n // self.world
             out["update"] = 4 * n * per_elem

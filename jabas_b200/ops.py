@@ -273,6 +273,16 @@ def dot_norms(ctx: Context, a: torch.Tensor, b: torch.Tensor, stat: torch.Tensor
                                             _stream_handle(ctx.device, stream)))
 
 
+def vsw_aggregate_scatter(ctx: Context, grads: Sequence[torch.Tensor], slot_ptrs: Sequence[int],
+                          shard_len: int, n: int, divisor: float, *, stream=None) -> None:
+    """Local sum of the K VSW gradients / divisor, scattered shard by shard into the staging
+    slots ``slot_ptrs[j]`` (raw device pointers into rank j's peer-mapped buffer)."""
+    gp = _ptr_array([_dev_f32(g, ctx.device, "grads[k]") for g in grads])
+    sp = _ptr_array([int(p) for p in slot_ptrs])
+    _lib.check(ctx._lib.jabas_vsw_aggregate_scatter_f32(ctx._h, gp, len(grads), sp, len(slot_ptrs), shard_len,
+                                                        n, divisor, _stream_handle(ctx.device, stream)))
+
+
 def peer_reduce(ctx: Context, peer_ptrs: Sequence[int], g_out_ptr: int, lo: int, hi: int, divisor: float, *,
                 half_divisor: float = 1.0, stat: Optional[torch.Tensor] = None, stream=None) -> None:
     """This rank's shard ``[lo, hi)`` of the world-averaged gradient, read from every rank's
@@ -330,5 +340,5 @@ def replicate(ctx: Context, src: torch.Tensor, dsts: Sequence[torch.Tensor], *, 
                                             src.numel(), _stream_handle(ctx.device, stream)))
 
 
-__all__ = ["Context", "Layout", "DynHp", "PeerGrad", "peer_reduce", "JabasError", "MAX_VSW", "MAX_GROUPS", "vsw_aggregate", "div_",
+__all__ = ["Context", "Layout", "DynHp", "PeerGrad", "peer_reduce", "vsw_aggregate_scatter", "JabasError", "MAX_VSW", "MAX_GROUPS", "vsw_aggregate", "div_",
            "sgd_momentum", "adam", "vsw_sgd_momentum", "vsw_adam", "MAX_FUSED_VSW", "sumsq", "clip_coef", "dot_norms", "dot_norms_static", "cosine_finalize", "replicate"]
