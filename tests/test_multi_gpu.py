@@ -117,6 +117,8 @@ def _engine_rank(rank, world, port, collective, kind, K, q, direct=None):
                            sub_group=groups[rank % 2], pair_group=pair, collective=collective)
         if direct is not None:
             eng.peer_direct = direct
+        if direct is False and K == 2:
+            eng.peer_form = "scatter"
         ref = ReferencePath(layout, K, opt, total_num_decoupled_workers=T, arith="c")
         rng = np.random.default_rng(5)
         w0 = rng.standard_normal(layout.total).astype(np.float32)
@@ -165,8 +167,9 @@ def _engine_rank(rank, world, port, collective, kind, K, q, direct=None):
                                                       ("peer", "sgd", 2, False), ("nccl", "sgd", 2, None)])
 def test_engine_exchange_modes_match_reference_path(collective, kind, K, direct):
     """The gradient path at engine level on 2 (or, when visible, 4) GPUs: the peer-memory
-    exchange in both forms (``direct``: the update kernel reads both ranks' sums; otherwise
-    reduce-scatter kernel + gathering update kernel), eager and as a replayed CUDA graph, and
+    exchange in its forms (``direct``: the update kernel reads both ranks' sums; otherwise a
+    reduce kernel that pulls its shard from the peers — or, for the K = 2 case, local staging
+    slots filled by scattering aggregate kernels — and a gathering update kernel), eager and as a replayed CUDA graph, and
     the NCCL exchange, against the reference path over gloo."""
     world = 2 if torch.cuda.device_count() < 4 else 4
     if torch.cuda.device_count() < 2:
