@@ -154,6 +154,12 @@ def _engine_rank(rank, world, port, collective, kind, K, q, direct=None):
                 w = eng.weights[k].cpu()
                 worst_w = max(worst_w, float(((w - wr).abs() / wr.abs().clamp_min(1e-3)).max()))
             worst_c = max(worst_c, abs(cos - cos_ref))
+        # every rank must hold the same bits (no drift between data-parallel replicas)
+        chk = int(eng.weights[0].view(torch.int32).to(torch.int64).sum())
+        sums = [None] * world
+        dist.all_gather_object(sums, chk)
+        if len(set(sums)) != 1:
+            worst_w = float("inf")
         q.put((rank, worst_w, worst_c, eng.launches))
         dist.barrier()
         torch.cuda.synchronize()
