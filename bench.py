@@ -182,6 +182,10 @@ def _cpu_worker(rank, world, port, layout, K, opt, steps, warmup, threads, q, bu
     import torch.distributed as dist
     from oracle.reference_path import ReferencePath
     torch.set_num_threads(max(1, threads))
+    # When the parent is a torchrun worker its environment says "the elastic agent hosts the
+    # rendezvous store"; these CPU ranks rendezvous among themselves on their own port instead.
+    for var in [v for v in os.environ if v.startswith("TORCHELASTIC_")]:
+        os.environ.pop(var, None)
     if world > 1:
         dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
     ref = ReferencePath(layout, K, opt, total_num_decoupled_workers=world * K, similarity=True, arith="torch",

@@ -40,3 +40,18 @@ def test_default_arm_prints_one_json_line():
     assert d["gpu_launches"] >= 20 and d["value"] > 0 and d["e2e"]["value"] > 0
     assert d["e2e"]["h2d_bytes_per_step"] == 4 * 4 * (1 << 22) and d["e2e"]["d2h_bytes_per_step"] == 4
     assert d["cpu_baseline"]["value"] > 0 and d["dtype"] == "f32" and -1.0 <= d["cosine"] <= 1.0
+
+
+def test_reference_arm_under_torchrun_with_two_ranks():
+    """Launched the way a multi-GPU run is: rank 0 alone runs the CPU ranks (which must ignore
+    the launcher's rendezvous environment) and prints the line; the other rank exits 0."""
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29571", os.path.join(ROOT, "bench.py"),
+                          "--impl", "reference", "--gpus", "2", "--workload", "flat20", "--vsw", "2",
+                          "--steps", "2", "--warmup", "1"], capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [l for l in out.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["n_gpus"] == 2 and d["value"] > 0
+    assert "2 gloo rank(s)" in d["cpu_baseline"]["sample"]
