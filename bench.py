@@ -312,10 +312,22 @@ def run_ours(args):
     spec = OptimizerSpec(kind=opt["kind"], groups=opt["groups"], momentum=opt.get("momentum", 0.0),
                          betas=opt.get("betas", (0.9, 0.999)), eps=opt.get("eps", 1e-8))
     similarity = not args.no_similarity and (world * K) % 2 == 0 and (world > 1 or K % 2 == 0)
-    eng = GradientPath(layout, K, dev, spec, total_num_decoupled_workers=world * K,
-                       sub_group=sub_group, pair_group=pair_group, similarity=similarity,
-                       similarity_mode=args.similarity_mode, collective=args.collective,
-                       share_weights=args.share_weights)
+    collective, collective_note = args.collective, None
+
+    def make_engine(coll):
+        return GradientPath(layout, K, dev, spec, total_num_decoupled_workers=world * K,
+                            sub_group=sub_group, pair_group=pair_group, similarity=similarity,
+                            similarity_mode=args.similarity_mode, collective=coll,
+                            share_weights=args.share_weights)
+    try:
+        eng = make_engine(collective)
+    except Exception as e:
+        if world == 1 or collective != "peer":
+            raise
+        # peer mappings could not be set up on this machine (every rank sees the same failure):
+        # the exchange goes through NCCL instead, and the result line says so
+        collective, collective_note = "nccl", f"peer-memory set-up failed ({type(e).__name__}: {e})"[:200]
+        eng = make_engine("nccl")
     gen = torch.Generator(device=dev).manual_seed(7)
     eng.weights[0].normal_(generator=gen)
     if not args.share_weights:
@@ -453,7 +465,9 @@ def run_ours(args):
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": dict(config_dict(args, layout, K, lbs, opt, desc, world),
-                                            similarity="every iteration" if similarity else "off"),
+                                            similarity="every iteration" if similarity else "off",
+                                            **({"collective": "NCCL allreduce", "collective_note": collective_note}
+                                               if collective_note else {})),
         "gradient_path_gbs_per_gpu": alg["total"] / (ms_step / 1e3) / 1e9,
         "gradient_path_frac_of_hbm_peak": alg["total"] / (ms_step / 1e3) / 1e9 / peak,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
