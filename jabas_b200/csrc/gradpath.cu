@@ -763,6 +763,7 @@ struct jabas_ctx {
 struct jabas_layout {
     int device = 0;
     int nseg = 0;
+    int max_group = 0;
     unsigned long long total = 0;
     SegDev* dsegs = nullptr;
 };
@@ -959,6 +960,8 @@ int upd_prepare(jabas_ctx_t* ctx, UpdArgs& a, bool* vec, const GradSrc& src, flo
     if (layout) {
         if (layout->device != ctx->device) return fail(JABAS_EINVAL, "layout belongs to another device");
         if (base + n > layout->total) return fail(JABAS_EINVAL, "base + n exceeds the layout");
+        if (layout->max_group >= ngroups)
+            return fail(JABAS_EINVAL, "the layout names a param group that the call does not provide");
         a.segs = layout->dsegs; a.nseg = layout->nseg;
     }
     if (stat3 && (rc = ws_for(ctx, stream, &a.ws))) return rc;
@@ -1010,17 +1013,19 @@ int jabas_layout_create(jabas_ctx_t* ctx, const jabas_seg_t* segs, int nseg, uin
     if (!segs || nseg < 1) return fail(JABAS_EINVAL, "empty segment table");
     std::vector<SegDev> h((size_t)nseg);
     uint64_t pos = 0;
+    int max_group = 0;
     for (int i = 0; i < nseg; ++i) {
         if (segs[i].begin != pos || segs[i].end <= segs[i].begin)
             return fail(JABAS_EINVAL, "segments must be sorted, non-empty and contiguous from 0");
         if (segs[i].group >= JABAS_MAX_GROUPS) return fail(JABAS_EINVAL, "segment group out of range");
         h[i].begin = segs[i].begin; h[i].end = segs[i].end; h[i].group = segs[i].group; h[i].pad = 0;
         pos = segs[i].end;
+        if ((int)segs[i].group > max_group) max_group = (int)segs[i].group;
     }
     if (pos != total) return fail(JABAS_EINVAL, "segments do not cover [0, total)");
     jabas_layout_t* l = new (std::nothrow) jabas_layout_t();
     if (!l) return fail(JABAS_ENOMEM, "out of host memory");
-    l->device = ctx->device; l->nseg = nseg; l->total = total;
+    l->device = ctx->device; l->nseg = nseg; l->total = total; l->max_group = max_group;
     cudaError_t e = cudaMalloc(&l->dsegs, sizeof(SegDev) * (size_t)nseg);
     if (e == cudaSuccess) e = cudaMemcpy(l->dsegs, h.data(), sizeof(SegDev) * (size_t)nseg, cudaMemcpyHostToDevice);
     if (e != cudaSuccess) {

@@ -59,6 +59,13 @@ class FusedBinding:
 
     def _spec(self) -> OptimizerSpec:
         o, d = self.optimizer, self.optimizer.defaults
+        # the kernels take lr and weight decay per group; everything else is per launch
+        shared = ("momentum", "dampening", "nesterov") if self.kind == "sgd" else ("betas", "eps")
+        for key in shared:
+            vals = {repr(g.get(key, d.get(key))) for g in o.param_groups}
+            if len(vals) > 1:
+                raise NotImplementedError(f"param groups with different {key!r} are not supported by the "
+                                          f"fused update (only lr and weight_decay may differ)")
         groups = [dict(lr=float(g["lr"]), weight_decay=float(g.get("weight_decay", 0.0)))
                   for g in o.param_groups]
         if self.kind == "sgd":

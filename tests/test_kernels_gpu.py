@@ -407,3 +407,12 @@ def test_gradient_norm_clipping(ctx, n, opt, max_norm):
     else:                                               # the two fp64 sums rounded to neighbouring fp32 norms
         assert np.allclose(_host(w[0]), p, rtol=1e-6, atol=1e-9)
     assert np.array_equal(_host(dg), g)                 # the gradient buffer itself is not rewritten
+
+
+def test_layout_group_must_be_provided(ctx):
+    from jabas_b200 import ops, JabasError
+    x = torch.zeros(64, device="cuda")
+    lay = ops.Layout(ctx, [(0, 32, 0), (32, 64, 2)], 64)
+    with pytest.raises(JabasError, match="param group"):
+        ops.sgd_momentum(ctx, x, [x.clone()], x.clone(), [dict(lr=0.1), dict(lr=0.1)], momentum=0.9, layout=lay)
+    lay.close()

@@ -424,3 +424,13 @@ def test_replicas_may_share_one_weight_buffer(wsm):
         assert abs(float(tr.cos_placeholder) - cos_ref) < 1e-5
     tr.change_num_models(2); tr.change_num_models(4)
     assert eng.weights[3].data_ptr() == eng.weights[0].data_ptr()
+
+
+def test_groups_may_differ_only_in_lr_and_weight_decay():
+    tr = jabas_b200.IIDPTrainer("cpu", 8, 2, 0, "sequential")
+    tr._backend = oracle_backend
+    tr.prepare_stream_parallel(_model(), torch.nn.CrossEntropyLoss())
+    groups = _groups(tr.main_model)
+    groups[0]["momentum"] = 0.5
+    with pytest.raises(NotImplementedError, match="momentum"):
+        tr.prepare_weight_sync_method(torch.optim.SGD(groups, lr=0.1, momentum=0.9))
