@@ -41,6 +41,10 @@ def subgroup_allreduce_hook(state: GradientSimilarityState, bucket) -> torch.fut
     if hasattr(bucket, "engine"):
         # one kernel: local sum of the K VSW buckets -> main bucket / T and undivided copy
         tensor = bucket.aggregate_with_half(state.total_num_decoupled_workers)
+        if bucket.deferred:                    # one GPU, or the peer-memory exchange: nothing to send here
+            fut = torch.futures.Future()
+            fut.set_result([tensor])
+            return fut
     else:
         tensor = bucket.get_tensors()[0].detach().clone()
     future_work = _allreduce_sum_fut(state.sub_group, tensor)

@@ -410,6 +410,8 @@ class GradientPath:
     def materialize(self, b: Optional[int] = None) -> None:
         """Run the aggregation of deferred buckets after all (someone needs the averaged
         gradient itself, e.g. norm clipping)."""
+        if self.collective == "peer" and self._deferred:
+            raise NotImplementedError("norm clipping is not available with the peer-memory exchange")
         for bb in sorted(self._deferred if b is None else ({b} & self._deferred)):
             self._deferred.discard(bb)
             self.aggregate(bb, divide=True, similarity=self._sim_step)
@@ -418,6 +420,13 @@ class GradientPath:
         """Optimizer update of the given buckets (None: the whole model), as one fused
         aggregate+update kernel where the aggregation was deferred."""
         nb = self.layout.num_buckets
+        if self.collective == "peer":
+            if buckets is not None or len(self._deferred) != nb:
+                raise RuntimeError("the peer-memory exchange runs once over the whole model, after every "
+                                   "bucket's hook has deferred to it (weight_sync_method='sequential')")
+            self._deferred.clear()
+            self._peer_iteration()
+            return
         if buckets is None:
             if len(self._deferred) == nb:
                 self._deferred.clear()
@@ -505,6 +514,8 @@ class GradientPath:
         """Cosine of the two half-gradients; identical on every rank (rank 0's value)."""
         if not self._sim_step:
             return None
+        if self.collective == "peer":              # finalised inside the exchange, identical on every rank
+            return self.cos
         if self.world > 1 and self.similarity_mode == "pair_exchange":
             # jabas/train/trainer.py:470-483
             if self.rank in (self.src0, self.src1):

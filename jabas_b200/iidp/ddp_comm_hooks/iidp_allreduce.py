@@ -31,6 +31,10 @@ def iidp_allreduce_hook(state: IIDPState, bucket) -> torch.futures.Future:
     if hasattr(bucket, "engine"):
         bucket.ensure_averaged(state.total_num_decoupled_workers)
         tensor = bucket.buffer(materialize=False)
+        if bucket.deferred:                    # aggregation and exchange happen in the optimizer step
+            fut = torch.futures.Future()
+            fut.set_result([tensor])
+            return fut
     else:
         tensor = bucket.buffer() if hasattr(bucket, "buffer") else bucket.get_tensors()[0]
         tensor.div_(state.total_num_decoupled_workers)

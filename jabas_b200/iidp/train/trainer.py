@@ -118,6 +118,12 @@ class IIDPTrainer(object):
         # share_weights=True: the K replicas' parameters are views of ONE flat weight buffer
         # (they are only read between updates), which removes the write-back to K-1 replicas
         share_weights = kwargs.pop("share_weights", False)
+        # collective="peer": several GPUs exchange gradients through this library's kernels over
+        # NVLink peer memory, once per iteration at step time (sequential weight sync only)
+        collective = kwargs.pop("collective", "nccl")
+        if collective == "peer" and self.weight_sync_method != "sequential":
+            raise NotImplementedError("collective='peer' works on the whole model at step time: "
+                                      "use weight_sync_method='sequential'")
         self.criterion = criterion
         K = self.num_models
         self.model_streams = [torch.cuda.Stream(self.device) if self._cuda else None for _ in range(K)]
@@ -126,7 +132,8 @@ class IIDPTrainer(object):
         self.reducer = VSWReducer(self.device, K, self.total_num_decoupled_workers, bucket_cap_mb,
                                   similarity=self._similarity_enabled(),
                                   similarity_mode=self._similarity_mode(), backend=self._backend,
-                                  first_bucket_bytes=first_bucket_bytes, share_weights=share_weights)
+                                  first_bucket_bytes=first_bucket_bytes, share_weights=share_weights,
+                                  collective=collective)
         self._sync_buffer_barrier = [None, None]
         self.local_models = [
             IndependentIdenticalDataParallel(
@@ -147,7 +154,8 @@ class IIDPTrainer(object):
         self.main_optimizer = optimizer
         self.binding = FusedBinding(optimizer, self.reducer.engine, self.main_model._params)
         # one GPU: let the update kernel aggregate the VSW gradients itself (one launch per bucket)
-        self.reducer.engine.defer_local = self.reducer.engine.can_fuse_local()
+        eng = self.reducer.engine
+        eng.defer_local = eng.can_fuse_local() or eng.collective == "peer"
         if hasattr(optimizer, "bind"):
             optimizer.bind(self.binding)
         self.local_optimizers = [optimizer] + [_ReplicaOptimizer(optimizer, self.reducer, k)

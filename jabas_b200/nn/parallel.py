@@ -32,6 +32,7 @@ class VSWGradBucket:
     def __init__(self, engine: GradientPath, index: int, is_last: bool, vsw: int, scope=None):
         self.engine, self._index, self._is_last, self.vsw = engine, index, is_last, vsw
         self._summed = self._averaged = False
+        self.deferred = False             # the hook left aggregation AND exchange to the optimizer step
         # every kernel of the path runs on ONE stream, whatever stream a future callback
         # happens to be on: the statistic accumulates bucket after bucket
         self._scope = scope if scope is not None else contextlib.nullcontext
@@ -75,7 +76,7 @@ class VSWGradBucket:
         if eng.defer_local and not self._summed:
             with self._scope():
                 eng.defer(self._index, similarity=False)
-            self._averaged = True
+            self._averaged = self.deferred = True
             return
         with self._scope():
             if self._summed:
@@ -96,7 +97,7 @@ class VSWGradBucket:
         if eng.defer_local:
             with self._scope():
                 eng.defer(self._index, similarity=True)
-            self._averaged = True
+            self._averaged = self.deferred = True
             return eng.stat
         with self._scope():
             eng.aggregate(self._index, divide=True, similarity=True)
@@ -123,13 +124,15 @@ class VSWReducer:
     def __init__(self, device, num_local_models: int, total_num_models: int,
                  bucket_cap_mb: float = DEFAULT_BUCKET_CAP_MB, similarity: bool = False,
                  similarity_mode: str = "fused", process_group=None, backend=None,
-                 first_bucket_bytes: Optional[int] = None, share_weights: bool = False):
+                 first_bucket_bytes: Optional[int] = None, share_weights: bool = False,
+                 collective: str = "nccl"):
         self.device = torch.device(device)
         self.K = int(num_local_models)
         self.T = int(total_num_models)
         self.bucket_cap_mb = bucket_cap_mb
         self.first_bucket_bytes = first_bucket_bytes
         self.share_weights = share_weights
+        self.collective = collective
         self.similarity, self.similarity_mode = similarity, similarity_mode
         self.process_group, self.backend = process_group, backend
         self.engine: Optional[GradientPath] = None
@@ -150,7 +153,8 @@ class VSWReducer:
             self.engine = GradientPath(self.layout, self.K, self.device, None,
                                        total_num_decoupled_workers=self.T, process_group=self.process_group,
                                        similarity=self.similarity, similarity_mode=self.similarity_mode,
-                                       backend=self.backend, share_weights=self.share_weights)
+                                       backend=self.backend, share_weights=self.share_weights,
+                                       collective=self.collective)
             if self.device.type == "cuda":
                 self.path_stream = torch.cuda.Stream(self.device)
         self.wrappers[k] = wrapper

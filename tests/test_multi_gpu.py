@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _rank_main(rank, world, port, mode, kind, wsm, q):
+def _rank_main(rank, world, port, mode, kind, wsm, q, collective="nccl"):
     try:
         sys.path.insert(0, HERE)
         sys.path.insert(0, os.path.dirname(HERE))
@@ -28,7 +28,7 @@ def _rank_main(rank, world, port, mode, kind, wsm, q):
         K = 2
         tr = jabas_b200.JABASTrainer(rank, 8, K, 0, wsm, dict(T.CFG), similarity_mode=mode)
         tr.prepare_stream_parallel(T._model(), torch.nn.CrossEntropyLoss().cuda(), bucket_cap_mb=0.05,
-                                   first_bucket_bytes=4096)
+                                   first_bucket_bytes=4096, collective=collective)
         groups = T._groups(tr.main_model)
         if kind == "sgd":
             opt = (ShardSGD if wsm == "overlap" else torch.optim.SGD)(groups, lr=0.1, momentum=0.9)
@@ -66,16 +66,18 @@ def _rank_main(rank, world, port, mode, kind, wsm, q):
         q.put((rank, "error", traceback.format_exc(), 0))
 
 
-@pytest.mark.parametrize("mode,kind,wsm", [("fused", "sgd", "overlap"), ("pair_exchange", "sgd", "sequential"),
-                                           ("fused", "adamw", "overlap"), ("fused", "adamw", "sequential")])
-def test_two_nccl_ranks_match_reference_path(mode, kind, wsm):
+@pytest.mark.parametrize("mode,kind,wsm,collective", [
+    ("fused", "sgd", "overlap", "nccl"), ("pair_exchange", "sgd", "sequential", "nccl"),
+    ("fused", "adamw", "overlap", "nccl"), ("fused", "adamw", "sequential", "nccl"),
+    ("fused", "sgd", "sequential", "peer"), ("fused", "adamw", "sequential", "peer")])
+def test_two_nccl_ranks_match_reference_path(mode, kind, wsm, collective):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + (os.getpid() + hash((mode, kind, wsm))) % 400
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, mode, kind, wsm, q)) for r in range(2)]
+    port = 29500 + (os.getpid() + hash((mode, kind, wsm, collective))) % 400
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, mode, kind, wsm, q, collective)) for r in range(2)]
     for p in procs:
         p.start()
     res = [q.get(timeout=300) for _ in procs]
