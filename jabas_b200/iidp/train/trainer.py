@@ -76,6 +76,9 @@ class IIDPTrainer(object):
         self.reducer: Optional[VSWReducer] = None
         self.binding: Optional[FusedBinding] = None
         self._backend = None            # tests on CPU inject an oracle-backed double here
+        #: issue the K forward/backward passes from K Python threads (as the reference does,
+        #: jabas/train/trainer.py:584-588) instead of one after the other from the calling thread
+        self.threaded_compute = False
 
     # -- helpers -----------------------------------------------------------------------
     def trainer_print(self, message, status="info"):
@@ -310,14 +313,38 @@ class IIDPTrainer(object):
         if sync:
             self.reducer.prepare_for_backward(self._is_similarity_step())
         cur = torch.cuda.current_stream(self.device) if self._cuda else None
-        for k in range(self.num_models):
-            self.reducer.install_grad_views(k)
+
+        def run(k):
             if self._cuda:
-                self.model_streams[k].wait_stream(cur)
+                torch.cuda.set_device(self.device)
                 with torch.cuda.stream(self.model_streams[k]):
                     self._forward_backward(k, scatter_inputs[k], scatter_targets[k])
             else:
                 self._forward_backward(k, scatter_inputs[k], scatter_targets[k])
+
+        for k in range(self.num_models):
+            self.reducer.install_grad_views(k)
+            if self._cuda:
+                self.model_streams[k].wait_stream(cur)
+        if self.threaded_compute and self.num_models > 1:
+            import threading
+            errors = []
+
+            def guarded(k):
+                try:
+                    run(k)
+                except BaseException as e:     # re-raised in the calling thread
+                    errors.append(e)
+            threads = [threading.Thread(target=guarded, args=(k,)) for k in range(self.num_models)]
+            for t in threads:
+                t.start()
+            for t in threads:
+                t.join()
+            if errors:
+                raise errors[0]
+        else:
+            for k in range(self.num_models):
+                run(k)
 
     def _forward_backward(self, k, inputs, targets):
         out = self.local_models[k](inputs)

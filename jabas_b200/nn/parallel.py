@@ -140,6 +140,7 @@ class VSWReducer:
         self.wrappers: List[Optional["IndependentIdenticalDataParallel"]] = [None] * self.K
         self.path_stream: Optional[torch.cuda.Stream] = None
         self._lock = threading.Lock()
+        self._fire_lock = threading.Lock()    # hooks fire one bucket at a time, in bucket order
         self.futures: List[torch.futures.Future] = []
         self.require_sync = True
         self._reset_counters()
@@ -251,13 +252,14 @@ class VSWReducer:
     def _fire_ready_buckets(self) -> None:
         """Fire comm hooks in bucket order (every rank must issue its collectives in the
         same order), for every bucket that is complete on all K VSWs."""
-        while True:
-            with self._lock:
-                b = self._next_bucket
-                if b >= self.layout.num_buckets or self._vsw_done[b] < self.K:
-                    return
-                self._next_bucket += 1
-            self._fire(b)
+        with self._fire_lock:                 # K backward passes may run in K threads
+            while True:
+                with self._lock:
+                    b = self._next_bucket
+                    if b >= self.layout.num_buckets or self._vsw_done[b] < self.K:
+                        return
+                    self._next_bucket += 1
+                self._fire(b)
 
     def _fire(self, b: int) -> None:
         last = b == self.layout.num_buckets - 1

@@ -48,10 +48,12 @@ def _capture_vsw_gradients(tr):
     return captured
 
 
-@pytest.mark.parametrize("wsm", ["sequential", "overlap"])
-@pytest.mark.parametrize("kind", ["sgd", "adamw"])
-@pytest.mark.parametrize("K", [2, 4])
-def test_trainer_on_gpu_matches_reference_path(wsm, kind, K):
+@pytest.mark.parametrize("wsm,kind,K,threaded", [
+    ("sequential", "sgd", 2, False), ("overlap", "sgd", 2, False), ("sequential", "adamw", 2, False),
+    ("overlap", "adamw", 2, False), ("sequential", "sgd", 4, False), ("overlap", "sgd", 4, False),
+    ("sequential", "adamw", 4, False), ("overlap", "adamw", 4, False),
+    ("overlap", "sgd", 4, True), ("sequential", "adamw", 4, True)])
+def test_trainer_on_gpu_matches_reference_path(wsm, kind, K, threaded):
     import jabas_b200
     from jabas_b200.iidp.optim import ShardAdamW, ShardSGD
     from oracle.reference_path import ReferencePath
@@ -66,6 +68,7 @@ def test_trainer_on_gpu_matches_reference_path(wsm, kind, K):
         opt = (ShardAdamW if wsm == "overlap" else torch.optim.AdamW)(groups, lr=1e-2)
     tr.prepare_weight_sync_method(opt, None, _groups)
     tr.set_model_train()
+    tr.threaded_compute = threaded                      # K forward/backward passes from K threads
     ref = ReferencePath(tr.reducer.layout, K, _opt_dict(kind), total_num_decoupled_workers=K, arith="c")
     for k in range(K):
         ref.weights[k].copy_(tr.reducer.engine.weights[k].cpu())

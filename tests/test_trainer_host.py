@@ -434,3 +434,19 @@ def test_groups_may_differ_only_in_lr_and_weight_decay():
     groups[0]["momentum"] = 0.5
     with pytest.raises(NotImplementedError, match="momentum"):
         tr.prepare_weight_sync_method(torch.optim.SGD(groups, lr=0.1, momentum=0.9))
+
+
+@pytest.mark.parametrize("wsm", ["sequential", "overlap"])
+def test_threaded_compute_gives_the_same_result(wsm):
+    """K forward/backward passes from K threads: hooks still fire one bucket at a time, in
+    bucket order, and the result equals the single-threaded one bit for bit."""
+    K = 4
+    a, b = _make_trainer(K, wsm, "sgd"), _make_trainer(K, wsm, "sgd")
+    b.threaded_compute = True
+    g = torch.Generator().manual_seed(31)
+    for it in range(4):
+        x, y = torch.randn(8 * K, 20, generator=g), torch.randint(0, 10, (8 * K,), generator=g)
+        a.compute((x, y)); a.step()
+        b.compute((x, y)); b.step()
+        assert torch.equal(a.reducer.engine.weights[0], b.reducer.engine.weights[K - 1]), it
+        assert float(a.cos_placeholder) == float(b.cos_placeholder)
