@@ -384,6 +384,13 @@ def run_ours(args):
             eager_fn()
         barrier()
     events, eng.profile_events = eng.profile_events, None
+    # a short run (few steps) ends before the 50 ms clock sampler has seen the load: keep the
+    # same step running, untimed, until half a second of it has passed (same count on all ranks)
+    extra = int(500.0 / max(ms_step, 1e-3)) - args.steps * (2 if use_graph else 1)
+    if extra > 0:
+        for _ in range(extra):
+            step_fn()
+        barrier()
     clocks = sampler.stop() if rank == 0 else None
     cos = float(eng.cos)
 
