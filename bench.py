@@ -63,6 +63,9 @@ def parse_args():
                     help="yes: walk the DDP buckets as the comm hooks do; no / auto: the whole flat model per launch")
     ap.add_argument("--share-weights", action="store_true",
                     help="the K replicas alias one weight buffer (no write-back to K-1 replicas); not the default")
+    ap.add_argument("--staging", default="register", choices=["register", "bulk"],
+                    help="how the update kernels fetch their tiles: per-thread 128-bit loads (default) or "
+                         "TMA bulk copies into a shared-memory ring")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch every kernel / collective from Python instead of replaying one CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
@@ -107,6 +110,7 @@ def config_dict(args, layout, K, lbs, opt, desc, world):
         "overlap": not args.no_overlap,
         "cuda_graph": (not args.no_graph) and args.impl == "ours",
         "replica_weights": "one shared buffer" if getattr(args, "share_weights", False) else "K separate buffers",
+        "staging": getattr(args, "staging", "register"),
         "collective": ("peer-memory kernels over NVLink" if args.collective == "peer" else "NCCL allreduce")
                       if world > 1 else "none",
         "launch_granularity": "bucket" if args.per_bucket == "yes"
@@ -318,7 +322,7 @@ def run_ours(args):
         return GradientPath(layout, K, dev, spec, total_num_decoupled_workers=world * K,
                             sub_group=sub_group, pair_group=pair_group, similarity=similarity,
                             similarity_mode=args.similarity_mode, collective=coll,
-                            share_weights=args.share_weights)
+                            share_weights=args.share_weights, staging=args.staging)
     try:
         eng = make_engine(collective)
     except Exception as e:
@@ -393,6 +397,8 @@ def run_ours(args):
         barrier()
     clocks = sampler.stop() if rank == 0 else None
     cos = float(eng.cos)
+    if args.staging == "bulk" and eng.ctx.staging_timeouts() != 0:
+        raise RuntimeError("bulk staging: a wait for a copy ran out; the timed steps are incomplete")
 
     per_kernel = {}
     for kind, b, a, z in events:

@@ -109,6 +109,23 @@ JABAS_API const char* jabas_last_error(void);
 JABAS_API int jabas_ctx_create(int device, jabas_ctx_t** ctx);
 JABAS_API int jabas_ctx_destroy(jabas_ctx_t* ctx);
 
+/* How the update kernels (jabas_sgd_momentum_f32, jabas_adam_f32 and their jabas_vsw_* forms)
+ * bring a tile of their input streams on chip.  No reference counterpart: the reference's
+ * updates are per-tensor PyTorch ops (examples/resnet50/main.py:351-359).
+ *  - JABAS_STAGING_REGISTER (default): per-thread 128-bit loads straight into registers;
+ *  - JABAS_STAGING_BULK: TMA bulk copies (cp.async.bulk) of 4 KB per stream into a multi-stage
+ *    shared-memory ring, completion on mbarriers.  Results are bit-identical (the statistic to
+ *    fp64 summation order).  Launches whose gradient comes from peer shards keep the register
+ *    form.  Every wait on a copy is bounded; a wait that runs out ends the CTA's loop early and
+ *    is counted (the launch's outputs are then incomplete).
+ * jabas_ctx_set_staging allocates the 4-byte device counter the first time BULK is chosen.
+ * jabas_ctx_staging_timeouts synchronises the device and reads the counter (0 = every launch
+ * so far completed all of its copies). */
+#define JABAS_STAGING_REGISTER 0
+#define JABAS_STAGING_BULK     1
+JABAS_API int jabas_ctx_set_staging(jabas_ctx_t* ctx, int mode);
+JABAS_API int jabas_ctx_staging_timeouts(jabas_ctx_t* ctx, uint32_t* count);
+
 /* Uploads a segment table covering [0, total) of a flat parameter buffer.  Segments
  * must be sorted, non-empty and contiguous (seg[i].end == seg[i+1].begin).
  * Synchronous (one small cudaMemcpy); call at set-up, not per iteration. */

@@ -22,6 +22,7 @@ EXPORTS = (
     "jabas_replicate_f32", "jabas_dot_norms_static_f32", "jabas_vsw_sgd_momentum_f32",
     "jabas_vsw_adam_f32", "jabas_sumsq_f32", "jabas_clip_coef", "jabas_dynhp_create",
     "jabas_dynhp_destroy", "jabas_dynhp_push_sgd", "jabas_dynhp_push_adam", "jabas_peer_reduce_f32", "jabas_vsw_aggregate_scatter_f32",
+    "jabas_ctx_set_staging", "jabas_ctx_staging_timeouts",
 )
 
 
@@ -79,6 +80,8 @@ def load() -> ctypes.CDLL:
     lib.jabas_last_error.restype = ctypes.c_char_p
     lib.jabas_ctx_create.argtypes = [i32, pvp]
     lib.jabas_ctx_destroy.argtypes = [vp]
+    lib.jabas_ctx_set_staging.argtypes = [vp, i32]
+    lib.jabas_ctx_staging_timeouts.argtypes = [vp, ctypes.POINTER(ctypes.c_uint32)]
     lib.jabas_layout_create.argtypes = [vp, ctypes.POINTER(Seg), i32, u64, pvp]
     lib.jabas_layout_destroy.argtypes = [vp]
     lib.jabas_vsw_aggregate_f32.argtypes = [vp, pvp, i32, vp, vp, u64, f32, f32, vp, vp]

@@ -65,6 +65,59 @@ __device__ __forceinline__ void st4(float* p, float4 v)
     *reinterpret_cast<float4*>(p) = v;
 }
 
+// ---- bulk-copy (TMA, untiled) staging of tiles into shared memory ------------------------
+// One elected thread issues `cp.async.bulk` for every input stream of a tile; the copies
+// complete on an mbarrier of the stage, which the CTA's threads poll with a bounded number
+// of `try_wait`s.  Source, destination and byte count are multiples of 16 by construction
+// (16-byte aligned buffers, tiles of 4 KB, tails in whole 4-vectors).
+constexpr int kMaxStages = 4;
+constexpr int kStageTileVecs = kThreads;                 // one 4-vector per thread and stream
+constexpr unsigned kStageTileBytes = kStageTileVecs * 16; // 4 KB per stream and stage
+constexpr int kStageBudgetBytes = 72 * 1024;             // dynamic shared memory asked per CTA
+constexpr int kWaitSpins = 1 << 22;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p)
+{
+    return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(unsigned long long* b, unsigned count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* b, unsigned bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* b, unsigned parity)
+{
+    unsigned ok;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(ok)
+                 : "r"(smem_u32(b)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+// false: the copies of this stage did not land within the spin limit
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* b, unsigned parity)
+{
+    for (int spins = 0; spins < kWaitSpins; ++spins)
+        if (mbar_try_wait(b, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void bulk_load(void* dst_smem, const void* src, unsigned bytes, unsigned long long* b)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(b))
+                 : "memory");
+}
+// orders this thread's earlier generic-proxy accesses to shared memory before later async-proxy ones
+__device__ __forceinline__ void fence_proxy_async_smem()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 struct Acc3 {
     double d, a, b;
 };
@@ -313,6 +366,10 @@ struct UpdArgs {
     int K;
     float half_divisor;
     const UpdHp* dyn;         // nullable: hyper-parameters live in device memory (CUDA-graph replay)
+    // bulk-staged form only: pipeline depth, stream slots per stage (sized for the launch's
+    // largest stream count) and the device counter of waits that ran out
+    int stages, stage_slots;
+    unsigned int* timeouts;
     UpdHp hp;                 // ... otherwise they travel in the argument block
 };
 
@@ -456,40 +513,108 @@ __device__ __forceinline__ void load_hp(const UpdArgs& a, UpdHp& H)
 // 3 CTAs/SM (<= 85 registers) is 1 % ahead.
 __host__ __device__ constexpr int upd_min_ctas(int KAGG) { return KAGG <= 4 ? 1 : 3; }
 
-template <int OPT, bool STAT, int U, int KAGG>
-__global__ void __launch_bounds__(kThreads, upd_min_ctas(KAGG)) upd_vec_kernel(const UpdArgs a)
+// BULK: the inputs of a tile reach the registers through shared memory, staged by bulk
+// copies (one 4 KB copy per stream and stage, `stages` tiles in flight per CTA) instead of
+// per-thread 128-bit loads; U is 1.  Everything after the loads is the same code.
+template <int OPT, bool STAT, int U, int KAGG, bool BULK>
+__global__ void __launch_bounds__(kThreads, BULK ? 3 : upd_min_ctas(KAGG)) upd_vec_kernel(const UpdArgs a)
 {
+    static_assert(!BULK || U == 1, "the bulk-staged form handles one 4-vector per thread and tile");
     constexpr int KX = KAGG > 0 ? KAGG : 1;
     const float gscale = a.grad_scale ? __ldg(a.grad_scale) : 1.0f;
     const bool clip = gscale < 1.0f;
     const unsigned long long nvec = a.n >> 2;
     const unsigned long long tile = (unsigned long long)kThreads * U;
     __shared__ UpdHp H;
+    extern __shared__ __align__(128) unsigned char stage_raw[];
+    __shared__ unsigned long long stage_full[kMaxStages];
+    __shared__ volatile int stage_abort;
+    if (BULK && threadIdx.x == 0) {
+        for (int s = 0; s < kMaxStages; ++s) mbar_init(&stage_full[s], 1);
+        stage_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     load_hp(a, H);
     const bool use_m = OPT == OPT_ADAM || (H.flags & F_MOMENTUM);
     const bool load_m = OPT == OPT_ADAM || ((H.flags & F_MOMENTUM) && !(H.flags & F_FIRST));
+    // slots of a stage: gradients (KX), p, then m / v / half as far as this launch reads them
+    const int slot_m = KX + 1;
+    const int slot_v = slot_m + (load_m ? 1 : 0);
+    const int slot_h = slot_v + (OPT == OPT_ADAM ? 1 : 0);
+    const unsigned long long my_first = (unsigned long long)blockIdx.x * tile;
+    const unsigned long long stride = (unsigned long long)gridDim.x * tile;
+    // thread 0 only: start the copies of the tile that begins at 4-vector t into stage s
+    auto stage_issue = [&](unsigned long long t, int s) {
+        const unsigned long long left = nvec - t;
+        const unsigned bytes = left >= (unsigned long long)kStageTileVecs ? kStageTileBytes : (unsigned)left * 16u;
+        const int nslot = slot_h + ((STAT && KAGG == 0) ? 1 : 0);
+        unsigned char* sb = stage_raw + (size_t)s * a.stage_slots * kStageTileBytes;
+        mbar_expect_tx(&stage_full[s], bytes * (unsigned)nslot);
+        if (KAGG > 0) {
+#pragma unroll
+            for (int k = 0; k < KX; ++k) bulk_load(sb + k * kStageTileBytes, a.gk[k] + 4 * t, bytes, &stage_full[s]);
+        } else {
+            bulk_load(sb, a.g + 4 * t, bytes, &stage_full[s]);
+        }
+        bulk_load(sb + KX * kStageTileBytes, a.w[0] + 4 * t, bytes, &stage_full[s]);
+        if (load_m) bulk_load(sb + slot_m * kStageTileBytes, a.m + 4 * t, bytes, &stage_full[s]);
+        if (OPT == OPT_ADAM) bulk_load(sb + slot_v * kStageTileBytes, a.v + 4 * t, bytes, &stage_full[s]);
+        if (STAT && KAGG == 0) bulk_load(sb + slot_h * kStageTileBytes, a.half + 4 * t, bytes, &stage_full[s]);
+    };
+    if (BULK && threadIdx.x == 0) {
+        unsigned long long t = my_first;
+        for (int s = 0; s < a.stages && t < nvec; ++s, t += stride) stage_issue(t, s);
+    }
     Acc3 acc = {0.0, 0.0, 0.0};
-    for (unsigned long long t0 = (unsigned long long)blockIdx.x * tile; t0 < nvec;
-         t0 += (unsigned long long)gridDim.x * tile) {
+    int cur_stage = 0;            // stage and mbarrier phase parity of the tile being consumed
+    unsigned cur_parity = 0;
+    unsigned long long t0 = my_first;
+    for (; t0 < nvec; t0 += stride) {
         const bool full = t0 + tile <= nvec;
         float4 g[U], p[U], m[U], v[U], hs[U], xk[U][KX];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const unsigned long long x = t0 + (unsigned long long)u * kThreads + threadIdx.x;
-            m[u] = v[u] = hs[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (full || x < nvec) {
+        if (BULK) {
+            const int s = cur_stage;
+            if (!mbar_wait_bounded(&stage_full[s], cur_parity)) stage_abort = 1;
+            const float4* sb = reinterpret_cast<const float4*>(stage_raw + (size_t)s * a.stage_slots * kStageTileBytes);
+            m[0] = v[0] = hs[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (full || t0 + threadIdx.x < nvec) {
                 if (KAGG > 0) {
 #pragma unroll
-                    for (int k = 0; k < KX; ++k) xk[u][k] = ld4(a.gk[k] + 4 * x);
-                } else if (a.npeer > 0) {
-                    g[u] = ld4(peer_base(a, a.base + 4 * x) + a.base + 4 * x);
+                    for (int k = 0; k < KX; ++k) xk[0][k] = sb[k * kStageTileVecs + threadIdx.x];
                 } else {
-                    g[u] = ld4(a.g + 4 * x);
+                    g[0] = sb[threadIdx.x];
                 }
-                p[u] = ld4(a.w[0] + 4 * x);
-                if (load_m) m[u] = ld4(a.m + 4 * x);
-                if (OPT == OPT_ADAM) v[u] = ld4(a.v + 4 * x);
-                if (STAT && KAGG == 0) hs[u] = ld4(a.half + 4 * x);
+                p[0] = sb[KX * kStageTileVecs + threadIdx.x];
+                if (load_m) m[0] = sb[slot_m * kStageTileVecs + threadIdx.x];
+                if (OPT == OPT_ADAM) v[0] = sb[slot_v * kStageTileVecs + threadIdx.x];
+                if (STAT && KAGG == 0) hs[0] = sb[slot_h * kStageTileVecs + threadIdx.x];
+            }
+            __syncthreads();                       // the stage has been read by every thread
+            if (stage_abort) break;                // set before the barrier: the same for all threads
+            if (threadIdx.x == 0) {
+                const unsigned long long nt = t0 + (unsigned long long)a.stages * stride;
+                if (nt < nvec) { fence_proxy_async_smem(); stage_issue(nt, s); }
+            }
+            if (++cur_stage == a.stages) { cur_stage = 0; cur_parity ^= 1u; }
+        } else {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const unsigned long long x = t0 + (unsigned long long)u * kThreads + threadIdx.x;
+                m[u] = v[u] = hs[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (full || x < nvec) {
+                    if (KAGG > 0) {
+#pragma unroll
+                        for (int k = 0; k < KX; ++k) xk[u][k] = ld4(a.gk[k] + 4 * x);
+                    } else if (a.npeer > 0) {
+                        g[u] = ld4(peer_base(a, a.base + 4 * x) + a.base + 4 * x);
+                    } else {
+                        g[u] = ld4(a.g + 4 * x);
+                    }
+                    p[u] = ld4(a.w[0] + 4 * x);
+                    if (load_m) m[u] = ld4(a.m + 4 * x);
+                    if (OPT == OPT_ADAM) v[u] = ld4(a.v + 4 * x);
+                    if (STAT && KAGG == 0) hs[u] = ld4(a.half + 4 * x);
+                }
             }
         }
         if (KAGG > 0) {
@@ -550,6 +675,17 @@ __global__ void __launch_bounds__(kThreads, upd_min_ctas(KAGG)) upd_vec_kernel(c
             if (use_m) st4(a.m + 4 * x, m[u]);
             if (OPT == OPT_ADAM) st4(a.v + 4 * x, v[u]);
         }
+    }
+    if (BULK && stage_abort) {
+        // a wait ran out: report it, and give the copies still in flight one more bounded
+        // wait each so that none lands in shared memory after the CTA has gone
+        // (t0, cur_stage, cur_parity still describe the tile whose wait failed)
+        unsigned long long t = t0;
+        for (int j = 0; j < a.stages && t < nvec; ++j, t += stride) {
+            (void)mbar_wait_bounded(&stage_full[cur_stage], cur_parity);
+            if (++cur_stage == a.stages) { cur_stage = 0; cur_parity ^= 1u; }
+        }
+        if (threadIdx.x == 0 && a.timeouts) atomicAdd(a.timeouts, 1u);
     }
     const unsigned int rem = (unsigned int)(a.n & 3ull);
     if (blockIdx.x == 0 && threadIdx.x < rem) {
@@ -758,6 +894,8 @@ struct jabas_ctx {
     std::mutex mu;
     std::unordered_map<void*, StatWs> ws;   // one reduction workspace per stream
     std::unordered_map<const void*, int> occ;
+    int staging = JABAS_STAGING_REGISTER;   // how the update kernels fetch their tiles
+    unsigned int* d_timeouts = nullptr;     // bulk staging: waits that ran out (device counter)
 };
 
 struct jabas_layout {
@@ -797,8 +935,10 @@ int ctx_bind(jabas_ctx_t* ctx)
 // Resident CTAs per SM of a kernel, cached per context.
 template <typename KernelT>
 int grid_for(jabas_ctx_t* ctx, KernelT kernel, unsigned long long work_items, unsigned long long per_cta,
-             int* grid)
+             int* grid, size_t dyn_smem = 0)
 {
+    // a kernel is always launched with the same amount of dynamic shared memory or less than
+    // the amount it was first seen with, so one cache entry per kernel is enough
     int per_sm = 0;
     {
         std::lock_guard<std::mutex> lk(ctx->mu);
@@ -806,7 +946,10 @@ int grid_for(jabas_ctx_t* ctx, KernelT kernel, unsigned long long work_items, un
         if (it != ctx->occ.end()) per_sm = it->second;
     }
     if (per_sm == 0) {
-        JB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0));
+        if (dyn_smem > 0)
+            JB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBudgetBytes));
+        JB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads,
+                                                              dyn_smem > 0 ? (size_t)kStageBudgetBytes : 0));
         if (per_sm < 1) per_sm = 1;
         if (per_sm > kMaxCtasPerSm) per_sm = kMaxCtasPerSm;
         std::lock_guard<std::mutex> lk(ctx->mu);
@@ -864,27 +1007,49 @@ int agg_dispatch(jabas_ctx_t* ctx, const AggArgs& a, cudaStream_t st)
 
 constexpr int kMaxFusedVsw = 8;     // the fused aggregate+update form is instantiated for K <= 8
 
+// Stages of the bulk-staged form: as many tiles in flight as fit the shared-memory budget.
+inline int stage_count(int slots)
+{
+    int s = kStageBudgetBytes / (slots * (int)kStageTileBytes);
+    return s < 1 ? 1 : (s > kMaxStages ? kMaxStages : s);
+}
+
 template <int OPT, int KAGG>
-int upd_launch_vec(jabas_ctx_t* ctx, const UpdArgs& a, cudaStream_t st)
+int upd_launch_vec(jabas_ctx_t* ctx, UpdArgs& a, cudaStream_t st)
 {
     if (a.kagg != KAGG) {
         if constexpr (KAGG < kMaxFusedVsw) return upd_launch_vec<OPT, KAGG + 1>(ctx, a, st);
         return fail(JABAS_EINVAL, "fused aggregate+update supports at most 8 VSWs");
     }
-    constexpr int U = KAGG > 4 ? 1 : 2;
     int grid = 0, rc;
+    if (ctx->staging == JABAS_STAGING_BULK && a.npeer == 0) {
+        // slots for the launch's largest stream count: gradients, p, m [, v] [, half]
+        a.stage_slots = (KAGG > 0 ? KAGG : 1) + 2 + (OPT == OPT_ADAM ? 1 : 0) + ((a.stat && KAGG == 0) ? 1 : 0);
+        a.stages = stage_count(a.stage_slots);
+        a.timeouts = ctx->d_timeouts;
+        const size_t smem = (size_t)a.stages * a.stage_slots * kStageTileBytes;
+        if (a.stat) {
+            if ((rc = grid_for(ctx, upd_vec_kernel<OPT, true, 1, KAGG, true>, a.n >> 2, kThreads, &grid, smem))) return rc;
+            upd_vec_kernel<OPT, true, 1, KAGG, true><<<grid, kThreads, smem, st>>>(a);
+        } else {
+            if ((rc = grid_for(ctx, upd_vec_kernel<OPT, false, 1, KAGG, true>, a.n >> 2, kThreads, &grid, smem))) return rc;
+            upd_vec_kernel<OPT, false, 1, KAGG, true><<<grid, kThreads, smem, st>>>(a);
+        }
+        return JABAS_OK;
+    }
+    constexpr int U = KAGG > 4 ? 1 : 2;
     if (a.stat) {
-        if ((rc = grid_for(ctx, upd_vec_kernel<OPT, true, U, KAGG>, a.n >> 2, (unsigned long long)kThreads * U, &grid))) return rc;
-        upd_vec_kernel<OPT, true, U, KAGG><<<grid, kThreads, 0, st>>>(a);
+        if ((rc = grid_for(ctx, upd_vec_kernel<OPT, true, U, KAGG, false>, a.n >> 2, (unsigned long long)kThreads * U, &grid))) return rc;
+        upd_vec_kernel<OPT, true, U, KAGG, false><<<grid, kThreads, 0, st>>>(a);
     } else {
-        if ((rc = grid_for(ctx, upd_vec_kernel<OPT, false, U, KAGG>, a.n >> 2, (unsigned long long)kThreads * U, &grid))) return rc;
-        upd_vec_kernel<OPT, false, U, KAGG><<<grid, kThreads, 0, st>>>(a);
+        if ((rc = grid_for(ctx, upd_vec_kernel<OPT, false, U, KAGG, false>, a.n >> 2, (unsigned long long)kThreads * U, &grid))) return rc;
+        upd_vec_kernel<OPT, false, U, KAGG, false><<<grid, kThreads, 0, st>>>(a);
     }
     return JABAS_OK;
 }
 
 template <int OPT>
-int upd_launch(jabas_ctx_t* ctx, const UpdArgs& a, bool vec, cudaStream_t st)
+int upd_launch(jabas_ctx_t* ctx, UpdArgs& a, bool vec, cudaStream_t st)
 {
     int grid = 0, rc;
     if (vec) {
@@ -997,10 +1162,42 @@ int jabas_ctx_destroy(jabas_ctx_t* ctx)
 {
     if (!ctx) return JABAS_OK;
     int rc = ctx_bind(ctx);
-    if (rc == JABAS_OK)
+    if (rc == JABAS_OK) {
         for (auto& kv : ctx->ws) cudaFree(kv.second.counter);
+        if (ctx->d_timeouts) cudaFree(ctx->d_timeouts);
+    }
     delete ctx;
     return rc;
+}
+
+int jabas_ctx_set_staging(jabas_ctx_t* ctx, int mode)
+{
+    int rc = ctx_bind(ctx);
+    if (rc) return rc;
+    if (mode != JABAS_STAGING_REGISTER && mode != JABAS_STAGING_BULK)
+        return fail(JABAS_EINVAL, "staging mode must be JABAS_STAGING_REGISTER or JABAS_STAGING_BULK");
+    if (mode == JABAS_STAGING_BULK && !ctx->d_timeouts) {
+        unsigned int* d = nullptr;
+        if (cudaMalloc(&d, sizeof(unsigned int)) != cudaSuccess) return fail(JABAS_ENOMEM, "out of device memory");
+        cudaError_t e = cudaMemset(d, 0, sizeof(unsigned int));
+        if (e != cudaSuccess) { cudaFree(d); return fail(JABAS_ECUDA, cudaGetErrorString(e)); }
+        ctx->d_timeouts = d;
+    }
+    ctx->staging = mode;
+    return JABAS_OK;
+}
+
+int jabas_ctx_staging_timeouts(jabas_ctx_t* ctx, uint32_t* count)
+{
+    int rc = ctx_bind(ctx);
+    if (rc) return rc;
+    if (!count) return fail(JABAS_EINVAL, "count is null");
+    *count = 0;
+    if (!ctx->d_timeouts) return JABAS_OK;
+    unsigned int h = 0;
+    JB_CUDA(cudaMemcpy(&h, ctx->d_timeouts, sizeof(h), cudaMemcpyDeviceToHost));
+    *count = h;
+    return JABAS_OK;
 }
 
 int jabas_layout_create(jabas_ctx_t* ctx, const jabas_seg_t* segs, int nseg, uint64_t total,

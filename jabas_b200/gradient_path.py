@@ -60,7 +60,7 @@ class GradientPath:
                  total_num_decoupled_workers: int, process_group=None, sub_group=None,
                  pair_group=None, first_subgroup_src_rank: int = 0, second_subgroup_src_rank: int = 1,
                  similarity: bool = True, similarity_mode: str = "fused", backend=None,
-                 collective: str = "nccl", share_weights: bool = False):
+                 collective: str = "nccl", share_weights: bool = False, staging: str = "register"):
         if backend is None:
             from . import ops as backend          # the CUDA library; raises without a GPU
         self.ops = backend
@@ -89,6 +89,8 @@ class GradientPath:
                 assert self.K >= 2 and self.K % 2 == 0, \
                     "on one GPU the two halves are the even and the odd VSWs: K must be even"
         self.ctx = self.ops.Context(self.device)
+        if staging != "register":                 # "bulk": TMA bulk copies into shared memory
+            self.ctx.set_staging(staging)
         self.dev_layout = None
         n = layout.total
         f32 = dict(dtype=torch.float32, device=self.device)

@@ -86,6 +86,24 @@ class Context:
         h = ctypes.c_void_p()
         _lib.check(self._lib.jabas_ctx_create(self.device.index, ctypes.byref(h)))
         self._h = h
+        self.staging = "register"
+
+    STAGING = {"register": 0, "bulk": 1}
+
+    def set_staging(self, mode: str) -> None:
+        """How the update kernels fetch their tiles: ``"register"`` (per-thread 128-bit
+        loads, default) or ``"bulk"`` (TMA bulk copies into a shared-memory ring)."""
+        if mode not in self.STAGING:
+            raise ValueError("staging must be 'register' or 'bulk'")
+        _lib.check(self._lib.jabas_ctx_set_staging(self._h, self.STAGING[mode]))
+        self.staging = mode
+
+    def staging_timeouts(self) -> int:
+        """Bulk staging: number of CTAs whose bounded wait for a copy ran out since the
+        context was created (synchronises the device; 0 when all is well)."""
+        c = ctypes.c_uint32(0)
+        _lib.check(self._lib.jabas_ctx_staging_timeouts(self._h, ctypes.byref(c)))
+        return int(c.value)
 
     def close(self) -> None:
         if getattr(self, "_h", None):

@@ -8,7 +8,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _engine(kind, K, per_bucket):
+def _engine(kind, K, per_bucket, staging="register"):
     from jabas_b200.gradient_path import GradientPath, OptimizerSpec
     from jabas_b200.layout import build_layout
     shapes = [(64, 3, 7, 7), (64,), (64,), (256, 64, 3, 3), (1000, 257), (1000,)]
@@ -18,7 +18,8 @@ def _engine(kind, K, per_bucket):
         spec = OptimizerSpec("sgd", [dict(lr=0.1, weight_decay=0.0), dict(lr=0.1, weight_decay=1e-4)], momentum=0.9)
     else:
         spec = OptimizerSpec("adamw", [dict(lr=1e-3, weight_decay=0.0), dict(lr=1e-3, weight_decay=0.05)])
-    eng = GradientPath(layout, K, torch.device("cuda", 0), spec, total_num_decoupled_workers=K)
+    eng = GradientPath(layout, K, torch.device("cuda", 0), spec, total_num_decoupled_workers=K,
+                       staging=staging)
     g = torch.Generator(device="cuda").manual_seed(3)
     eng.weights[0].normal_(generator=g)
     for b, e in zip([0] + [x[1] for x in layout.buckets], [x[0] for x in layout.buckets] + [layout.total]):
@@ -36,9 +37,10 @@ def _fill_grads(eng, it):
 
 @pytest.mark.parametrize("kind", ["sgd", "adamw"])
 @pytest.mark.parametrize("per_bucket", [False, True])
-def test_graph_replay_is_bit_identical_to_eager(kind, per_bucket):
+@pytest.mark.parametrize("staging", ["register", "bulk"])
+def test_graph_replay_is_bit_identical_to_eager(kind, per_bucket, staging):
     eager, how = _engine(kind, 4, per_bucket)
-    graphed, _ = _engine(kind, 4, per_bucket)
+    graphed, _ = _engine(kind, 4, per_bucket, staging)
     lrs = [0.1, 0.1, 0.05, 0.2, 0.01]
     cos_e = []
     for it, lr in enumerate(lrs):
@@ -72,6 +74,10 @@ def test_graph_replay_is_bit_identical_to_eager(kind, per_bucket):
     for k in range(4):
         assert torch.equal(graphed.weights[k], eager.weights[0]), k
     assert torch.equal(graphed.m, eager.m)
-    assert cos_g == cos_e[2:]
+    if staging == "register":
+        assert cos_g == cos_e[2:]
+    else:                                    # other tile-to-thread map: fp64 sums in another order
+        assert np.allclose(cos_g, cos_e[2:], rtol=0, atol=1e-6)
+        assert graphed.ctx.staging_timeouts() == 0
     assert graphed.launches_per_replay >= 2
     eager.close(); graphed.close()

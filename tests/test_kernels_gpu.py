@@ -18,11 +18,15 @@ pytestmark = pytest.mark.gpu
 SIZES = [1, 3, 4, 5, 1023, 1025, 2 ** 20 + 1, 3 * 2 ** 20 + 2]
 
 
-@pytest.fixture(scope="module")
-def ctx():
+@pytest.fixture(scope="module", params=["register", "bulk"])
+def ctx(request):
+    """Every test of this module runs twice: with the update kernels loading their tiles
+    straight into registers, and through the bulk-copy (TMA) shared-memory ring."""
     from jabas_b200 import ops
     c = ops.Context(0)
+    c.set_staging(request.param)
     yield c
+    assert c.staging_timeouts() == 0          # no bounded wait for a bulk copy ever ran out
     c.close()
 
 
