@@ -508,10 +508,12 @@ __device__ __forceinline__ void load_hp(const UpdArgs& a, UpdHp& H)
 // summed in registers (ascending k), divided by T and consumed at once, so the averaged
 // gradient never makes a round trip through HBM; the statistic then comes from the
 // even-/odd-VSW partial sums that are in registers anyway.
-// Resident CTAs per SM asked of the compiler.  Measured on B200 (2^24..2^29 elements): up to
-// K = 4 two tiles per thread at 2 CTAs/SM win by ~5 %; from K = 5 one tile per thread at
-// 3 CTAs/SM (<= 85 registers) is 1 % ahead.
-__host__ __device__ constexpr int upd_min_ctas(int KAGG) { return KAGG <= 4 ? 1 : 3; }
+// Resident CTAs per SM asked of the compiler.  Measured on B200 (2^24..2^29 elements), two
+// tiles per thread throughout K <= 4: with up to two gradient streams the kernel needs the
+// third CTA per SM to cover its latency (K = 2: +23 % over 2 CTAs/SM at 118 registers);
+// K = 3 and 4 are 3-7 % faster at 2 CTAs/SM with the registers that takes (K = 4 would
+// spill at 80); from K = 5 one tile per thread at 3 CTAs/SM is 1 % ahead.
+__host__ __device__ constexpr int upd_min_ctas(int KAGG) { return (KAGG == 3 || KAGG == 4) ? 1 : 3; }
 
 // BULK: the inputs of a tile reach the registers through shared memory, staged by bulk
 // copies (one 4 KB copy per stream and stage, `stages` tiles in flight per CTA) instead of
@@ -617,6 +619,18 @@ __global__ void __launch_bounds__(kThreads, BULK ? 3 : upd_min_ctas(KAGG)) upd_v
                 }
             }
         }
+        // segment of the tile's first element, uniform over the CTA: looked up here, before the
+        // first use of the tile's data, so that the search runs while the loads are in flight
+        int seg0 = 0, gi0 = 0;
+        bool uniform = true;
+        if (a.segs) {
+            const unsigned long long e0 = a.base + 4 * t0;
+            unsigned long long e1 = a.base + 4 * (t0 + tile);
+            if (e1 > a.base + a.n) e1 = a.base + a.n;
+            seg0 = seg_find(a.segs, a.nseg, e0);
+            uniform = __ldg(&a.segs[seg0].end) >= e1;
+            gi0 = (int)__ldg(&a.segs[seg0].group);
+        }
         if (KAGG > 0) {
 #pragma unroll
             for (int u = 0; u < U; ++u) {
@@ -637,17 +651,6 @@ __global__ void __launch_bounds__(kThreads, BULK ? 3 : upd_min_ctas(KAGG)) upd_v
                     acc_vec(acc, div4(e, a.half_divisor), div4(o, a.half_divisor));
                 }
             }
-        }
-        // segment of the tile's first element; uniform over the CTA
-        int seg0 = 0, gi0 = 0;
-        bool uniform = true;
-        if (a.segs) {
-            const unsigned long long e0 = a.base + 4 * t0;
-            unsigned long long e1 = a.base + 4 * (t0 + tile);
-            if (e1 > a.base + a.n) e1 = a.base + a.n;
-            seg0 = seg_find(a.segs, a.nseg, e0);
-            uniform = __ldg(&a.segs[seg0].end) >= e1;
-            gi0 = (int)__ldg(&a.segs[seg0].group);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
