@@ -40,7 +40,7 @@ WORKLOADS = {
 # dram__bytes_read + dram__bytes_write of one launch divided by the launch's algorithmic bytes,
 # from the ncu captures summarised under profiles/ (ResNet-50 layout, K = 4, SGD-momentum); the
 # kernels stream every byte once, so the ratio carries over to other sizes.
-NCU_TRAFFIC_RATIO = {"fused_step": 1067.7 / 1124.5, "update": 760.1 / 817.8, "aggregate": 457.4 / 511.1}
+NCU_TRAFFIC_RATIO = {"fused_step": 1067.4 / 1124.5, "update": 760.1 / 817.8, "aggregate": 457.4 / 511.1}
 
 
 def parse_args():
