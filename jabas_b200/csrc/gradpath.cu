@@ -940,8 +940,8 @@ template <typename KernelT>
 int grid_for(jabas_ctx_t* ctx, KernelT kernel, unsigned long long work_items, unsigned long long per_cta,
              int* grid, size_t dyn_smem = 0)
 {
-    // a kernel is always launched with the same amount of dynamic shared memory or less than
-    // the amount it was first seen with, so one cache entry per kernel is enough
+    // kernels that take dynamic shared memory (the bulk-staged forms) never ask for more than
+    // kStageBudgetBytes: the occupancy is computed once, for that budget, and cached per kernel
     int per_sm = 0;
     {
         std::lock_guard<std::mutex> lk(ctx->mu);
