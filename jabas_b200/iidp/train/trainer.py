@@ -127,6 +127,8 @@ class IIDPTrainer(object):
         if collective == "peer" and self.weight_sync_method != "sequential":
             raise NotImplementedError("collective='peer' works on the whole model at step time: "
                                       "use weight_sync_method='sequential'")
+        # staging="bulk": the update kernels fetch their tiles by TMA bulk copies (same results)
+        staging = kwargs.pop("staging", "register")
         self.criterion = criterion
         K = self.num_models
         self.model_streams = [torch.cuda.Stream(self.device) if self._cuda else None for _ in range(K)]
@@ -136,7 +138,7 @@ class IIDPTrainer(object):
                                   similarity=self._similarity_enabled(),
                                   similarity_mode=self._similarity_mode(), backend=self._backend,
                                   first_bucket_bytes=first_bucket_bytes, share_weights=share_weights,
-                                  collective=collective)
+                                  collective=collective, staging=staging)
         self._sync_buffer_barrier = [None, None]
         self.local_models = [
             IndependentIdenticalDataParallel(

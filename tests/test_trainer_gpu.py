@@ -48,18 +48,20 @@ def _capture_vsw_gradients(tr):
     return captured
 
 
-@pytest.mark.parametrize("wsm,kind,K,threaded", [
-    ("sequential", "sgd", 2, False), ("overlap", "sgd", 2, False), ("sequential", "adamw", 2, False),
-    ("overlap", "adamw", 2, False), ("sequential", "sgd", 4, False), ("overlap", "sgd", 4, False),
-    ("sequential", "adamw", 4, False), ("overlap", "adamw", 4, False),
-    ("overlap", "sgd", 4, True), ("sequential", "adamw", 4, True)])
-def test_trainer_on_gpu_matches_reference_path(wsm, kind, K, threaded):
+@pytest.mark.parametrize("wsm,kind,K,threaded,staging", [
+    ("sequential", "sgd", 2, False, "register"), ("overlap", "sgd", 2, False, "register"),
+    ("sequential", "adamw", 2, False, "register"), ("overlap", "adamw", 2, False, "register"),
+    ("sequential", "sgd", 4, False, "register"), ("overlap", "sgd", 4, False, "register"),
+    ("sequential", "adamw", 4, False, "register"), ("overlap", "adamw", 4, False, "register"),
+    ("overlap", "sgd", 4, True, "register"), ("sequential", "adamw", 4, True, "register"),
+    ("sequential", "sgd", 4, False, "bulk"), ("overlap", "adamw", 2, False, "bulk")])
+def test_trainer_on_gpu_matches_reference_path(wsm, kind, K, threaded, staging):
     import jabas_b200
     from jabas_b200.iidp.optim import ShardAdamW, ShardSGD
     from oracle.reference_path import ReferencePath
     tr = jabas_b200.JABASTrainer(0, 8, K, 0, wsm, dict(CFG))
     tr.prepare_stream_parallel(_model(), torch.nn.CrossEntropyLoss().cuda(), bucket_cap_mb=0.05,
-                               first_bucket_bytes=4096)
+                               first_bucket_bytes=4096, staging=staging)
     assert tr.reducer.layout.num_buckets >= 3
     groups = _groups(tr.main_model)
     if kind == "sgd":
@@ -94,6 +96,8 @@ def test_trainer_on_gpu_matches_reference_path(wsm, kind, K, threaded):
         for p0, pk in zip(tr.local_models[0].parameters(), tr.local_models[K - 1].parameters()):
             assert torch.equal(p0, pk)
     assert tr.reducer.engine.launches > launches0          # the CUDA library did the work
+    if staging == "bulk":
+        assert tr.reducer.engine.ctx.staging_timeouts() == 0
 
 
 def test_runtime_change_of_vsw_count_on_gpu():
