@@ -275,8 +275,8 @@ JABAS_API int jabas_replicate_f32(jabas_ctx_t* ctx, const float* src, float* con
  * It takes no context and calls no cudaMalloc / cudaFree: the per-CTA partial sums live in
  * a static device array inside the library (about 48 KiB per GPU, held until exit).
  *  - n may not exceed JABAS_STATIC_MAX_ELEMS; larger inputs are refused with JABAS_EINVAL.
- *  - The first call on each device looks up the array's device address; make that first
- *    call (with the device current) before any stream capture.
+ *  - The first call on each device looks up the array's device address (a host-side query,
+ *    made with that device current).
  *  - All calls share the one array: two calls that overlap on the GPU (different streams,
  *    or different threads on different streams) race.  Keep them on one stream or order
  *    them with events. */
