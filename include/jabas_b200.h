@@ -116,8 +116,9 @@ JABAS_API int jabas_ctx_destroy(jabas_ctx_t* ctx);
  *  - JABAS_STAGING_BULK: TMA bulk copies (cp.async.bulk) of 4 KB per stream into a multi-stage
  *    shared-memory ring, completion on mbarriers.  Results are bit-identical (the statistic to
  *    fp64 summation order).  Launches whose gradient comes from peer shards keep the register
- *    form.  Every wait on a copy is bounded; a wait that runs out ends the CTA's loop early and
- *    is counted (the launch's outputs are then incomplete).
+ *    form.  Every wait on a copy is bounded by wall time (the GPU's global timer, 50 ms by
+ *    default); a wait that runs out ends the CTA's loop early, at the same tile for all of its
+ *    threads, and is counted (the launch's outputs are then incomplete).
  * jabas_ctx_set_staging allocates the 4-byte device counter the first time BULK is chosen.
  * jabas_ctx_staging_timeouts synchronises the device and reads the counter (0 = every launch
  * so far completed all of its copies). */
@@ -125,6 +126,19 @@ JABAS_API int jabas_ctx_destroy(jabas_ctx_t* ctx);
 #define JABAS_STAGING_BULK     1
 JABAS_API int jabas_ctx_set_staging(jabas_ctx_t* ctx, int mode);
 JABAS_API int jabas_ctx_staging_timeouts(jabas_ctx_t* ctx, uint32_t* count);
+
+/* Wall-time limits of the two kinds of device-side wait in this library, in milliseconds:
+ * a CTA's wait for a bulk copy into its shared-memory ring (default 50), and a CTA's wait for
+ * another GPU's progress inside the pipelined exchange (jabas_exchange_*; default 1000, which
+ * has to absorb the skew between ranks).  A wait that runs out never traps: the kernel records
+ * it and returns.  No reference counterpart. */
+JABAS_API int jabas_ctx_set_wait_limits(jabas_ctx_t* ctx, double staging_ms, double peer_ms);
+
+/* Test seam (host-side fault injection): when on, every stage barrier of the bulk-staged update
+ * kernels expects 16 bytes more than are copied, so each CTA's first wait runs out after the
+ * staging limit while every copy that was issued still completes.  Used to exercise the
+ * time-out path without faulting the GPU; never set in production. */
+JABAS_API int jabas_ctx_inject_staging_stall(jabas_ctx_t* ctx, int on);
 
 /* Uploads a segment table covering [0, total) of a flat parameter buffer.  Segments
  * must be sorted, non-empty and contiguous (seg[i].end == seg[i+1].begin).
@@ -246,6 +260,87 @@ JABAS_API int jabas_peer_reduce_f32(jabas_ctx_t* ctx, const float* const* xs, in
                           uint64_t lo, uint64_t hi, float divisor, float half_divisor,
                           double* stat3, void* stream);
 
+/* ---- The cross-GPU gradient path as ONE pipelined kernel per GPU --------------------------------
+ *
+ * Replaces, for one element range of the flat buffers, the whole per-bucket chain of the
+ * reference: IIDP's local aggregation of the K VSW buckets, the sub-group and world allreduces
+ * fired per bucket by the comm hook (jabas/ddp_comm_hooks/similarity_allreduce.py:20-45,
+ * registered at jabas/train/trainer.py:327-337), the optimizer step, the weight copy to the VSW
+ * replicas (jabas/train/trainer.py:530-534) and the sums of the cosine (:470-483).
+ *
+ * The range is cut into chunks of nranks * pieces_per_shard * JABAS_EXCHANGE_PIECE elements and
+ * every chunk into nranks shards.  One persistent kernel per GPU draws work items (aggregate /
+ * reduce / update pieces) from an ordered queue, so that the NVLink-bound reduce of chunk c runs
+ * together with the HBM-bound aggregate of chunk c+1 and update of chunk c-1.  Ranks synchronise
+ * through epoch flags stored into each other's flag blocks with plain peer stores; every wait is
+ * bounded by the context's peer wait limit (jabas_ctx_set_wait_limits) and a wait that runs out is
+ * reported through jabas_exchange_status, never by a trap.  Summation order is fixed: VSWs
+ * ascending, then ranks ascending with each rank's sum divided by `divisor` first; E / O of the
+ * statistic are the sums over even / odd ranks divided by `half_divisor`.  All ranks end with
+ * bit-identical weights.
+ *
+ * Set-up: every rank owns three buffers that all ranks can address (peer mappings; the caller
+ * allocates and exchanges them, e.g. with torch symmetric memory): `px` and `pg`, as long as the
+ * flat buffers (fp32), and a flag block of jabas_exchange_flag_words(max_slots) uint32 that must be
+ * zero before the first launch on ANY rank.  `max_slots` bounds slot_base + chunks of a launch;
+ * launches of one iteration that cover different ranges (one per DDP bucket) use disjoint slots.
+ * Every rank must issue the same sequence of launches.  Launches of one exchange must not overlap
+ * on the GPU (keep them on one stream). */
+#define JABAS_EXCHANGE_PIECE 8192u
+typedef struct jabas_exchange jabas_exchange_t;
+typedef struct {
+    int nranks;                     /* 2..8 */
+    int rank;
+    const float* const* px;         /* nranks device pointers, rank order (valid on this GPU) */
+    const float* const* pg;
+    uint32_t* const* flags;
+    uint32_t max_slots;
+    uint32_t pieces_per_shard;      /* Q: chunk = nranks * Q * JABAS_EXCHANGE_PIECE elements */
+} jabas_exchange_desc_t;
+
+/* Per-rank buffers of a launch.  grads: Kg VSW gradient buffers; w: K weight replicas (w[0] is the
+ * main replica); m, v: optimizer state; all indexed like the flat buffers (element `base` of the
+ * launch is element `base` of each).  stat3 (nullable, device): += this rank's share of
+ * (<E,O>, |E|^2, |O|^2). */
+typedef struct {
+    const float* const* grads;
+    int Kg;
+    int K;
+    float* const* w;
+    float* m;
+    float* v;
+    double* stat3;
+} jabas_exchange_bufs_t;
+
+JABAS_API size_t jabas_exchange_flag_words(uint32_t max_slots);
+JABAS_API int jabas_exchange_create(jabas_ctx_t* ctx, const jabas_exchange_desc_t* desc, jabas_exchange_t** out);
+JABAS_API int jabas_exchange_destroy(jabas_exchange_t* ex);
+/* Synchronises the device and clears the exchange's local counters, launch counter and status (to
+ * be followed by zeroing the flag blocks on every rank and a barrier: recovery after a time-out). */
+JABAS_API int jabas_exchange_reset(jabas_exchange_t* ex);
+/* Synchronous read of the status word (0 = no wait ever ran out; otherwise bit 31 set, bits 24..27
+ * the phase that gave up: 2 reduce, 3 update, 4 statistic, bits 0..23 the slot) and, optionally,
+ * of the number of completed launches. */
+JABAS_API int jabas_exchange_status(jabas_exchange_t* ex, uint32_t* status, uint32_t* launches);
+
+/* One launch over elements [base, base + n) (both multiples of 4).  Exactly one of sgd / adam is
+ * non-NULL; groups / layout as in jabas_sgd_momentum_f32.  nlocal == 1: exs[0] / bufs[0] are this
+ * GPU's rank (the production form, one process per GPU).  nlocal == nranks: all ranks live on
+ * this one GPU (exs[r] has rank r) and run as ONE launch sized so that every CTA is resident — the
+ * form single-GPU tests of the protocol use; it synchronises the stream once. */
+JABAS_API int jabas_exchange_step_f32(jabas_exchange_t* const* exs, const jabas_exchange_bufs_t* bufs, int nlocal,
+                                      uint64_t n, uint64_t base, uint32_t slot_base, float divisor,
+                                      float half_divisor, const jabas_layout_t* layout,
+                                      const jabas_group_t* groups, int ngroups, const jabas_sgd_hp_t* sgd,
+                                      const jabas_adam_hp_t* adam, void* stream);
+
+/* After the launches of an iteration: every rank publishes its three sums to all ranks, waits
+ * (bounded) for the others', adds them in rank order — stat3 then holds the sums over all ranks,
+ * identical everywhere — and writes cos_out[0] = stat3[0] / sqrt(max(stat3[1]*stat3[2], eps^2)).
+ * Replaces the all_gather / cosine_similarity / broadcast of jabas/train/trainer.py:470-483. */
+JABAS_API int jabas_exchange_cosine(jabas_exchange_t* const* exs, double* const* stat3, float* const* cos_out,
+                                    int nlocal, double eps, void* stream);
+
 /* stat3[0..2] += sum of x[i]^2 (fp64).  First half of gradient-norm clipping:
  * clip_grad_norm_for_overlap at examples/gnmt/seq2seq/train/shard_optimizer.py:75-76 and
  * clip_grad_norm_ at examples/gnmt/seq2seq/train/trainer.py:157-161. */
@@ -276,7 +371,7 @@ JABAS_API int jabas_replicate_f32(jabas_ctx_t* ctx, const float* src, float* con
  * a static device array inside the library (about 48 KiB per GPU, held until exit).
  *  - n may not exceed JABAS_STATIC_MAX_ELEMS; larger inputs are refused with JABAS_EINVAL.
  *  - The first call on each device looks up the array's device address (a host-side query,
- *    made with that device current).
+ *    made with that device current); make that first call before any stream capture begins.
  *  - All calls share the one array: two calls that overlap on the GPU (different streams,
  *    or different threads on different streams) race.  Keep them on one stream or order
  *    them with events. */

@@ -22,8 +22,13 @@ EXPORTS = (
     "jabas_replicate_f32", "jabas_dot_norms_static_f32", "jabas_vsw_sgd_momentum_f32",
     "jabas_vsw_adam_f32", "jabas_sumsq_f32", "jabas_clip_coef", "jabas_dynhp_create",
     "jabas_dynhp_destroy", "jabas_dynhp_push_sgd", "jabas_dynhp_push_adam", "jabas_peer_reduce_f32", "jabas_vsw_aggregate_scatter_f32",
-    "jabas_ctx_set_staging", "jabas_ctx_staging_timeouts",
+    "jabas_ctx_set_staging", "jabas_ctx_staging_timeouts", "jabas_ctx_set_wait_limits",
+    "jabas_ctx_inject_staging_stall", "jabas_exchange_flag_words", "jabas_exchange_create",
+    "jabas_exchange_destroy", "jabas_exchange_reset", "jabas_exchange_status", "jabas_exchange_step_f32",
+    "jabas_exchange_cosine",
 )
+
+EXCHANGE_PIECE = 8192          # JABAS_EXCHANGE_PIECE
 
 
 class Seg(ctypes.Structure):
@@ -55,6 +60,19 @@ class AdamHp(ctypes.Structure):
                 ("peer_grad", ctypes.POINTER(PeerSrc))]
 
 
+class ExchangeDesc(ctypes.Structure):
+    _fields_ = [("nranks", ctypes.c_int), ("rank", ctypes.c_int),
+                ("px", ctypes.POINTER(ctypes.c_void_p)), ("pg", ctypes.POINTER(ctypes.c_void_p)),
+                ("flags", ctypes.POINTER(ctypes.c_void_p)), ("max_slots", ctypes.c_uint32),
+                ("pieces_per_shard", ctypes.c_uint32)]
+
+
+class ExchangeBufs(ctypes.Structure):
+    _fields_ = [("grads", ctypes.POINTER(ctypes.c_void_p)), ("Kg", ctypes.c_int), ("K", ctypes.c_int),
+                ("w", ctypes.POINTER(ctypes.c_void_p)), ("m", ctypes.c_void_p), ("v", ctypes.c_void_p),
+                ("stat3", ctypes.c_void_p)]
+
+
 class JabasError(RuntimeError):
     """A libjabas_b200 call returned a negative status."""
 
@@ -82,6 +100,18 @@ def load() -> ctypes.CDLL:
     lib.jabas_ctx_destroy.argtypes = [vp]
     lib.jabas_ctx_set_staging.argtypes = [vp, i32]
     lib.jabas_ctx_staging_timeouts.argtypes = [vp, ctypes.POINTER(ctypes.c_uint32)]
+    lib.jabas_ctx_set_wait_limits.argtypes = [vp, f64, f64]
+    lib.jabas_ctx_inject_staging_stall.argtypes = [vp, i32]
+    u32 = ctypes.c_uint32
+    lib.jabas_exchange_flag_words.argtypes = [u32]
+    lib.jabas_exchange_create.argtypes = [vp, ctypes.POINTER(ExchangeDesc), pvp]
+    lib.jabas_exchange_destroy.argtypes = [vp]
+    lib.jabas_exchange_reset.argtypes = [vp]
+    lib.jabas_exchange_status.argtypes = [vp, ctypes.POINTER(u32), ctypes.POINTER(u32)]
+    lib.jabas_exchange_step_f32.argtypes = [pvp, ctypes.POINTER(ExchangeBufs), i32, u64, u64, u32, f32, f32, vp,
+                                            ctypes.POINTER(Group), i32, ctypes.POINTER(SgdHp),
+                                            ctypes.POINTER(AdamHp), vp]
+    lib.jabas_exchange_cosine.argtypes = [pvp, pvp, pvp, i32, f64, vp]
     lib.jabas_layout_create.argtypes = [vp, ctypes.POINTER(Seg), i32, u64, pvp]
     lib.jabas_layout_destroy.argtypes = [vp]
     lib.jabas_vsw_aggregate_f32.argtypes = [vp, pvp, i32, vp, vp, u64, f32, f32, vp, vp]
@@ -110,8 +140,9 @@ def load() -> ctypes.CDLL:
     lib.jabas_replicate_f32.argtypes = [vp, vp, pvp, i32, u64, vp]
     lib.jabas_dot_norms_static_f32.argtypes = [vp, vp, u64, vp, vp]
     for name in EXPORTS:
-        if name != "jabas_last_error":
+        if name not in ("jabas_last_error", "jabas_exchange_flag_words"):
             getattr(lib, name).restype = i32
+    lib.jabas_exchange_flag_words.restype = ctypes.c_size_t
     _lib = lib
     return lib
 

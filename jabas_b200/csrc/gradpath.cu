@@ -12,58 +12,23 @@
 //     warp shuffle and a shared-memory tree to one partial per CTA, and the last CTA
 //     to finish (ticket counter) adds the partials in index order: the result does
 //     not depend on scheduling.
-#include "jabas_b200.h"
+#include "common.cuh"
 
-#include <cuda_runtime.h>
-
-#include <cmath>
 #include <cstdio>
-#include <cstring>
-#include <mutex>
 #include <new>
-#include <string>
-#include <unordered_map>
 #include <vector>
 
 namespace {
-
-constexpr int kThreads = 256;
-constexpr int kWarps = kThreads / 32;
-constexpr int kMaxCtasPerSm = 8;
-
 thread_local std::string g_err;
+}
 
-int fail(int code, const std::string& msg)
+int jb_fail(int code, const std::string& msg)
 {
     g_err = msg;
     return code;
 }
 
-#define JB_CUDA(expr)                                                                     \
-    do {                                                                                  \
-        cudaError_t e__ = (expr);                                                         \
-        if (e__ != cudaSuccess)                                                           \
-            return fail(JABAS_ECUDA, std::string(#expr) + ": " + cudaGetErrorString(e__)); \
-    } while (0)
-
-// ----------------------------------------------------------------------------------
-// device helpers
-// ----------------------------------------------------------------------------------
-
-// Plain (coherent) 128-bit load that does not allocate in L1: every input is read once
-// per launch, and outputs may alias inputs, which rules out the non-coherent path.
-__device__ __forceinline__ float4 ld4(const float* p)
-{
-    float4 v;
-    asm volatile("ld.global.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                 : "l"(p));
-    return v;
-}
-__device__ __forceinline__ void st4(float* p, float4 v)
-{
-    *reinterpret_cast<float4*>(p) = v;
-}
+namespace {
 
 // ---- bulk-copy (TMA, untiled) staging of tiles into shared memory ------------------------
 // One elected thread issues `cp.async.bulk` for every input stream of a tile; the copies
@@ -74,7 +39,6 @@ constexpr int kMaxStages = 4;
 constexpr int kStageTileVecs = kThreads;                 // one 4-vector per thread and stream
 constexpr unsigned kStageTileBytes = kStageTileVecs * 16; // 4 KB per stream and stage
 constexpr int kStageBudgetBytes = 72 * 1024;             // dynamic shared memory asked per CTA
-constexpr int kWaitSpins = 1 << 22;
 
 __device__ __forceinline__ unsigned smem_u32(const void* p)
 {
@@ -98,12 +62,18 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* b, unsigned pa
                  : "memory");
     return ok != 0;
 }
-// false: the copies of this stage did not land within the spin limit
-__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* b, unsigned parity)
+// false: the copies of this stage did not land within `limit_ns` nanoseconds of wall time
+// (the limit is a time, not a poll count, so it does not depend on how long one poll takes)
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* b, unsigned parity, unsigned long long limit_ns)
 {
-    for (int spins = 0; spins < kWaitSpins; ++spins)
-        if (mbar_try_wait(b, parity)) return true;
-    return false;
+    if (mbar_try_wait(b, parity)) return true;
+    const unsigned long long t0 = gtime_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try_wait(b, parity)) return true;
+        if (gtime_ns() - t0 > limit_ns) return false;
+    }
 }
 __device__ __forceinline__ void bulk_load(void* dst_smem, const void* src, unsigned bytes, unsigned long long* b)
 {
@@ -116,55 +86,6 @@ __device__ __forceinline__ void bulk_load(void* dst_smem, const void* src, unsig
 __device__ __forceinline__ void fence_proxy_async_smem()
 {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-
-struct Acc3 {
-    double d, a, b;
-};
-
-struct StatWs {
-    double* partials;       // 3 doubles per CTA
-    unsigned int* counter;  // ticket, returns to 0 at the end of every launch
-};
-
-__device__ __forceinline__ void acc_vec(Acc3& acc, float4 e, float4 o)
-{
-    float d = __fmul_rn(e.x, o.x), a = __fmul_rn(e.x, e.x), b = __fmul_rn(o.x, o.x);
-    d = __fmaf_rn(e.y, o.y, d); a = __fmaf_rn(e.y, e.y, a); b = __fmaf_rn(o.y, o.y, b);
-    d = __fmaf_rn(e.z, o.z, d); a = __fmaf_rn(e.z, e.z, a); b = __fmaf_rn(o.z, o.z, b);
-    d = __fmaf_rn(e.w, o.w, d); a = __fmaf_rn(e.w, e.w, a); b = __fmaf_rn(o.w, o.w, b);
-    acc.d += (double)d; acc.a += (double)a; acc.b += (double)b;
-}
-__device__ __forceinline__ void acc_one(Acc3& acc, float e, float o)
-{
-    acc.d += (double)e * (double)o; acc.a += (double)e * (double)e; acc.b += (double)o * (double)o;
-}
-
-__device__ __forceinline__ Acc3 warp_sum(Acc3 v)
-{
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-        v.d += __shfl_down_sync(0xffffffffu, v.d, off);
-        v.a += __shfl_down_sync(0xffffffffu, v.a, off);
-        v.b += __shfl_down_sync(0xffffffffu, v.b, off);
-    }
-    return v;
-}
-
-// CTA-wide sum, valid in thread 0.
-__device__ __forceinline__ Acc3 block_sum(Acc3 v, double (*sm)[kWarps])
-{
-    v = warp_sum(v);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    __syncthreads();
-    if (lane == 0) { sm[0][warp] = v.d; sm[1][warp] = v.a; sm[2][warp] = v.b; }
-    __syncthreads();
-    Acc3 r = {0.0, 0.0, 0.0};
-    if (threadIdx.x == 0) {
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) { r.d += sm[0][w]; r.a += sm[1][w]; r.b += sm[2][w]; }
-    }
-    return r;
 }
 
 // One partial per CTA; the last CTA to arrive adds them in CTA order into stat3.
@@ -232,15 +153,6 @@ __device__ __forceinline__ float* agg_dst(const AggArgs& a, unsigned long long i
 }
 
 __host__ __device__ constexpr int agg_unroll(int K) { return K <= 2 ? 4 : (K <= 4 ? 2 : 1); }
-
-__device__ __forceinline__ float4 add4(float4 a, float4 b)
-{
-    return make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w));
-}
-__device__ __forceinline__ float4 div4(float4 a, float d)
-{
-    return make_float4(__fdiv_rn(a.x, d), __fdiv_rn(a.y, d), __fdiv_rn(a.z, d), __fdiv_rn(a.w, d));
-}
 
 // Per-element form: the tail of the vector kernel and the whole of the unaligned path.
 template <bool STAT>
@@ -321,30 +233,6 @@ __global__ void __launch_bounds__(kThreads) agg_scalar_kernel(const AggArgs a)
 // fused optimizer update + write-back + statistic
 // ----------------------------------------------------------------------------------
 
-struct SegDev {
-    unsigned long long begin, end;
-    unsigned int group, pad;
-};
-
-struct GroupDev {
-    float wd;      // weight decay
-    float s0;      // SGD: -lr             Adam: 1 - lr*wd (decoupled decay factor)
-    float s1;      // SGD: unused          Adam: -(lr / (1 - beta1^t))
-    float s2;      // SGD: unused          Adam: sqrt(1 - beta2^t)
-};
-
-// Everything an update kernel needs that may change from one iteration to the next.
-struct UpdHp {
-    GroupDev grp[JABAS_MAX_GROUPS];
-    unsigned int flags;
-    unsigned int wd_mask;     // bit i: group i has weight_decay != 0
-    float c0, c1, c2, c3, c4; // SGD: mu, 1-dampening | Adam: b1, b2, 1-b1, 1-b2, eps
-    float pad;
-};
-
-enum { OPT_SGD = 0, OPT_ADAM = 1 };
-enum { F_NESTEROV = 1, F_FIRST = 2, F_MOMENTUM = 4, F_DECOUPLED = 8 };
-
 struct UpdArgs {
     const float* g;                     // averaged gradient (two-kernel form) ...
     const float* gk[JABAS_MAX_VSW];     // ... or the kagg VSW gradients to aggregate on the fly
@@ -370,6 +258,8 @@ struct UpdArgs {
     // largest stream count) and the device counter of waits that ran out
     int stages, stage_slots;
     unsigned int* timeouts;
+    unsigned long long wait_ns;   // wall-time limit of one wait for a stage's copies
+    unsigned int extra_tx;        // test seam: bytes a stage's barrier expects beyond what is copied
     UpdHp hp;                 // ... otherwise they travel in the argument block
 };
 
@@ -382,52 +272,6 @@ __device__ __forceinline__ const float* peer_base(const UpdArgs& a, unsigned lon
     for (int r = 1; r < JABAS_MAX_VSW; ++r)
         if (owner >= (unsigned long long)r && r < a.npeer) gp = a.gk[r];
     return gp;
-}
-
-// index of the segment that holds element `idx` (segments are contiguous and sorted)
-__device__ __forceinline__ int seg_find(const SegDev* segs, int nseg, unsigned long long idx)
-{
-    int lo = 0, hi = nseg - 1;
-    while (lo < hi) {
-        const int mid = (lo + hi) >> 1;
-        if (__ldg(&segs[mid].end) <= idx) lo = mid + 1; else hi = mid;
-    }
-    return lo;
-}
-
-template <int OPT>
-__device__ __forceinline__ void upd_math(const UpdHp& a, const GroupDev& h, bool has_wd, float g,
-                                         float& p, float& m, float& v)
-{
-    if (OPT == OPT_SGD) {
-        float d = g;
-        if (has_wd) d = __fmaf_rn(h.wd, p, d);
-        if (a.flags & F_MOMENTUM) {
-            float b;
-            if (a.flags & F_FIRST) b = d;
-            else b = __fmaf_rn(a.c1, d, __fmul_rn(a.c0, m));
-            m = b;
-            d = (a.flags & F_NESTEROV) ? __fmaf_rn(a.c0, b, d) : b;
-        }
-        p = __fmaf_rn(h.s0, d, p);
-    } else {
-        if (a.flags & F_DECOUPLED) p = __fmul_rn(p, h.s0);
-        else if (has_wd) g = __fmaf_rn(h.wd, p, g);
-        m = __fmaf_rn(a.c2, g, __fmul_rn(a.c0, m));
-        v = __fmaf_rn(__fmul_rn(a.c3, g), g, __fmul_rn(a.c1, v));
-        const float denom = __fadd_rn(__fdiv_rn(__fsqrt_rn(v), h.s2), a.c4);
-        p = __fmaf_rn(h.s1, __fdiv_rn(m, denom), p);
-    }
-}
-
-template <int OPT>
-__device__ __forceinline__ void upd_math4(const UpdHp& a, const GroupDev& h, bool has_wd, float4 g,
-                                          float4& p, float4& m, float4& v)
-{
-    upd_math<OPT>(a, h, has_wd, g.x, p.x, m.x, v.x);
-    upd_math<OPT>(a, h, has_wd, g.y, p.y, m.y, v.y);
-    upd_math<OPT>(a, h, has_wd, g.z, p.z, m.z, v.z);
-    upd_math<OPT>(a, h, has_wd, g.w, p.w, m.w, v.w);
 }
 
 template <bool STAT>
@@ -530,10 +374,9 @@ __global__ void __launch_bounds__(kThreads, BULK ? 3 : upd_min_ctas(KAGG)) upd_v
     __shared__ UpdHp H;
     extern __shared__ __align__(128) unsigned char stage_raw[];
     __shared__ unsigned long long stage_full[kMaxStages];
-    __shared__ volatile int stage_abort;
+    bool stage_abort = false;     // decided per tile by a CTA-wide vote: the same in every thread
     if (BULK && threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; ++s) mbar_init(&stage_full[s], 1);
-        stage_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     load_hp(a, H);
@@ -551,7 +394,7 @@ __global__ void __launch_bounds__(kThreads, BULK ? 3 : upd_min_ctas(KAGG)) upd_v
         const unsigned bytes = left >= (unsigned long long)kStageTileVecs ? kStageTileBytes : (unsigned)left * 16u;
         const int nslot = slot_h + ((STAT && KAGG == 0) ? 1 : 0);
         unsigned char* sb = stage_raw + (size_t)s * a.stage_slots * kStageTileBytes;
-        mbar_expect_tx(&stage_full[s], bytes * (unsigned)nslot);
+        mbar_expect_tx(&stage_full[s], bytes * (unsigned)nslot + a.extra_tx);
         if (KAGG > 0) {
 #pragma unroll
             for (int k = 0; k < KX; ++k) bulk_load(sb + k * kStageTileBytes, a.gk[k] + 4 * t, bytes, &stage_full[s]);
@@ -576,7 +419,7 @@ __global__ void __launch_bounds__(kThreads, BULK ? 3 : upd_min_ctas(KAGG)) upd_v
         float4 g[U], p[U], m[U], v[U], hs[U], xk[U][KX];
         if (BULK) {
             const int s = cur_stage;
-            if (!mbar_wait_bounded(&stage_full[s], cur_parity)) stage_abort = 1;
+            const bool landed = mbar_wait_bounded(&stage_full[s], cur_parity, a.wait_ns);
             const float4* sb = reinterpret_cast<const float4*>(stage_raw + (size_t)s * a.stage_slots * kStageTileBytes);
             m[0] = v[0] = hs[0] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (full || t0 + threadIdx.x < nvec) {
@@ -591,8 +434,9 @@ __global__ void __launch_bounds__(kThreads, BULK ? 3 : upd_min_ctas(KAGG)) upd_v
                 if (OPT == OPT_ADAM) v[0] = sb[slot_v * kStageTileVecs + threadIdx.x];
                 if (STAT && KAGG == 0) hs[0] = sb[slot_h * kStageTileVecs + threadIdx.x];
             }
-            __syncthreads();                       // the stage has been read by every thread
-            if (stage_abort) break;                // set before the barrier: the same for all threads
+            // the stage has been read by every thread; one vote per tile, so that all threads
+            // leave the loop at the same tile when any thread's wait ran out
+            if (__syncthreads_or(!landed)) { stage_abort = true; break; }
             if (threadIdx.x == 0) {
                 const unsigned long long nt = t0 + (unsigned long long)a.stages * stride;
                 if (nt < nvec) { fence_proxy_async_smem(); stage_issue(nt, s); }
@@ -685,7 +529,7 @@ __global__ void __launch_bounds__(kThreads, BULK ? 3 : upd_min_ctas(KAGG)) upd_v
         // (t0, cur_stage, cur_parity still describe the tile whose wait failed)
         unsigned long long t = t0;
         for (int j = 0; j < a.stages && t < nvec; ++j, t += stride) {
-            (void)mbar_wait_bounded(&stage_full[cur_stage], cur_parity);
+            (void)mbar_wait_bounded(&stage_full[cur_stage], cur_parity, a.wait_ns);
             if (++cur_stage == a.stages) { cur_stage = 0; cur_parity ^= 1u; }
         }
         if (threadIdx.x == 0 && a.timeouts) atomicAdd(a.timeouts, 1u);
@@ -886,47 +730,9 @@ __global__ void __launch_bounds__(kThreads) replicate_kernel(const RepArgs a)
 // host side
 // ----------------------------------------------------------------------------------
 
-inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-
 }  // namespace
 
-struct jabas_ctx {
-    int device = 0;
-    int sm_count = 0;
-    int max_grid = 0;
-    std::mutex mu;
-    std::unordered_map<void*, StatWs> ws;   // one reduction workspace per stream
-    std::unordered_map<const void*, int> occ;
-    int staging = JABAS_STAGING_REGISTER;   // how the update kernels fetch their tiles
-    unsigned int* d_timeouts = nullptr;     // bulk staging: waits that ran out (device counter)
-};
-
-struct jabas_layout {
-    int device = 0;
-    int nseg = 0;
-    int max_group = 0;
-    unsigned long long total = 0;
-    SegDev* dsegs = nullptr;
-};
-
-// Device-resident hyper-parameter block.  A captured CUDA graph bakes kernel arguments in;
-// what changes every iteration (lr, Adam step, first-step flag) therefore lives in device
-// memory and is refreshed by a small stream-ordered copy BEFORE each replay, outside the
-// graph, from a ring of pinned slots (a slot is reused only after its copy has completed).
-struct jabas_dynhp {
-    static constexpr int kSlots = 8;
-    int device = 0;
-    int kind = -1;                  // OPT_SGD / OPT_ADAM once pushed
-    UpdHp* dev = nullptr;
-    UpdHp* pinned = nullptr;        // kSlots entries
-    cudaEvent_t done[kSlots] = {};
-    int next = 0;
-    std::mutex mu;
-};
-
-namespace {
-
-int ctx_bind(jabas_ctx_t* ctx)
+int jb_ctx_bind(jabas_ctx_t* ctx)
 {
     if (!ctx) return fail(JABAS_EINVAL, "ctx is null");
     int cur = -1;
@@ -934,6 +740,10 @@ int ctx_bind(jabas_ctx_t* ctx)
     if (cur != ctx->device) JB_CUDA(cudaSetDevice(ctx->device));
     return JABAS_OK;
 }
+
+namespace {
+
+inline int ctx_bind(jabas_ctx_t* ctx) { return jb_ctx_bind(ctx); }
 
 // Resident CTAs per SM of a kernel, cached per context.
 template <typename KernelT>
@@ -1030,6 +840,8 @@ int upd_launch_vec(jabas_ctx_t* ctx, UpdArgs& a, cudaStream_t st)
         a.stage_slots = (KAGG > 0 ? KAGG : 1) + 2 + (OPT == OPT_ADAM ? 1 : 0) + ((a.stat && KAGG == 0) ? 1 : 0);
         a.stages = stage_count(a.stage_slots);
         a.timeouts = ctx->d_timeouts;
+        a.wait_ns = (unsigned long long)(ctx->staging_wait_ms * 1e6);
+        a.extra_tx = ctx->stall_tx;
         const size_t smem = (size_t)a.stages * a.stage_slots * kStageTileBytes;
         if (a.stat) {
             if ((rc = grid_for(ctx, upd_vec_kernel<OPT, true, 1, KAGG, true>, a.n >> 2, kThreads, &grid, smem))) return rc;
@@ -1138,6 +950,42 @@ int upd_prepare(jabas_ctx_t* ctx, UpdArgs& a, bool* vec, const GradSrc& src, flo
 
 }  // namespace
 
+// Host -> kernel form of the hyper-parameters: fp64 scalars rounded to fp32 once.
+int jb_fill_sgd_hp(UpdHp& h, const jabas_group_t* groups, int ngroups, const jabas_sgd_hp_t* hp)
+{
+    std::memset(&h, 0, sizeof(h));
+    h.c0 = (float)hp->momentum;
+    h.c1 = (float)(1.0 - hp->dampening);
+    h.flags = (hp->nesterov ? F_NESTEROV : 0u) | (hp->first_step ? F_FIRST : 0u) |
+              (hp->momentum != 0.0 ? F_MOMENTUM : 0u);
+    for (int i = 0; i < ngroups; ++i) {
+        h.grp[i].wd = (float)groups[i].weight_decay;
+        h.grp[i].s0 = (float)(-groups[i].lr);
+        if (groups[i].weight_decay != 0.0) h.wd_mask |= 1u << i;
+    }
+    return JABAS_OK;
+}
+
+int jb_fill_adam_hp(UpdHp& h, const jabas_group_t* groups, int ngroups, const jabas_adam_hp_t* hp)
+{
+    std::memset(&h, 0, sizeof(h));
+    h.c0 = (float)hp->beta1; h.c1 = (float)hp->beta2;
+    h.c2 = (float)(1.0 - hp->beta1); h.c3 = (float)(1.0 - hp->beta2);
+    h.c4 = (float)hp->eps;
+    h.flags = hp->decoupled ? F_DECOUPLED : 0u;
+    for (int i = 0; i < ngroups; ++i) {
+        if (groups[i].step < 1) return fail(JABAS_EINVAL, "Adam step must be >= 1");
+        const double bc1 = 1.0 - std::pow(hp->beta1, (double)groups[i].step);
+        const double bc2 = 1.0 - std::pow(hp->beta2, (double)groups[i].step);
+        h.grp[i].wd = (float)groups[i].weight_decay;
+        h.grp[i].s0 = (float)(1.0 - groups[i].lr * groups[i].weight_decay);
+        h.grp[i].s1 = (float)(-(groups[i].lr / bc1));
+        h.grp[i].s2 = (float)std::sqrt(bc2);
+        if (groups[i].weight_decay != 0.0) h.wd_mask |= 1u << i;
+    }
+    return JABAS_OK;
+}
+
 extern "C" {
 
 int jabas_version(void) { return JABAS_B200_VERSION; }
@@ -1187,6 +1035,25 @@ int jabas_ctx_set_staging(jabas_ctx_t* ctx, int mode)
         ctx->d_timeouts = d;
     }
     ctx->staging = mode;
+    return JABAS_OK;
+}
+
+int jabas_ctx_set_wait_limits(jabas_ctx_t* ctx, double staging_ms, double peer_ms)
+{
+    int rc = ctx_bind(ctx);
+    if (rc) return rc;
+    if (!(staging_ms > 0.0) || !(peer_ms > 0.0) || staging_ms > 60e3 || peer_ms > 60e3)
+        return fail(JABAS_EINVAL, "wait limits must be in (0, 60000] milliseconds");
+    ctx->staging_wait_ms = staging_ms;
+    ctx->peer_wait_ms = peer_ms;
+    return JABAS_OK;
+}
+
+int jabas_ctx_inject_staging_stall(jabas_ctx_t* ctx, int on)
+{
+    int rc = ctx_bind(ctx);
+    if (rc) return rc;
+    ctx->stall_tx = on ? 16u : 0u;
     return JABAS_OK;
 }
 
@@ -1359,42 +1226,6 @@ static int set_peer_src(UpdArgs& a, const jabas_peer_src_t* ps, bool* vec)
     return JABAS_OK;
 }
 
-// Host -> kernel form of the hyper-parameters: fp64 scalars rounded to fp32 once.
-static int fill_sgd_hp(UpdHp& h, const jabas_group_t* groups, int ngroups, const jabas_sgd_hp_t* hp)
-{
-    std::memset(&h, 0, sizeof(h));
-    h.c0 = (float)hp->momentum;
-    h.c1 = (float)(1.0 - hp->dampening);
-    h.flags = (hp->nesterov ? F_NESTEROV : 0u) | (hp->first_step ? F_FIRST : 0u) |
-              (hp->momentum != 0.0 ? F_MOMENTUM : 0u);
-    for (int i = 0; i < ngroups; ++i) {
-        h.grp[i].wd = (float)groups[i].weight_decay;
-        h.grp[i].s0 = (float)(-groups[i].lr);
-        if (groups[i].weight_decay != 0.0) h.wd_mask |= 1u << i;
-    }
-    return JABAS_OK;
-}
-
-static int fill_adam_hp(UpdHp& h, const jabas_group_t* groups, int ngroups, const jabas_adam_hp_t* hp)
-{
-    std::memset(&h, 0, sizeof(h));
-    h.c0 = (float)hp->beta1; h.c1 = (float)hp->beta2;
-    h.c2 = (float)(1.0 - hp->beta1); h.c3 = (float)(1.0 - hp->beta2);
-    h.c4 = (float)hp->eps;
-    h.flags = hp->decoupled ? F_DECOUPLED : 0u;
-    for (int i = 0; i < ngroups; ++i) {
-        if (groups[i].step < 1) return fail(JABAS_EINVAL, "Adam step must be >= 1");
-        const double bc1 = 1.0 - std::pow(hp->beta1, (double)groups[i].step);
-        const double bc2 = 1.0 - std::pow(hp->beta2, (double)groups[i].step);
-        h.grp[i].wd = (float)groups[i].weight_decay;
-        h.grp[i].s0 = (float)(1.0 - groups[i].lr * groups[i].weight_decay);
-        h.grp[i].s1 = (float)(-(groups[i].lr / bc1));
-        h.grp[i].s2 = (float)std::sqrt(bc2);
-        if (groups[i].weight_decay != 0.0) h.wd_mask |= 1u << i;
-    }
-    return JABAS_OK;
-}
-
 static int sgd_impl(jabas_ctx_t* ctx, const GradSrc& src, float* const* w, int K, float* m,
                     uint64_t n, uint64_t base, const jabas_layout_t* layout,
                     const jabas_group_t* groups, int ngroups, const jabas_sgd_hp_t* hp,
@@ -1412,7 +1243,7 @@ static int sgd_impl(jabas_ctx_t* ctx, const GradSrc& src, float* const* w, int K
     if (n == 0) return JABAS_OK;
     a.grad_scale = hp->grad_scale;
     if ((rc = set_peer_src(a, hp->peer_grad, &vec))) return rc;
-    if ((rc = fill_sgd_hp(a.hp, groups, ngroups, hp))) return rc;
+    if ((rc = jb_fill_sgd_hp(a.hp, groups, ngroups, hp))) return rc;
     if (hp->dynamic) {
         if (hp->dynamic->kind != OPT_SGD) return fail(JABAS_EINVAL, "the dynamic block holds Adam hyper-parameters");
         a.dyn = hp->dynamic->dev;
@@ -1456,7 +1287,7 @@ static int adam_impl(jabas_ctx_t* ctx, const GradSrc& src, float* const* w, int 
     if (n == 0) return JABAS_OK;
     a.grad_scale = hp->grad_scale;
     if ((rc = set_peer_src(a, hp->peer_grad, &vec))) return rc;
-    if ((rc = fill_adam_hp(a.hp, groups, ngroups, hp))) return rc;
+    if ((rc = jb_fill_adam_hp(a.hp, groups, ngroups, hp))) return rc;
     if (hp->dynamic) {
         if (hp->dynamic->kind != OPT_ADAM) return fail(JABAS_EINVAL, "the dynamic block holds SGD hyper-parameters");
         a.dyn = hp->dynamic->dev;
@@ -1542,7 +1373,7 @@ int jabas_dynhp_push_sgd(jabas_dynhp_t* h, const jabas_group_t* groups, int ngro
     if (!h || !groups || !hp) return fail(JABAS_EINVAL, "null argument");
     if (ngroups < 1 || ngroups > JABAS_MAX_GROUPS) return fail(JABAS_EINVAL, "ngroups must be in [1, JABAS_MAX_GROUPS]");
     UpdHp v;
-    int rc = fill_sgd_hp(v, groups, ngroups, hp);
+    int rc = jb_fill_sgd_hp(v, groups, ngroups, hp);
     return rc ? rc : dynhp_push(h, v, OPT_SGD, stream);
 }
 
@@ -1552,7 +1383,7 @@ int jabas_dynhp_push_adam(jabas_dynhp_t* h, const jabas_group_t* groups, int ngr
     if (!h || !groups || !hp) return fail(JABAS_EINVAL, "null argument");
     if (ngroups < 1 || ngroups > JABAS_MAX_GROUPS) return fail(JABAS_EINVAL, "ngroups must be in [1, JABAS_MAX_GROUPS]");
     UpdHp v;
-    int rc = fill_adam_hp(v, groups, ngroups, hp);
+    int rc = jb_fill_adam_hp(v, groups, ngroups, hp);
     return rc ? rc : dynhp_push(h, v, OPT_ADAM, stream);
 }
 
@@ -1734,8 +1565,7 @@ extern "C" int jabas_dot_norms_static_f32(const float* a, const float* b, uint64
     unsigned long long grid = (items + per_cta - 1) / per_cta;
     const unsigned long long cap = (unsigned long long)sms * kMaxCtasPerSm;
     if (grid > cap) grid = cap;
-    if (grid > (unsigned long long)kStaticMaxCtas)
-        return fail(JABAS_EINVAL, "this device needs more partial-sum slots than the static scratch holds");
+    if (grid > (unsigned long long)kStaticMaxCtas) grid = kStaticMaxCtas;   // the kernel strides over the rest
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // The array keeps whatever the previous call left: the ticket must start at zero.
     JB_CUDA(cudaMemsetAsync(ws.counter, 0, sizeof(unsigned int), st));

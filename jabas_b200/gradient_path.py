@@ -60,7 +60,8 @@ class GradientPath:
                  total_num_decoupled_workers: int, process_group=None, sub_group=None,
                  pair_group=None, first_subgroup_src_rank: int = 0, second_subgroup_src_rank: int = 1,
                  similarity: bool = True, similarity_mode: str = "fused", backend=None,
-                 collective: str = "nccl", share_weights: bool = False, staging: str = "register"):
+                 collective: str = "nccl", share_weights: bool = False, staging: str = "register",
+                 peer_form: str = "pipeline", peer_wait_ms: Optional[float] = None):
         if backend is None:
             from . import ops as backend          # the CUDA library; raises without a GPU
         self.ops = backend
@@ -91,6 +92,8 @@ class GradientPath:
         self.ctx = self.ops.Context(self.device)
         if staging != "register":                 # "bulk": TMA bulk copies into shared memory
             self.ctx.set_staging(staging)
+        if peer_wait_ms is not None:
+            self.ctx.set_wait_limits(peer_ms=peer_wait_ms)
         self.dev_layout = None
         n = layout.total
         f32 = dict(dtype=torch.float32, device=self.device)
@@ -106,18 +109,34 @@ class GradientPath:
         self.grads = [torch.zeros(n, **f32) for _ in range(self.K)]
         if collective not in ("nccl", "peer"):
             raise ValueError("collective must be 'nccl' or 'peer'")
+        if collective == "peer" and staging != "register":
+            # a launch that reads another GPU's memory always loads straight into registers
+            raise ValueError("staging='bulk' cannot be combined with collective='peer': kernels that read "
+                             "peer-mapped memory use per-thread loads")
+        if peer_form not in ("pipeline", "pull", "scatter", "direct"):
+            raise ValueError("peer_form must be 'pipeline', 'pull', 'scatter' or 'direct'")
         self.collective = collective if self.world > 1 else "nccl"
         self.half = torch.zeros(n, **f32) if (self.similarity and self.world > 1
                                               and self.collective == "nccl") else None
-        #: two ranks: the update kernel reads both sums itself; more ranks: reduce-scatter kernel first
-        self.peer_direct = self.world == 2
-        #: reduce-scatter stage with more than two ranks: "pull" — the reduce kernel reads its shard
-        #: from every rank's buffer over NVLink; "scatter" — the aggregate kernel stores its sums into
-        #: the owners' staging slots and the reduce is local.  Measured on 8 B200: 0.598 vs 0.641 ms
-        #: per step (4 GPUs: 0.526 vs 0.533), so "pull" is the default.
-        self.peer_form = "pull"
+        #: how collective="peer" moves the gradients between GPUs:
+        #:   "pipeline" (default) ONE persistent kernel per launch draws aggregate / reduce / update
+        #:              pieces from an ordered queue; ranks synchronise through epoch flags in peer
+        #:              memory (bounded waits), so NVLink and HBM phases overlap chunk by chunk; works
+        #:              per bucket (hooks during backward) and over the whole model
+        #:   "pull"     three kernels over the whole model separated by NCCL barriers: aggregate,
+        #:              reduce kernel that reads its shard from every rank, gathering update
+        #:   "scatter"  as "pull", but the aggregate kernel stores its sums into the owners' slots
+        #:   "direct"   two ranks only: the update kernel reads both ranks' sums itself
+        self.peer_form = peer_form
+        self.peer_direct = peer_form == "direct"
+        if self.peer_direct and self.world != 2 and self.collective == "peer":
+            raise ValueError("peer_form='direct' needs exactly two ranks")
+        self.exchange = None
         if self.collective == "peer":
-            self._setup_peer_exchange()
+            if self.peer_form == "pipeline":
+                self._setup_pipeline_exchange()
+            else:
+                self._setup_peer_exchange()
         self.stat = torch.zeros(3, dtype=torch.float64, device=self.device)
         self.cos = torch.zeros(1, **f32)
         self.steps = 0                               # completed optimizer steps
@@ -169,12 +188,88 @@ class GradientPath:
         self._peer_grad = self.ops.PeerGrad(self.pg_ptrs, self.shard_len)
         self._tok = torch.zeros(1, dtype=torch.float32, device=self.device)
 
+    def _setup_pipeline_exchange(self) -> None:
+        """Buffers of the pipelined exchange, all of them symmetric (allocated and exchanged by
+        torch symmetric memory, addressed by this library's kernels): ``px`` takes this rank's
+        undivided local sum, ``pgrad`` the shards of the averaged gradient this rank reduces, and
+        a block of epoch flags that the other ranks store into.  Chunks of about 2^20 elements."""
+        import torch.distributed._symmetric_memory as symm_mem
+        n, world = self.layout.total, self.world
+        if world > 8:
+            raise ValueError("the pipelined exchange serves up to 8 ranks (one NVSwitch domain)")
+        group = self.pg if self.pg is not None else dist.group.WORLD
+        piece = self.ops.EXCHANGE_PIECE
+        q = max(1, (1 << 20) // (world * piece))
+        chunk = world * q * piece
+        per_bucket = [-(-self._bucket_span(b)[1] // chunk) for b in range(self.layout.num_buckets)]
+        self._slot_base = [sum(per_bucket[:b]) for b in range(len(per_bucket))]
+        max_slots = max(-(-n // chunk), sum(per_bucket), 1)
+        words = self.ops.exchange_flag_words(max_slots)
+        self.px = symm_mem.empty(n, dtype=torch.float32, device=self.device)
+        self.pgrad = symm_mem.empty(n, dtype=torch.float32, device=self.device)
+        self.xflags = symm_mem.empty(words, dtype=torch.int32, device=self.device)
+        self.px.zero_(); self.pgrad.zero_(); self.xflags.zero_()
+        self._px_h = symm_mem.rendezvous(self.px, group)
+        self._pg_h = symm_mem.rendezvous(self.pgrad, group)
+        self._fl_h = symm_mem.rendezvous(self.xflags, group)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.pg)                   # every rank's flag block is zero before any launch
+        self.exchange = self.ops.Exchange(self.ctx, world, self.rank,
+                                          [int(p) for p in self._px_h.buffer_ptrs],
+                                          [int(p) for p in self._pg_h.buffer_ptrs],
+                                          [int(p) for p in self._fl_h.buffer_ptrs], max_slots, q)
+
+    def _bucket_span(self, b: Optional[int]):
+        """(first element, length) of a launch over bucket ``b`` (None: the whole flat buffer); a
+        bucket's span runs to the 128-byte boundary its successor starts on (padding is zero)."""
+        if b is None:
+            return 0, self.layout.total
+        begin, end = self.layout.buckets[b]
+        nxt = self.layout.buckets[b + 1][0] if b + 1 < self.layout.num_buckets else self.layout.total
+        return begin, nxt - begin
+
+    def exchange_launch(self, b: Optional[int] = None) -> None:
+        """One launch of the pipelined exchange: aggregation, cross-GPU reduction, update,
+        write-back and this rank's share of the statistic for bucket ``b`` (None: the model)."""
+        begin, length = self._bucket_span(b)
+        if length == 0:
+            return
+        o = self.opt
+        bufs = dict(grads=self.grads, weights=self._replicas(0, self.layout.total), m=self.m, v=self.v,
+                    stat=self.stat if self._sim_step else None)
+        kw = dict(kind=o.kind, layout=self.dev_layout, dynamic=self._dyn)
+        if o.kind == "sgd":
+            kw.update(momentum=o.momentum, dampening=o.dampening, nesterov=o.nesterov,
+                      first_step=(self.steps == 0))
+            groups = o.groups
+        else:
+            kw.update(beta1=o.betas[0], beta2=o.betas[1], eps=o.eps)
+            groups = [dict(gr, step=self.steps + 1) for gr in o.groups]
+        ev = self._ev_begin()
+        self.ops.exchange_step([self.exchange], [bufs], length, begin, 0 if b is None else self._slot_base[b],
+                               float(self.T), self.T / 2, groups, **kw)
+        self._ev_end("exchange", b, ev)
+        self.launches += 1
+
+    def check_exchange(self) -> None:
+        """Raise if a bounded wait of the pipelined exchange ever ran out (synchronises the device)."""
+        if self.exchange is not None:
+            status, _ = self.exchange.status()
+            if status:
+                phase = {2: "reduce", 3: "update", 4: "statistic"}.get((status >> 24) & 0xf, "?")
+                raise RuntimeError(f"pipelined exchange: a wait on another rank ran out in the {phase} phase "
+                                   f"(slot {status & 0xffffff}); this iteration's weights are incomplete")
+
     def _peer_iteration(self) -> Optional[torch.Tensor]:
-        """Whole flat model through the peer-memory exchange.  More than two ranks:
+        """Whole flat model through the peer-memory exchange.  ``peer_form="pipeline"``: one
+        launch (plus the 32-thread statistic kernel).  The older forms, more than two ranks:
         aggregate -> barrier -> reduce kernel for this rank's shard (reads every rank's sums
         over NVLink, or, in the "scatter" form, the local staging slots the aggregate kernels
         stored into; statistic from the exact even/odd-rank halves) -> barrier carrying the
         3-double statistic -> update kernel that gathers the gradient shards over NVLink."""
+        if self.exchange is not None:
+            self.exchange_launch(None)
+            return self.finish_similarity()
         sim = self._sim_step
         n = self.layout.total
         direct = self.peer_direct and self.world <= getattr(self.ops, "MAX_FUSED_VSW", 0)
@@ -422,10 +517,23 @@ class GradientPath:
         """Optimizer update of the given buckets (None: the whole model), as one fused
         aggregate+update kernel where the aggregation was deferred."""
         nb = self.layout.num_buckets
+        if self.collective == "peer" and self.exchange is not None:
+            todo = range(nb) if buckets is None else list(buckets)
+            if any(b not in self._deferred for b in todo):
+                raise RuntimeError("the pipelined exchange aggregates the VSW gradients itself: the comm hooks "
+                                   "must have left the bucket untouched")
+            if buckets is None and len(self._deferred) == nb:
+                self._deferred.clear()
+                self.exchange_launch(None)             # one launch over the whole model
+                return
+            for b in todo:
+                self._deferred.discard(b)
+                self.exchange_launch(b)                # per bucket: overlaps the rest of backward
+            return
         if self.collective == "peer":
             if buckets is not None or len(self._deferred) != nb:
-                raise RuntimeError("the peer-memory exchange runs once over the whole model, after every "
-                                   "bucket's hook has deferred to it (weight_sync_method='sequential')")
+                raise RuntimeError("this form of the peer-memory exchange runs once over the whole model, after "
+                                   "every bucket's hook has deferred to it (weight_sync_method='sequential')")
             self._deferred.clear()
             self._peer_iteration()
             return
@@ -516,6 +624,12 @@ class GradientPath:
         """Cosine of the two half-gradients; identical on every rank (rank 0's value)."""
         if not self._sim_step:
             return None
+        if self.exchange is not None:
+            # every rank publishes its three sums, adds all ranks' in rank order, finalizes: the
+            # cosine has the same bits everywhere and no broadcast is needed
+            self.ops.exchange_cosine([self.exchange], [self.stat], [self.cos])
+            self.launches += 1
+            return self.cos
         if self.collective == "peer":              # finalised inside the exchange, identical on every rank
             return self.cos
         if self.world > 1 and self.similarity_mode == "pair_exchange":
@@ -638,6 +752,18 @@ class GradientPath:
         upd = 4 * n * per_elem + (4 * n if (similarity_step and multi) else 0)
         fused = 4 * n * (K + per_elem - 1)          # the averaged gradient stays in registers
         out = {"aggregate": agg, "update": upd, "total": agg + upd, "fused_step": fused}
+        if self.exchange is not None:
+            # one kernel; through THIS GPU's HBM: the aggregate pieces read K gradients and write the
+            # local sum; the reduce pieces read that sum once (1/n by this rank, the rest by peers) and
+            # write this rank's shard; the update pieces read the shard once from HBM (peers' reads of
+            # it are served by L2 at best), p, m [, v] and write the replicas and the state
+            w = self.world
+            out["aggregate"] = 4 * n * (K + 1)
+            out["peer_reduce"] = 4 * n + 4 * n // w
+            out["update"] = 4 * n * (per_elem - 1) + 4 * n // w
+            out["exchange"] = out["aggregate"] + out["peer_reduce"] + out["update"]
+            out["nvlink_in"] = 2 * 4 * n * (w - 1) // w
+            return out
         if self.collective == "peer":
             # what the kernels of the peer exchange move through THIS GPU's HBM: the aggregate
             # reads K gradients and writes one buffer's worth of partial sums (1/n of it locally,
@@ -655,6 +781,20 @@ class GradientPath:
         return out
 
     def close(self) -> None:
+        """Release in dependency order: captured graph (it holds the kernels and collectives of an
+        iteration), exchange handle, symmetric-memory buffers and their handles, layout, context."""
+        self._graph = None
+        self._graph_stream = None
+        if self._dyn is not None:
+            self._dyn.close()
+            self._dyn = None
+        if self.exchange is not None:
+            self.exchange.close()
+            self.exchange = None
+        for name in ("_px_h", "_pg_h", "_fl_h", "_peer_grad", "px", "pgrad", "xflags"):
+            if hasattr(self, name):
+                setattr(self, name, None)
         if self.dev_layout is not None:
             self.dev_layout.close()
+            self.dev_layout = None
         self.ctx.close()

@@ -122,10 +122,13 @@ class IIDPTrainer(object):
         # (they are only read between updates), which removes the write-back to K-1 replicas
         share_weights = kwargs.pop("share_weights", False)
         # collective="peer": several GPUs exchange gradients through this library's kernels over
-        # NVLink peer memory, once per iteration at step time (sequential weight sync only)
+        # NVLink peer memory.  peer_form="pipeline" (default): one pipelined kernel per bucket, fired
+        # by the bucket's hook chain during backward ('overlap'), or one over the whole model at step
+        # time ('sequential'); the other forms run once per iteration at step time only
         collective = kwargs.pop("collective", "nccl")
-        if collective == "peer" and self.weight_sync_method != "sequential":
-            raise NotImplementedError("collective='peer' works on the whole model at step time: "
+        peer_form = kwargs.pop("peer_form", "pipeline")
+        if collective == "peer" and peer_form != "pipeline" and self.weight_sync_method != "sequential":
+            raise NotImplementedError(f"peer_form={peer_form!r} works on the whole model at step time: "
                                       "use weight_sync_method='sequential'")
         # staging="bulk": the update kernels fetch their tiles by TMA bulk copies (same results)
         staging = kwargs.pop("staging", "register")
@@ -138,7 +141,7 @@ class IIDPTrainer(object):
                                   similarity=self._similarity_enabled(),
                                   similarity_mode=self._similarity_mode(), backend=self._backend,
                                   first_bucket_bytes=first_bucket_bytes, share_weights=share_weights,
-                                  collective=collective, staging=staging)
+                                  collective=collective, staging=staging, peer_form=peer_form)
         self._sync_buffer_barrier = [None, None]
         self.local_models = [
             IndependentIdenticalDataParallel(

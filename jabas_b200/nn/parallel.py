@@ -125,9 +125,10 @@ class VSWReducer:
                  bucket_cap_mb: float = DEFAULT_BUCKET_CAP_MB, similarity: bool = False,
                  similarity_mode: str = "fused", process_group=None, backend=None,
                  first_bucket_bytes: Optional[int] = None, share_weights: bool = False,
-                 collective: str = "nccl", staging: str = "register"):
+                 collective: str = "nccl", staging: str = "register", peer_form: str = "pipeline"):
         self.device = torch.device(device)
         self.staging = staging
+        self.peer_form = peer_form
         self.K = int(num_local_models)
         self.T = int(total_num_models)
         self.bucket_cap_mb = bucket_cap_mb
@@ -156,7 +157,8 @@ class VSWReducer:
                                        total_num_decoupled_workers=self.T, process_group=self.process_group,
                                        similarity=self.similarity, similarity_mode=self.similarity_mode,
                                        backend=self.backend, share_weights=self.share_weights,
-                                       collective=self.collective, staging=self.staging)
+                                       collective=self.collective, staging=self.staging,
+                                       peer_form=self.peer_form)
             if self.device.type == "cuda":
                 self.path_stream = torch.cuda.Stream(self.device)
         self.wrappers[k] = wrapper

@@ -105,6 +105,16 @@ class Context:
         _lib.check(self._lib.jabas_ctx_staging_timeouts(self._h, ctypes.byref(c)))
         return int(c.value)
 
+    def set_wait_limits(self, staging_ms: float = 50.0, peer_ms: float = 1000.0) -> None:
+        """Wall-time limits of the device-side waits: for a bulk copy into the shared-memory ring
+        and for another GPU's progress inside the pipelined exchange.  A wait that runs out is
+        reported (``staging_timeouts`` / ``Exchange.status``), never trapped."""
+        _lib.check(self._lib.jabas_ctx_set_wait_limits(self._h, float(staging_ms), float(peer_ms)))
+
+    def inject_staging_stall(self, on: bool) -> None:
+        """Test seam: the bulk-staged kernels' stage barriers expect more bytes than are copied."""
+        _lib.check(self._lib.jabas_ctx_inject_staging_stall(self._h, int(bool(on))))
+
     def close(self) -> None:
         if getattr(self, "_h", None):
             self._lib.jabas_ctx_destroy(self._h)
@@ -327,6 +337,104 @@ def clip_coef(ctx: Context, sumsq_stat: torch.Tensor, max_norm: float, coef_out:
                                         _stream_handle(ctx.device, stream)))
 
 
+EXCHANGE_PIECE = _lib.EXCHANGE_PIECE
+
+
+def exchange_flag_words(max_slots: int) -> int:
+    """uint32 words of one rank's flag block for an exchange with ``max_slots`` chunk slots."""
+    return int(_lib.load().jabas_exchange_flag_words(int(max_slots)))
+
+
+class Exchange:
+    """One rank's handle on the pipelined cross-GPU exchange (``jabas_exchange_*``).
+
+    ``px``, ``pg`` and ``flags`` are lists of raw device pointers, one per rank in rank order, all
+    addressable from this GPU (peer mappings for the other ranks); the flag blocks must be zero
+    before the first launch on any rank."""
+
+    def __init__(self, ctx: Context, nranks: int, rank: int, px: Sequence[int], pg: Sequence[int],
+                 flags: Sequence[int], max_slots: int, pieces_per_shard: int):
+        self.ctx, self.nranks, self.rank = ctx, int(nranks), int(rank)
+        self.max_slots, self.Q = int(max_slots), int(pieces_per_shard)
+        self.chunk_elems = self.nranks * self.Q * EXCHANGE_PIECE
+        self._px, self._pg, self._fl = _ptr_array(px), _ptr_array(pg), _ptr_array(flags)
+        desc = _lib.ExchangeDesc(self.nranks, self.rank, self._px, self._pg, self._fl, self.max_slots, self.Q)
+        h = ctypes.c_void_p()
+        _lib.check(ctx._lib.jabas_exchange_create(ctx._h, ctypes.byref(desc), ctypes.byref(h)))
+        self._h = h
+
+    def slots_for(self, n: int) -> int:
+        """Chunk slots a launch over ``n`` elements occupies."""
+        return -(-int(n) // self.chunk_elems)
+
+    def status(self):
+        """(status word, completed launches); synchronises the device.  Status 0: no wait ran out."""
+        st, la = ctypes.c_uint32(0), ctypes.c_uint32(0)
+        _lib.check(self.ctx._lib.jabas_exchange_status(self._h, ctypes.byref(st), ctypes.byref(la)))
+        return int(st.value), int(la.value)
+
+    def reset(self) -> None:
+        _lib.check(self.ctx._lib.jabas_exchange_reset(self._h))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self.ctx._lib.jabas_exchange_destroy(self._h)
+            self._h = None
+
+    def __del__(self):  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _exchange_bufs(ctx, grads, weights, m, v, stat):
+    gp = _ptr_array([_dev_f32(g, ctx.device, "grads[k]") for g in grads])
+    wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
+    b = _lib.ExchangeBufs(gp, len(grads), len(weights), wp,
+                          None if m is None else _dev_f32(m, ctx.device, "m"),
+                          None if v is None else _dev_f32(v, ctx.device, "v"), _stat_ptr(stat, ctx.device))
+    return b, (gp, wp)
+
+
+def exchange_step(exs: Sequence[Exchange], bufs: Sequence[dict], n: int, base: int, slot_base: int,
+                  divisor: float, half_divisor: float, groups: Sequence[dict], *, kind: str,
+                  layout: Optional[Layout] = None, momentum: float = 0.0, dampening: float = 0.0,
+                  nesterov: bool = False, first_step: bool = False, beta1: float = 0.9, beta2: float = 0.999,
+                  eps: float = 1e-8, dynamic: Optional["DynHp"] = None, stream=None) -> None:
+    """One launch of the pipelined exchange over elements ``[base, base + n)`` of the flat buffers.
+
+    ``exs`` / ``bufs`` hold ONE entry in production (this GPU's rank; ``bufs[i]`` is a dict with
+    ``grads`` (K flat VSW gradient buffers), ``weights`` (replicas), ``m``, ``v``, ``stat``) or
+    one entry per rank when all ranks live on this GPU (single-GPU tests of the protocol).
+    ``kind`` is ``"sgd"``, ``"adam"`` or ``"adamw"``."""
+    ctx = exs[0].ctx
+    keep, arr = [], (_lib.ExchangeBufs * len(exs))()
+    for i, b in enumerate(bufs):
+        arr[i], k = _exchange_bufs(ctx, b["grads"], b["weights"], b.get("m"), b.get("v"), b.get("stat"))
+        keep.append(k)
+    hs = _ptr_array([e._h.value for e in exs])
+    sgd = adam = None
+    if kind == "sgd":
+        sgd = ctypes.pointer(_lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), None, _dyn_ptr(dynamic), None))
+    else:
+        adam = ctypes.pointer(_lib.AdamHp(beta1, beta2, eps, int(kind == "adamw"), 0, None, _dyn_ptr(dynamic), None))
+    _lib.check(ctx._lib.jabas_exchange_step_f32(
+        hs, arr, len(exs), int(n), int(base), int(slot_base), float(divisor), float(half_divisor),
+        None if layout is None else layout._h, _groups_array(groups), len(groups), sgd, adam,
+        _stream_handle(ctx.device, stream)))
+
+
+def exchange_cosine(exs: Sequence[Exchange], stats: Sequence[torch.Tensor], cos_outs: Sequence[torch.Tensor], *,
+                    eps: float = 1e-8, stream=None) -> None:
+    """Sum the ranks' three statistic sums (rank order, identical everywhere) and finalize the cosine."""
+    ctx = exs[0].ctx
+    hs = _ptr_array([e._h.value for e in exs])
+    sp = _ptr_array([_stat_ptr(s, ctx.device) for s in stats])
+    cp = _ptr_array([_dev_f32(c, ctx.device, "cos_out") for c in cos_outs])
+    _lib.check(ctx._lib.jabas_exchange_cosine(hs, sp, cp, len(exs), eps, _stream_handle(ctx.device, stream)))
+
+
 STATIC_MAX_ELEMS = 1 << 31
 
 
@@ -358,5 +466,5 @@ def replicate(ctx: Context, src: torch.Tensor, dsts: Sequence[torch.Tensor], *, 
                                             src.numel(), _stream_handle(ctx.device, stream)))
 
 
-__all__ = ["Context", "Layout", "DynHp", "PeerGrad", "peer_reduce", "vsw_aggregate_scatter", "JabasError", "MAX_VSW", "MAX_GROUPS", "vsw_aggregate", "div_",
+__all__ = ["Context", "Layout", "DynHp", "PeerGrad", "Exchange", "exchange_step", "exchange_cosine", "exchange_flag_words", "EXCHANGE_PIECE", "peer_reduce", "vsw_aggregate_scatter", "JabasError", "MAX_VSW", "MAX_GROUPS", "vsw_aggregate", "div_",
            "sgd_momentum", "adam", "vsw_sgd_momentum", "vsw_adam", "MAX_FUSED_VSW", "sumsq", "clip_coef", "dot_norms", "dot_norms_static", "cosine_finalize", "replicate"]

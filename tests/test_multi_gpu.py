@@ -58,8 +58,12 @@ def _rank_main(rank, world, port, mode, kind, wsm, q, collective="nccl"):
             w = tr.reducer.engine.weights[K - 1].cpu()
             worst_w = max(worst_w, float(((w - wr).abs() / wr.abs().clamp_min(1e-3)).max()))
             worst_c = max(worst_c, abs(float(tr.cos_placeholder) - cos_ref))
+        if tr.reducer.engine.exchange is not None:
+            tr.reducer.engine.check_exchange()
         q.put((rank, worst_w, worst_c, tr.reducer.engine.launches))
         dist.barrier()
+        torch.cuda.synchronize()
+        tr.reducer.engine.close()
         dist.destroy_process_group()
     except Exception:  # pragma: no cover
         import traceback
@@ -69,7 +73,8 @@ def _rank_main(rank, world, port, mode, kind, wsm, q, collective="nccl"):
 @pytest.mark.parametrize("mode,kind,wsm,collective", [
     ("fused", "sgd", "overlap", "nccl"), ("pair_exchange", "sgd", "sequential", "nccl"),
     ("fused", "adamw", "overlap", "nccl"), ("fused", "adamw", "sequential", "nccl"),
-    ("fused", "sgd", "sequential", "peer"), ("fused", "adamw", "sequential", "peer")])
+    ("fused", "sgd", "sequential", "peer"), ("fused", "adamw", "sequential", "peer"),
+    ("fused", "sgd", "overlap", "peer"), ("fused", "adamw", "overlap", "peer")])
 def test_two_nccl_ranks_match_reference_path(mode, kind, wsm, collective):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -108,19 +113,18 @@ def _engine_rank(rank, world, port, collective, kind, K, q, direct=None):
         if kind == "sgd":
             opt = dict(kind="sgd", groups=[dict(lr=0.1, weight_decay=0.0), dict(lr=0.1, weight_decay=1e-4)], momentum=0.9)
         else:
-            opt = dict(kind="adamw", groups=[dict(lr=1e-3, weight_decay=0.0), dict(lr=1e-3, weight_decay=0.05)],
+            opt = dict(kind=kind, groups=[dict(lr=1e-3, weight_decay=0.0), dict(lr=1e-3, weight_decay=0.05)],
                        betas=(0.9, 0.999), eps=1e-8)
         spec = OptimizerSpec(opt["kind"], opt["groups"], momentum=opt.get("momentum", 0.0))
         idx = [[r for r in range(world) if r % 2 == p] for p in (0, 1)]
         groups = [dist.new_group(ix) for ix in idx]
         pair = dist.new_group([idx[0][0], idx[1][0]])
         T = world * K
+        form = direct or "pipeline"
+        if form == "direct" and world != 2:
+            form = "pull"                                  # the direct form exists for two ranks only
         eng = GradientPath(layout, K, torch.device("cuda", rank), spec, total_num_decoupled_workers=T,
-                           sub_group=groups[rank % 2], pair_group=pair, collective=collective)
-        if direct is not None:
-            eng.peer_direct = direct
-        if direct is False and K == 2:
-            eng.peer_form = "scatter"
+                           sub_group=groups[rank % 2], pair_group=pair, collective=collective, peer_form=form)
         ref = ReferencePath(layout, K, opt, total_num_decoupled_workers=T, arith="c")
         rng = np.random.default_rng(5)
         w0 = rng.standard_normal(layout.total).astype(np.float32)
@@ -162,23 +166,31 @@ def _engine_rank(rank, world, port, collective, kind, K, q, direct=None):
         dist.all_gather_object(sums, chk)
         if len(set(sums)) != 1:
             worst_w = float("inf")
+        if eng.exchange is not None:
+            eng.check_exchange()                           # no bounded wait ever ran out
         q.put((rank, worst_w, worst_c, eng.launches))
+        # orderly exit: the captured graph and the peer mappings go before the process group
         dist.barrier()
         torch.cuda.synchronize()
-        os._exit(0)
+        eng.close()
+        del eng
+        dist.destroy_process_group()
     except Exception:  # pragma: no cover
         import traceback
         q.put((rank, "error", traceback.format_exc(), 0))
 
 
-@pytest.mark.parametrize("collective,kind,K,direct", [("peer", "sgd", 4, None), ("peer", "adamw", 1, False),
-                                                      ("peer", "sgd", 2, False), ("nccl", "sgd", 2, None)])
+@pytest.mark.parametrize("collective,kind,K,direct", [
+    ("peer", "sgd", 4, "pipeline"), ("peer", "adamw", 2, "pipeline"), ("peer", "adam", 1, "pipeline"),
+    ("peer", "sgd", 4, "direct"), ("peer", "adamw", 1, "pull"), ("peer", "sgd", 2, "scatter"),
+    ("nccl", "sgd", 2, None)])
 def test_engine_exchange_modes_match_reference_path(collective, kind, K, direct):
     """The gradient path at engine level on 2 (or, when visible, 4) GPUs: the peer-memory
-    exchange in its forms (``direct``: the update kernel reads both ranks' sums; otherwise a
-    reduce kernel that pulls its shard from the peers — or, for the K = 2 case, local staging
-    slots filled by scattering aggregate kernels — and a gathering update kernel), eager and as a replayed CUDA graph, and
-    the NCCL exchange, against the reference path over gloo."""
+    exchange in its forms (``pipeline``: one persistent kernel with flag-ordered aggregate /
+    reduce / update pieces; ``direct``: the update kernel reads both ranks' sums; ``pull``: a
+    reduce kernel that reads its shard from the peers; ``scatter``: local staging slots filled
+    by scattering aggregate kernels), eager and as a replayed CUDA graph, and the NCCL
+    exchange, against the reference path over gloo."""
     world = 2 if torch.cuda.device_count() < 4 else 4
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

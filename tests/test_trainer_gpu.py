@@ -100,30 +100,59 @@ def test_trainer_on_gpu_matches_reference_path(wsm, kind, K, threaded, staging):
         assert tr.reducer.engine.ctx.staging_timeouts() == 0
 
 
-def test_runtime_change_of_vsw_count_on_gpu():
-    """K: 2 -> 4 -> 2 between iterations on the device: surviving flat buffers keep their
-    addresses, new replicas are filled by the replicate kernel, steps keep all replicas equal."""
+def _feed(ref, captured, lay):
+    for (k, b), t in captured.items():
+        ref.grads[k][lay.buckets[b][0]:lay.buckets[b][1]].copy_(t.cpu())
+    captured.clear()
+
+
+def _ref_with_vsws(ref, new_k, T):
+    """The oracle after a change of the VSW count: a fresh ``ReferencePath`` with ``new_k``
+    replicas that carries over the main weights, the optimizer state and the step count."""
+    from oracle.reference_path import ReferencePath
+    out = ReferencePath(ref.layout, new_k, ref.opt, total_num_decoupled_workers=T, arith="c")
+    for k in range(new_k):
+        out.weights[k].copy_(ref.weights[0])
+    out.m.copy_(ref.m); out.v.copy_(ref.v)
+    out.steps = ref.steps
+    return out
+
+
+@pytest.mark.parametrize("wsm", ["overlap", "sequential"])
+def test_runtime_change_of_vsw_count_on_gpu(wsm):
+    """K: 2 -> 4 -> 2 between iterations on the device (jabas/train/trainer.py:485-575):
+    surviving flat buffers keep their addresses, new replicas are filled by the replicate
+    kernel, and after every change the weights of all replicas and the cosine follow the
+    oracle fed with the gradients captured from the run (T and T/2 change with K)."""
     import jabas_b200
     from jabas_b200.iidp.optim import ShardSGD
-    tr = jabas_b200.JABASTrainer(0, 8, 2, 0, "overlap", dict(CFG))
+    from oracle.reference_path import ReferencePath
+    tr = jabas_b200.JABASTrainer(0, 8, 2, 0, wsm, dict(CFG))
     tr.prepare_stream_parallel(_model(), torch.nn.CrossEntropyLoss().cuda(), bucket_cap_mb=0.05,
                                first_bucket_bytes=4096)
-    tr.prepare_weight_sync_method(ShardSGD(_groups(tr.main_model), lr=0.1, momentum=0.9), None, _groups)
+    opt = (ShardSGD if wsm == "overlap" else torch.optim.SGD)(_groups(tr.main_model), lr=0.1, momentum=0.9)
+    tr.prepare_weight_sync_method(opt, None, _groups)
     tr.set_model_train()
-    eng = tr.reducer.engine
+    eng, lay = tr.reducer.engine, tr.reducer.layout
+    ref = ReferencePath(lay, 2, _opt_dict("sgd"), total_num_decoupled_workers=2, arith="c")
+    for k in range(2):
+        ref.weights[k].copy_(eng.weights[k].cpu())
     g = torch.Generator().manual_seed(2)
+    state = {"ref": ref, "captured": _capture_vsw_gradients(tr)}
 
     def one_step(K):
-        before = eng.weights[0].clone()
         x = torch.randn(8 * K, 3, 16, 16, generator=g).cuda()
         y = torch.randint(0, 10, (8 * K,), generator=g).cuda()
         tr.compute((x, y))
         assert tr.step() is True
         torch.cuda.synchronize()
-        assert not torch.equal(before, eng.weights[0])
-        for k in range(1, K):
-            assert torch.equal(eng.weights[k], eng.weights[0]), k
-        assert -1.0 <= float(tr.cos_placeholder) <= 1.0
+        assert len(state["captured"]) == K * lay.num_buckets
+        _feed(state["ref"], state["captured"], lay)
+        cos_ref = state["ref"].run_iteration()
+        assert abs(float(tr.cos_placeholder) - cos_ref) < 1e-5
+        for k in range(K):
+            assert torch.equal(eng.weights[k].cpu(), state["ref"].weights[0]), k
+        assert torch.equal(eng.m.cpu(), state["ref"].m)
 
     one_step(2)
     ptrs = (eng.weights[0].data_ptr(), eng.grads[1].data_ptr(), eng.m.data_ptr())
@@ -132,10 +161,156 @@ def test_runtime_change_of_vsw_count_on_gpu():
     assert eng.K == 4 and tr.total_num_decoupled_workers == 4
     assert (eng.weights[0].data_ptr(), eng.grads[1].data_ptr(), eng.m.data_ptr()) == ptrs
     assert torch.equal(eng.weights[3], eng.weights[0])
+    state["ref"] = _ref_with_vsws(state["ref"], 4, 4)
+    state["captured"] = _capture_vsw_gradients(tr)          # the new VSWs' hooks are wrapped too
+    one_step(4)
     one_step(4)
     tr.change_num_models(2)
     assert eng.K == 2 and eng.weights[0].data_ptr() == ptrs[0]
+    state["ref"] = _ref_with_vsws(state["ref"], 2, 2)
+    state["captured"] = _capture_vsw_gradients(tr)
     one_step(2)
+
+
+@pytest.mark.parametrize("wsm,kind", [("sequential", "sgd"), ("overlap", "adamw")])
+def test_gradient_accumulation_on_gpu(wsm, kind):
+    """accum_step = 1 (jabas/train/trainer.py:572-575, 604-612): the first micro-step only
+    accumulates into the flat gradient views (no hook fires, no kernel of the path runs), the
+    second one synchronises; T = K * (accum_step + 1).  Oracle: fed with the accumulated buckets."""
+    import jabas_b200
+    from jabas_b200.iidp.optim import ShardAdamW, ShardSGD
+    from oracle.reference_path import ReferencePath
+    K, accum = 2, 1
+    tr = jabas_b200.JABASTrainer(0, 8, K, accum, wsm, dict(CFG))
+    tr.prepare_stream_parallel(_model(), torch.nn.CrossEntropyLoss().cuda(), bucket_cap_mb=0.05,
+                               first_bucket_bytes=4096)
+    groups = _groups(tr.main_model)
+    if kind == "sgd":
+        opt = (ShardSGD if wsm == "overlap" else torch.optim.SGD)(groups, lr=0.1, momentum=0.9)
+    else:
+        opt = (ShardAdamW if wsm == "overlap" else torch.optim.AdamW)(groups, lr=1e-2)
+    tr.prepare_weight_sync_method(opt, None, _groups)
+    tr.set_model_train()
+    T = tr.total_num_decoupled_workers
+    assert T == K * (accum + 1) and tr.is_accum_mode
+    eng, lay = tr.reducer.engine, tr.reducer.layout
+    ref = ReferencePath(lay, K, _opt_dict(kind), total_num_decoupled_workers=T, arith="c")
+    for k in range(K):
+        ref.weights[k].copy_(eng.weights[k].cpu())
+    captured = _capture_vsw_gradients(tr)
+    g = torch.Generator().manual_seed(4)
+    for it in range(3):
+        launches = eng.launches
+        for micro in range(accum + 1):
+            x = torch.randn(8 * K, 3, 16, 16, generator=g).cuda()
+            y = torch.randint(0, 10, (8 * K,), generator=g).cuda()
+            tr.compute((x, y))
+            done = tr.step()
+            assert done is (micro == accum)
+            if micro < accum:
+                torch.cuda.synchronize()
+                assert not captured and eng.launches == launches      # nothing fired, nothing launched
+        torch.cuda.synchronize()
+        assert len(captured) == K * lay.num_buckets
+        _feed(ref, captured, lay)
+        cos_ref = ref.run_iteration()
+        assert abs(float(tr.cos_placeholder) - cos_ref) < 1e-5
+        for k in range(K):
+            assert torch.equal(eng.weights[k].cpu(), ref.weights[0]), (it, k)
+        # the flat gradients were zeroed for the next accumulation
+        assert float(eng.grads[1].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("kind", ["sgd", "adamw"])
+def test_checkpoint_round_trip_on_gpu(kind, tmp_path):
+    """save() after two iterations, load() into a FRESH trainer on the GPU, run iteration 3 in
+    both: bit-equal weights, optimizer state, Adam step, similarity step and LR modifier
+    (jabas/train/trainer.py:105-169, 748-799).  Also: a checkpoint whose optimizer entry is a
+    stock ``torch.optim`` state dict (the reference's format) loads into the flat buffers."""
+    import jabas_b200
+    from jabas_b200.iidp.optim import ShardAdamW, ShardSGD
+    # two trainers must compute the same bits from the same batch: deterministic convolutions
+    monkey_prev = torch.backends.cudnn.deterministic
+    torch.backends.cudnn.deterministic = True
+
+    def make(K=2):
+        tr = jabas_b200.JABASTrainer(0, 8, K, 0, "overlap", dict(CFG, enable_adjust=True))
+        tr.prepare_stream_parallel(_model(), torch.nn.CrossEntropyLoss().cuda(), bucket_cap_mb=0.05,
+                                   first_bucket_bytes=4096)
+        groups = _groups(tr.main_model)
+        opt = ShardSGD(groups, lr=0.1, momentum=0.9) if kind == "sgd" else ShardAdamW(groups, lr=1e-2)
+        tr.prepare_weight_sync_method(opt, None, _groups)
+        tr.set_model_train()
+        return tr
+
+    def batch(seed, K=2):
+        g = torch.Generator().manual_seed(seed)
+        return (torch.randn(8 * K, 3, 16, 16, generator=g).cuda(), torch.randint(0, 10, (8 * K,), generator=g).cuda())
+
+    a = make()
+    a.config_params["global_lr_modifier"] = 1.25
+    for it in range(2):
+        a.compute(batch(it)); a.step()
+    torch.cuda.synchronize()
+    path = a.save(str(tmp_path / "ckpt"))
+    b = make()
+    b.load(path)
+    assert b.similarity_state.step == a.similarity_state.step == 3
+    assert b.config_params["global_lr_modifier"] == 1.25
+    assert b.sync_step == a.sync_step == 2
+    ea, eb = a.reducer.engine, b.reducer.engine
+    assert eb.steps == ea.steps == 2
+    assert torch.equal(eb.weights[0], ea.weights[0]) and torch.equal(eb.weights[1], ea.weights[0])
+    assert torch.equal(eb.m, ea.m)
+    if kind != "sgd":
+        assert torch.equal(eb.v, ea.v)
+    # BatchNorm running statistics travel with the model state dict
+    for (na, ba), (nb_, bb) in zip(a.main_model.module.named_buffers(), b.main_model.module.named_buffers()):
+        assert na == nb_ and torch.equal(ba, bb)
+    for tr in (a, b):
+        tr.compute(batch(7)); tr.step()
+    torch.cuda.synchronize()
+    assert torch.equal(eb.weights[0], ea.weights[0]) and torch.equal(eb.weights[1], ea.weights[1])
+    assert torch.equal(eb.m, ea.m)
+    if kind != "sgd":
+        assert torch.equal(eb.v, ea.v)
+        pa, pb = a.main_model._params[0], b.main_model._params[0]
+        assert float(a.main_optimizer.state[pa]["step"]) == float(b.main_optimizer.state[pb]["step"]) == 3.0
+    assert float(a.cos_placeholder) == float(b.cos_placeholder)
+    assert a.similarity_state.step == b.similarity_state.step == 4
+
+    # the reference's format: model + a stock torch.optim state dict, trained without this library
+    torch.manual_seed(0)
+    stock = _model()
+    sgroups = _groups(stock)
+    sopt = torch.optim.SGD(sgroups, lr=0.1, momentum=0.9) if kind == "sgd" else torch.optim.AdamW(sgroups, lr=1e-2)
+    for it in range(2):
+        x, y = batch(it, K=1)
+        sopt.zero_grad()
+        torch.nn.functional.cross_entropy(stock(x), y).backward()
+        sopt.step()
+    sd = {"epoch": 1, "total_epoch_time": 0.0, "step": 2, "model": stock.state_dict(),
+          "optimizer": sopt.state_dict(), "scheduler": None, "global_batch_size": 16, "local_batch_size": 8}
+    p2 = str(tmp_path / "stock.pth")
+    torch.save(sd, p2)
+    c = make()
+    c.load(p2)
+    ec = c.reducer.engine
+    lay = c.reducer.layout
+    for p_stock, slot in zip(stock.parameters(), lay.slots):
+        sl = slice(slot.offset, slot.offset + slot.numel)
+        assert torch.equal(ec.weights[0][sl], p_stock.detach().reshape(-1))
+        assert torch.equal(ec.weights[1][sl], p_stock.detach().reshape(-1))
+        st = sopt.state[p_stock]
+        key = "momentum_buffer" if kind == "sgd" else "exp_avg"
+        assert torch.equal(ec.m[sl], st[key].reshape(-1))
+        if kind != "sgd":
+            assert torch.equal(ec.v[sl], st["exp_avg_sq"].reshape(-1))
+    assert ec.steps == 2
+    c.compute(batch(9)); c.step()                         # and training goes on from there
+    torch.cuda.synchronize()
+    assert torch.isfinite(ec.weights[0]).all()
+    torch.backends.cudnn.deterministic = monkey_prev
 
 
 def test_resnet50_two_vsws_five_iterations():
