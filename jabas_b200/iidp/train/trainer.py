@@ -132,6 +132,8 @@ class IIDPTrainer(object):
                                       "use weight_sync_method='sequential'")
         # staging="bulk": the update kernels fetch their tiles by TMA bulk copies (same results)
         staging = kwargs.pop("staging", "register")
+        # as in DistributedDataParallel: module buffers follow rank 0's main replica at every forward
+        self.broadcast_buffers = kwargs.pop("broadcast_buffers", True)
         self.criterion = criterion
         K = self.num_models
         self.model_streams = [torch.cuda.Stream(self.device) if self._cuda else None for _ in range(K)]
@@ -317,6 +319,8 @@ class IIDPTrainer(object):
             self.binding.sync_hyperparams()
         if sync:
             self.reducer.prepare_for_backward(self._is_similarity_step())
+        if getattr(self, "broadcast_buffers", True) and self.local_accum_step == 0:
+            self.reducer.sync_buffers()              # before the K streams fork off the current one
         cur = torch.cuda.current_stream(self.device) if self._cuda else None
 
         def run(k):

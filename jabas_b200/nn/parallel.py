@@ -145,6 +145,8 @@ class VSWReducer:
         self._fire_lock = threading.Lock()    # hooks fire one bucket at a time, in bucket order
         self.futures: List[torch.futures.Future] = []
         self.require_sync = True
+        self.buffers_flat: List[Optional[torch.Tensor]] = []     # one flat byte buffer of module buffers per VSW
+        self.num_module_buffers = 0
         self._reset_counters()
 
     # -- set-up -------------------------------------------------------------------------
@@ -174,8 +176,50 @@ class VSWReducer:
                 w.copy_(p.data)
                 p.data = w
         self.install_grad_views(k)
+        self._flatten_buffers(k, wrapper.module)
         for i, p in enumerate(params):
             p.register_post_accumulate_grad_hook(self._make_hook(k, self.layout.slots[i].bucket))
+
+    def _flatten_buffers(self, k: int, module: nn.Module) -> None:
+        """Module BUFFERS (BatchNorm running statistics, step counters) of VSW ``k`` become views
+        of one flat byte buffer per VSW, every buffer on a 16-byte boundary, so that all of them
+        are synchronised by one copy kernel (and one broadcast) instead of one op per buffer."""
+        named = [(n, b) for n, b in module.named_buffers() if b is not None]
+        sizes = [(b.numel() * b.element_size() + 15) // 16 * 16 for _, b in named]
+        total = max(16, sum(sizes))
+        flat = torch.zeros(total, dtype=torch.uint8, device=self.device)
+        owners = {n: (m, n.rsplit(".", 1)[-1]) for n, _ in named
+                  for m in [module.get_submodule(n.rsplit(".", 1)[0]) if "." in n else module]}
+        pos = 0
+        for (name, buf), size in zip(named, sizes):
+            nbytes = buf.numel() * buf.element_size()
+            view = flat[pos:pos + nbytes].view(buf.dtype).view(buf.shape)
+            with torch.no_grad():
+                view.copy_(buf)
+            mod, leaf = owners[name]
+            mod._buffers[leaf] = view
+            pos += size
+        while len(self.buffers_flat) <= k:
+            self.buffers_flat.append(None)
+        self.buffers_flat[k] = flat
+        self.num_module_buffers = len(named)
+
+    def sync_buffers(self, group=None) -> None:
+        """Module buffers of every VSW on every rank <- rank 0's main replica (VSW 0), the
+        ``broadcast_buffers=True`` behaviour of DistributedDataParallel that the reference's
+        patched wrapper keeps (it receives ``sync_buffer_barrier`` for exactly this step,
+        jabas/train/trainer.py:515-521, 584-588): one broadcast of the flat buffer between ranks
+        and one replicate kernel between the VSWs, on the current stream."""
+        flats = [f for f in self.buffers_flat[:self.K] if f is not None]
+        if not self.num_module_buffers or not flats:
+            return
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.broadcast(flats[0], 0, group=group)
+        if len(flats) > 1:
+            eng = self.engine
+            eng.ops.replicate(eng.ctx, flats[0].view(torch.float32), [f.view(torch.float32) for f in flats[1:]])
+            eng.launches += 1
 
     def resize(self, new_k: int, total_num_models: int) -> None:
         """Grow or shrink the set of VSWs.  Wrappers of removed VSWs are dropped here; the
@@ -186,6 +230,7 @@ class VSWReducer:
             self.wrappers.extend([None] * (new_k - self.K))
         else:
             del self.wrappers[new_k:]
+            del self.buffers_flat[new_k:]
         self.K, self.T = int(new_k), int(total_num_models)
         self.engine.set_total_workers(total_num_models)
         self._reset_counters()

@@ -420,3 +420,43 @@ def test_layout_group_must_be_provided(ctx):
     with pytest.raises(JabasError, match="param group"):
         ops.sgd_momentum(ctx, x, [x.clone()], x.clone(), [dict(lr=0.1), dict(lr=0.1)], momentum=0.9, layout=lay)
     lay.close()
+
+
+def test_bulk_staging_wait_runs_out_and_is_reported():
+    """Host-side fault injection: the stage barriers of the bulk-staged update kernel expect 16
+    bytes more than are copied, so every CTA's first wait runs out after the (lowered) wall-time
+    limit.  All copies that were issued complete, the kernel returns, the context counts the
+    time-outs and stays usable; with the injection off the same launch is bit-exact again."""
+    from jabas_b200 import ops
+    c = ops.Context(0)
+    c.set_staging("bulk")
+    c.set_wait_limits(staging_ms=2.0)
+    n, K = 2 ** 20 + 8, 2
+    rng = np.random.default_rng(12)
+    g, p = _rand(rng, n, 1e-3), _rand(rng, n)
+    dg, dm = _dev(g), torch.zeros(n, device="cuda")
+    dw = [_dev(p) for _ in range(K)]
+    groups = [dict(lr=0.1, weight_decay=1e-4)]
+    c.inject_staging_stall(True)
+    a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    ops.sgd_momentum(c, dg, dw, dm, groups, momentum=0.9, first_step=True)
+    z.record()
+    torch.cuda.synchronize()
+    assert c.staging_timeouts() > 0
+    assert a.elapsed_time(z) < 1000.0                      # bounded by time: a few waits of 2 ms per CTA
+    c.inject_staging_stall(False)
+    c.set_wait_limits(staging_ms=50.0)
+    before = c.staging_timeouts()
+    for w in dw:
+        w.copy_(torch.from_numpy(p))
+    dm.zero_()
+    ops.sgd_momentum(c, dg, dw, dm, groups, momentum=0.9, first_step=True)
+    torch.cuda.synchronize()
+    assert c.staging_timeouts() == before                  # no new time-out
+    m_o = np.zeros(n, np.float32)
+    O.sgd_momentum(g, p, m_o, lr=0.1, weight_decay=1e-4, momentum=0.9, first_step=True)
+    for w in dw:
+        assert np.array_equal(_host(w), p)
+    assert np.array_equal(_host(dm), m_o)
+    c.close()

@@ -60,6 +60,13 @@ def _rank_main(rank, world, port, mode, kind, wsm, q, collective="nccl"):
             worst_c = max(worst_c, abs(float(tr.cos_placeholder) - cos_ref))
         if tr.reducer.engine.exchange is not None:
             tr.reducer.engine.check_exchange()
+        # module buffers: after a synchronisation every VSW on every rank holds rank 0's
+        tr.reducer.sync_buffers()
+        torch.cuda.synchronize()
+        sums = [None] * world
+        dist.all_gather_object(sums, [int(f.to(torch.int64).sum()) for f in tr.reducer.buffers_flat])
+        if len({tuple(s) for s in sums}) != 1 or len(set(sums[0])) != 1:
+            worst_w = float("inf")
         q.put((rank, worst_w, worst_c, tr.reducer.engine.launches))
         dist.barrier()
         torch.cuda.synchronize()

@@ -172,6 +172,46 @@ def test_runtime_change_of_vsw_count_on_gpu(wsm):
     one_step(2)
 
 
+def test_module_buffers_follow_the_main_replica():
+    """BatchNorm running statistics and step counters of all K VSWs are views of one flat buffer
+    per VSW and are overwritten with VSW 0's at the start of every iteration (the
+    ``broadcast_buffers`` step of DistributedDataParallel that the reference keeps through
+    ``sync_buffer_barrier``, jabas/train/trainer.py:515-528), by ONE replicate kernel."""
+    import jabas_b200
+    from jabas_b200.iidp.optim import ShardSGD
+    K = 4
+    tr = jabas_b200.JABASTrainer(0, 8, K, 0, "overlap", dict(CFG))
+    tr.prepare_stream_parallel(_model(), torch.nn.CrossEntropyLoss().cuda(), bucket_cap_mb=0.05,
+                               first_bucket_bytes=4096)
+    tr.prepare_weight_sync_method(ShardSGD(_groups(tr.main_model), lr=0.1, momentum=0.9), None, _groups)
+    tr.set_model_train()
+    red = tr.reducer
+    assert red.num_module_buffers == 6 and len(red.buffers_flat) == K      # 2 BatchNorm layers x 3 buffers
+    for k in range(K):                        # the modules' buffers ARE the flat storage
+        lo = red.buffers_flat[k].data_ptr()
+        for b in tr.local_models[k].module.buffers():
+            assert lo <= b.data_ptr() < lo + red.buffers_flat[k].numel()
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(8 * K, 3, 16, 16, generator=g).cuda()
+    y = torch.randint(0, 10, (8 * K,), generator=g).cuda()
+    tr.compute((x, y)); tr.step()
+    torch.cuda.synchronize()
+    bufs = [[b.clone().cpu() for b in lm.module.buffers()] for lm in tr.local_models]
+    assert any(not torch.equal(a, b) for a, b in zip(bufs[0], bufs[1]))     # different data, different statistics
+    launches = red.engine.launches
+    red.sync_buffers()
+    torch.cuda.synchronize()
+    assert red.engine.launches == launches + 1
+    for lm in tr.local_models:                # CPU restatement: every buffer <- VSW 0's
+        for b, want in zip(lm.module.buffers(), bufs[0]):
+            assert b.dtype == want.dtype and torch.equal(b.cpu(), want)
+    # the next iteration starts from the synchronised statistics and training goes on
+    tr.compute((x, y)); tr.step()
+    torch.cuda.synchronize()
+    nbt = [int(lm.module[1].num_batches_tracked) for lm in tr.local_models]
+    assert nbt == [2] * K
+
+
 @pytest.mark.parametrize("wsm,kind", [("sequential", "sgd"), ("overlap", "adamw")])
 def test_gradient_accumulation_on_gpu(wsm, kind):
     """accum_step = 1 (jabas/train/trainer.py:572-575, 604-612): the first micro-step only

@@ -450,3 +450,38 @@ def test_threaded_compute_gives_the_same_result(wsm):
         b.compute((x, y)); b.step()
         assert torch.equal(a.reducer.engine.weights[0], b.reducer.engine.weights[K - 1]), it
         assert float(a.cos_placeholder) == float(b.cos_placeholder)
+
+
+def test_module_buffers_are_flat_views_and_follow_vsw0():
+    """Host logic of the buffer synchronisation: every module buffer of every VSW is a view of
+    that VSW's flat byte buffer (dtype and shape kept), and ``sync_buffers`` gives all VSWs the
+    main replica's values — the DistributedDataParallel ``broadcast_buffers`` step."""
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(20, 32), torch.nn.BatchNorm1d(32), torch.nn.ReLU(),
+                                torch.nn.Linear(32, 10))
+    K = 3
+    tr = jabas_b200.IIDPTrainer("cpu", 8, K, 0, "sequential")
+    tr._backend = oracle_backend
+    tr.prepare_stream_parallel(model, torch.nn.CrossEntropyLoss(), bucket_cap_mb=0.01, first_bucket_bytes=2048)
+    tr.prepare_weight_sync_method(torch.optim.SGD(tr.main_model.parameters(), lr=0.1, momentum=0.9))
+    tr.set_model_train()
+    red = tr.reducer
+    assert red.num_module_buffers == 3 and len(red.buffers_flat) == K
+    for k in range(K):
+        bn = tr.local_models[k].module[1]
+        assert bn.running_mean.dtype == torch.float32 and bn.num_batches_tracked.dtype == torch.int64
+        assert bn.running_mean.shape == (32,) and bn.num_batches_tracked.shape == ()
+        lo = red.buffers_flat[k].data_ptr()
+        for b in bn.buffers():
+            assert lo <= b.data_ptr() < lo + red.buffers_flat[k].numel() and b.data_ptr() % 16 == lo % 16
+    x, y = torch.randn(8 * K, 20), torch.randint(0, 10, (8 * K,))
+    tr.compute((x, y)); tr.step()
+    means = [lm.module[1].running_mean.clone() for lm in tr.local_models]
+    assert not torch.equal(means[0], means[1])
+    tr.compute((x, y)); tr.step()              # the next forward starts from VSW 0's statistics
+    for k in range(K):
+        assert int(tr.local_models[k].module[1].num_batches_tracked) == 2
+    red.sync_buffers()
+    for lm in tr.local_models[1:]:
+        for a, b in zip(lm.module.buffers(), tr.local_models[0].module.buffers()):
+            assert torch.equal(a, b)
