@@ -188,16 +188,16 @@ class VSWReducer:
         sizes = [(b.numel() * b.element_size() + 15) // 16 * 16 for _, b in named]
         total = max(16, sum(sizes))
         flat = torch.zeros(total, dtype=torch.uint8, device=self.device)
-        owners = {n: (m, n.rsplit(".", 1)[-1]) for n, _ in named
-                  for m in [module.get_submodule(n.rsplit(".", 1)[0]) if "." in n else module]}
         pos = 0
         for (name, buf), size in zip(named, sizes):
             nbytes = buf.numel() * buf.element_size()
             view = flat[pos:pos + nbytes].view(buf.dtype).view(buf.shape)
             with torch.no_grad():
                 view.copy_(buf)
-            mod, leaf = owners[name]
-            mod._buffers[leaf] = view
+            # same tensor object, new storage: the buffer keeps a version counter of its own (a
+            # view would share the flat buffer's, and BatchNorm's in-place update of one layer's
+            # statistics would invalidate the ones another layer saved for backward)
+            buf.data = view
             pos += size
         while len(self.buffers_flat) <= k:
             self.buffers_flat.append(None)

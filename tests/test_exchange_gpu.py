@@ -222,7 +222,9 @@ def test_exchange_wait_runs_out_when_a_rank_never_signals():
     t1.record()
     torch.cuda.synchronize()
     status, launches = exs[0].status()
-    assert status >> 31 == 1 and (status >> 24) & 0xf == 2          # gave up in the reduce phase
+    # gave up: in a reduce piece (rank 1's sums never arrive) or in an update piece whose wait for
+    # the reduced shard ran out at the same moment — whichever CTA recorded first
+    assert status >> 31 == 1 and (status >> 24) & 0xf in (2, 3)
     assert launches == 1
     assert t0.elapsed_time(t1) < 2000.0                               # bounded by time, not a hang
     # nothing was updated past the point of giving up, and the device still answers

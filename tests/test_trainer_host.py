@@ -485,3 +485,100 @@ def test_module_buffers_are_flat_views_and_follow_vsw0():
     for lm in tr.local_models[1:]:
         for a, b in zip(lm.module.buffers(), tr.local_models[0].module.buffers()):
             assert torch.equal(a, b)
+
+
+# ---------------------------------------------------------------------------------------
+# the reference's CPU-runnable configuration: ResNet-50, gloo world_size 2, K = 2, LBS 8
+# ---------------------------------------------------------------------------------------
+
+def _config1_rank(rank, world, port, iters, q):
+    try:
+        import torchvision
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+        torch.set_num_threads(max(1, (os.cpu_count() or 2) // world))
+        K, lbs = 2, 8
+        tr = jabas_b200.JABASTrainer("cpu", lbs, K, 0, "overlap", dict(CFG))
+        tr._backend = oracle_backend
+        torch.manual_seed(0)
+        tr.prepare_stream_parallel(torchvision.models.resnet50(), torch.nn.CrossEntropyLoss())   # 25 MiB buckets
+
+        def groups(m):
+            named = list(m.named_parameters())
+            return [{"params": [p for n, p in named if "bn" in n], "weight_decay": 0},
+                    {"params": [p for n, p in named if "bn" not in n], "weight_decay": 1e-4}]
+        tr.prepare_weight_sync_method(ShardSGD(groups(tr.main_model), 0.1, momentum=0.9, weight_decay=1e-4),
+                                      None, groups)
+        tr.set_model_train()
+        lay = tr.reducer.layout
+        assert lay.num_params == 25557032 and lay.bucket_sizes_mib() == [7.82, 30.04, 25.04, 25.32, 9.27]
+        assert tr.total_num_decoupled_workers == world * K
+        opt = dict(kind="sgd", groups=[dict(lr=0.1, weight_decay=0.0), dict(lr=0.1, weight_decay=1e-4)], momentum=0.9)
+        # two executions of the reference path's op sequence: stock torch CPU ops (weights), and the
+        # C oracle, whose cosine sums are fp64 — stock fp32 reductions over 25.6 M elements of real
+        # gradients (|g| ~ 200 at random init) are themselves off by up to ~1e-3 in the cosine
+        ref = ReferencePath(lay, K, opt, total_num_decoupled_workers=world * K, arith="torch")
+        ref64 = ReferencePath(lay, K, opt, total_num_decoupled_workers=world * K, arith="c")
+        for k in range(K):
+            ref.weights[k].copy_(tr.reducer.engine.weights[k])
+            ref64.weights[k].copy_(tr.reducer.engine.weights[k])
+        captured = {}
+        for k, lm in enumerate(tr.local_models):
+            def hook(state, bucket, k=k, orig=lm._hook):
+                captured[(k, bucket.index())] = bucket.buffer(materialize=False).clone()
+                return orig(state, bucket)
+            lm.register_comm_hook(lm._hook_state, hook)
+        worst_w = worst_c = 0.0
+        cosines = []
+        for it in range(iters):
+            xs, ys = [], []
+            for k in range(K):                               # seed = 1000 * rank + 10 * k + iteration
+                g = torch.Generator().manual_seed(1000 * rank + 10 * k + it)
+                xs.append(torch.randn(lbs, 3, 224, 224, generator=g))
+                ys.append(torch.randint(0, 1000, (lbs,), generator=g))
+            tr.compute((torch.cat(xs), torch.cat(ys)))
+            assert tr.step() is True
+            assert len(captured) == K * lay.num_buckets
+            for (k, b), t in captured.items():
+                ref.grads[k][lay.buckets[b][0]:lay.buckets[b][1]].copy_(t)
+                ref64.grads[k][lay.buckets[b][0]:lay.buckets[b][1]].copy_(t)
+            captured.clear()
+            cos_torch = ref.run_iteration()
+            cos_ref = ref64.run_iteration()
+            w = tr.reducer.engine.weights[K - 1]
+            for wr in (ref.weights[0], ref64.weights[0]):
+                worst_w = max(worst_w, float(((w - wr).abs() / wr.abs().clamp_min(1e-3)).max()))
+            worst_c = max(worst_c, abs(float(tr.cos_placeholder) - cos_ref))
+            assert abs(cos_torch - cos_ref) < 5e-3               # the stock fp32 reduction's own rounding
+            cosines.append(float(tr.cos_placeholder))
+        chk = int(tr.reducer.engine.weights[0].view(torch.int32).to(torch.int64).sum())
+        both = [None] * world
+        dist.all_gather_object(both, (chk, cosines))
+        q.put((rank, worst_w, worst_c, both[0] == both[1], cosines))
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:  # pragma: no cover
+        import traceback
+        q.put((rank, "error", traceback.format_exc(), False, []))
+
+
+def test_config1_resnet50_two_gloo_ranks_five_iterations():
+    """ResNet-50 (seed 0), CPU, gloo world_size 2, 2 VSWs per rank with local batch 8, N(0,1)
+    images, SGD momentum 0.9 lr 0.1 wd 1e-4 (BN parameters without decay), 25 MiB buckets,
+    statistic every iteration, 5 iterations: the trainer / hook / optimizer mirrors (device kernels
+    replaced by the oracle-backed double) against the reference path's op sequence executed with
+    stock torch CPU ops on the same ranks, fed with the gradients captured from the run."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() + 77) % 400
+    procs = [ctx.Process(target=_config1_rank, args=(r, 2, port, 5, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=900) for _ in procs]
+    for p in procs:
+        p.join(timeout=120)
+    for rank, w, c, same, cosines in res:
+        assert w != "error", c
+        assert w <= 1e-6, (rank, w)
+        assert c <= 1e-5, (rank, c)
+        assert same                                           # both ranks: same weights, same cosines
+        assert len(cosines) == 5 and all(-1.0 <= x <= 1.0 for x in cosines)
