@@ -685,6 +685,11 @@ def parity_check(D, args, layout, K, opt, collective):
     try:
         eng = build_engine(D, args, layout, K, opt, collective)
         seed_engine(D, eng, K, args.share_weights, seed_shift=31)
+        pad = torch.ones(layout.total, dtype=torch.bool, device=D.dev)
+        for b, e in layout.buckets:
+            pad[b:e] = False
+        for t in list(eng.weights) + list(eng.grads):     # padding between buckets is zero and stays zero
+            t[pad] = 0.0
         ref = ReferencePath(layout, K, opt, total_num_decoupled_workers=D.world * K, arith="c", world=D.world)
         for k in range(K):
             ref.weights[k].copy_(eng.weights[0].cpu())

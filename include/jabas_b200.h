@@ -268,11 +268,12 @@ JABAS_API int jabas_peer_reduce_f32(jabas_ctx_t* ctx, const float* const* xs, in
  * registered at jabas/train/trainer.py:327-337), the optimizer step, the weight copy to the VSW
  * replicas (jabas/train/trainer.py:530-534) and the sums of the cosine (:470-483).
  *
- * The range is cut into chunks of nranks * pieces_per_shard * JABAS_EXCHANGE_PIECE elements and
- * every chunk into nranks shards.  One persistent kernel per GPU draws work items (aggregate /
- * reduce / update pieces) from an ordered queue, so that the NVLink-bound reduce of chunk c runs
- * together with the HBM-bound aggregate of chunk c+1 and update of chunk c-1.  Ranks synchronise
- * through epoch flags stored into each other's flag blocks with plain peer stores; every wait is
+ * The range is cut into pieces of piece_elems elements, dealt to the ranks in turn (piece P is
+ * reduced by rank P mod nranks).  One persistent kernel per GPU draws work items (aggregate /
+ * reduce / update of one piece) from an ordered queue in which the reduce items of a window of
+ * pieces stand one step behind its aggregate items and one step ahead of its update items, so
+ * that NVLink-bound and HBM-bound work run together.  Ranks synchronise through per-piece epoch
+ * flags stored into each other's flag blocks with plain peer stores; every wait is
  * bounded by the context's peer wait limit (jabas_ctx_set_wait_limits) and a wait that runs out is
  * reported through jabas_exchange_status, never by a trap.  Summation order is fixed: VSWs
  * ascending, then ranks ascending with each rank's sum divided by `divisor` first; E / O of the
@@ -282,11 +283,11 @@ JABAS_API int jabas_peer_reduce_f32(jabas_ctx_t* ctx, const float* const* xs, in
  * Set-up: every rank owns three buffers that all ranks can address (peer mappings; the caller
  * allocates and exchanges them, e.g. with torch symmetric memory): `px` and `pg`, as long as the
  * flat buffers (fp32), and a flag block of jabas_exchange_flag_words(max_slots) uint32 that must be
- * zero before the first launch on ANY rank.  `max_slots` bounds slot_base + chunks of a launch;
+ * zero before the first launch on ANY rank.  `max_slots` bounds slot_base + pieces of a launch;
  * launches of one iteration that cover different ranges (one per DDP bucket) use disjoint slots.
  * Every rank must issue the same sequence of launches.  Launches of one exchange must not overlap
  * on the GPU (keep them on one stream). */
-#define JABAS_EXCHANGE_PIECE 8192u
+#define JABAS_EXCHANGE_PIECE 8192u       /* default elements of one work item, per stream */
 typedef struct jabas_exchange jabas_exchange_t;
 typedef struct {
     int nranks;                     /* 2..8 */
@@ -295,7 +296,9 @@ typedef struct {
     const float* const* pg;
     uint32_t* const* flags;
     uint32_t max_slots;
-    uint32_t pieces_per_shard;      /* Q: chunk = nranks * Q * JABAS_EXCHANGE_PIECE elements */
+    uint32_t window_pieces;         /* pieces per pipeline step; 0: sized from the launch grid */
+    uint32_t piece_elems;           /* 0: JABAS_EXCHANGE_PIECE; else a multiple of 1024 */
+    uint32_t reserved;
 } jabas_exchange_desc_t;
 
 /* Per-rank buffers of a launch.  grads: Kg VSW gradient buffers; w: K weight replicas (w[0] is the
@@ -319,7 +322,7 @@ JABAS_API int jabas_exchange_destroy(jabas_exchange_t* ex);
  * be followed by zeroing the flag blocks on every rank and a barrier: recovery after a time-out). */
 JABAS_API int jabas_exchange_reset(jabas_exchange_t* ex);
 /* Synchronous read of the status word (0 = no wait ever ran out; otherwise bit 31 set, bits 24..27
- * the phase that gave up: 2 reduce, 3 update, 4 statistic, bits 0..23 the slot) and, optionally,
+ * the phase that gave up: 2 reduce, 3 update, 4 statistic, bits 0..23 the piece slot) and, optionally,
  * of the number of completed launches. */
 JABAS_API int jabas_exchange_status(jabas_exchange_t* ex, uint32_t* status, uint32_t* launches);
 

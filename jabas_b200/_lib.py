@@ -64,7 +64,8 @@ class ExchangeDesc(ctypes.Structure):
     _fields_ = [("nranks", ctypes.c_int), ("rank", ctypes.c_int),
                 ("px", ctypes.POINTER(ctypes.c_void_p)), ("pg", ctypes.POINTER(ctypes.c_void_p)),
                 ("flags", ctypes.POINTER(ctypes.c_void_p)), ("max_slots", ctypes.c_uint32),
-                ("pieces_per_shard", ctypes.c_uint32)]
+                ("window_pieces", ctypes.c_uint32), ("piece_elems", ctypes.c_uint32),
+                ("reserved", ctypes.c_uint32)]
 
 
 class ExchangeBufs(ctypes.Structure):

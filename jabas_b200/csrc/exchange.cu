@@ -8,21 +8,22 @@
 //              gradient gathered from the owners' shards over NVLink, new
 //              weights written to all replicas                               (HBM-bound)
 //
-// The flat range is cut into chunks; every chunk into `nranks` shards (shard r is reduced by
-// rank r); every shard into Q pieces of kPieceElems elements.  A piece of one phase is one work
-// item.  Items stand in a queue ordered by pipeline step s = 0, 1, ...: step s holds the aggregate
-// items of chunk s, the reduce items of chunk s-1 and the update items of chunk s-2, interleaved
-// (one reduce item, then aggregate and update items in turn), so that at any moment the resident
-// CTAs work on NVLink-bound and HBM-bound items together and the two resources overlap.  CTAs
-// draw items with an atomic ticket, in queue order.
+// The flat range is cut into pieces of `piece` elements, dealt to the ranks in turn (piece P is
+// reduced by rank P mod n).  A piece of one phase is one work item.  Items stand in a queue
+// ordered by pipeline step s = 0, 1, ...: with windows of W pieces, step s holds the aggregate
+// items of window s, this rank's reduce items of window s-1 and the update items of window s-2,
+// interleaved (one reduce item, then aggregate and update items in turn), so that at any moment
+// the resident CTAs work on NVLink-bound and HBM-bound items together and the two resources
+// overlap.  CTAs draw items with an atomic ticket, in queue order.
 //
-// Dependencies are flags, not collectives: when the Q aggregate pieces of (chunk, shard r) are
-// done, this GPU stores the launch's epoch into rank r's flag block; a reduce item of rank r
-// waits for the n flags of its chunk; when the Q reduce pieces of a chunk are done, rank r stores
-// the epoch into every rank's flag block; an update item waits for the flag of the shard's
-// owner.  An item only ever waits for items of the previous pipeline step, and tickets are drawn
+// Dependencies are per-piece flags, not collectives: an aggregate item stores the launch's epoch
+// into the flag block of the piece's owner; the owner's reduce item waits for the n flags of its
+// piece and then stores the epoch into every rank's flag block; an update item waits for that
+// flag.  An item only ever waits for items of the previous pipeline step, and tickets are drawn
 // in order, so every item a wait depends on is already held by a running CTA on its GPU: no
-// deadlock, whatever the number of resident CTAs.  Every wait is bounded by wall time; a wait that
+// deadlock, whatever the number of resident CTAs; and a consumer's producer was drawn a whole
+// step (W-odd items) earlier, so waits are short as long as a step holds more items than there
+// are CTAs.  Every wait is bounded by wall time; a wait that
 // runs out records (phase, slot) in a status word, all CTAs of the launch drain, and the host
 // reads the status — the kernel never traps and never spins for ever.
 //
@@ -49,14 +50,13 @@ struct ExArgs {
     float* px_local;
     float* pg_local;
     unsigned int* ctrl;                 // local: queue / done / launches / status, one 128-byte line each
-    unsigned int* agg_cnt;              // local: [max_slots][kExMaxRanks] pieces done per (slot, shard)
-    unsigned int* red_cnt;              // local: [max_slots]
-    double* piece_stat;                 // local: [max_slots * Q][3]
+    double* piece_stat;                 // local: [max_slots][3], written for the pieces this rank reduces
     double* stat;                       // nullable: += this launch's (<E,O>, |E|^2, |O|^2) over this rank's shards
     const SegDev* segs;
     unsigned long long base, n;         // element range of the launch
     unsigned long long wait_ns;
-    unsigned int chunk_elems, Q, nchunks, slot_base, max_slots;
+    unsigned long long npieces;         // pieces of the launch
+    unsigned int piece, window, nsteps, slot_base, max_slots;   // piece: elements of an item; window: pieces per step
     int nseg, K, Kw, nranks, rank;
     float divisor, half_divisor;
     const UpdHp* dyn;
@@ -67,20 +67,19 @@ struct ExArgs {
 
 namespace {
 
-constexpr unsigned kPieceElems = JABAS_EXCHANGE_PIECE;   // elements of one work item, per stream
 constexpr int kExU = 2;                                  // 4-vectors per thread and inner step
 constexpr unsigned kTileVecs = kThreads * kExU;
 
 enum { CTL_QUEUE = 0, CTL_DONE = 32, CTL_LAUNCHES = 64, CTL_STATUS = 96, CTL_STAT_EPOCH = 128, CTL_WORDS = 160 };
 enum { PH_AGG = 1, PH_RED = 2, PH_UPD = 3, PH_STAT = 4 };
 
-__host__ __device__ inline size_t flag_words(unsigned max_slots) { return (size_t)max_slots * 2 * kExMaxRanks + 8 * kExMaxRanks; }
+// flag block of a rank: [max_slots][8] aggregate flags (one per source rank), [max_slots] reduce
+// flags, then (on a 32-byte boundary) 8 statistic slots of 8 words
+__host__ __device__ inline size_t stat_base(unsigned max_slots) { return ((size_t)max_slots * (kExMaxRanks + 1) + 7) / 8 * 8; }
+__host__ __device__ inline size_t flag_words(unsigned max_slots) { return stat_base(max_slots) + 8 * kExMaxRanks; }
 __device__ __forceinline__ unsigned agg_flag_idx(unsigned slot, int src) { return slot * kExMaxRanks + src; }
-__device__ __forceinline__ unsigned red_flag_idx(unsigned max_slots, unsigned slot, int src)
-{
-    return (max_slots + slot) * kExMaxRanks + src;
-}
-__device__ __forceinline__ unsigned stat_idx(unsigned max_slots, int src) { return (2 * max_slots + src) * kExMaxRanks; }
+__device__ __forceinline__ unsigned red_flag_idx(unsigned max_slots, unsigned slot) { return max_slots * kExMaxRanks + slot; }
+__device__ __forceinline__ unsigned stat_idx(unsigned max_slots, int src) { return (unsigned)stat_base(max_slots) + src * 8; }
 
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p)
 {
@@ -91,6 +90,10 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p)
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v)
 {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys(unsigned* p, unsigned v)
+{
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ unsigned ld_volatile(const unsigned* p)
 {
@@ -118,14 +121,18 @@ __device__ __forceinline__ bool wait_epoch(const unsigned* f, unsigned epoch, un
     return false;
 }
 
+// A wait ran out: record where (first one wins) and push the ticket counter past the end of the
+// queue, so that every CTA's next draw ends its loop without a per-item look at the status word.
+constexpr unsigned kQueueAbort = 0x80000000u;
 __device__ __forceinline__ void record_timeout(const ExArgs& a, int phase, unsigned slot)
 {
     atomicCAS(a.ctrl + CTL_STATUS, 0u, 0x80000000u | ((unsigned)phase << 24) | (slot & 0xffffffu));
+    atomicOr(a.ctrl + CTL_QUEUE, kQueueAbort);
 }
 
 // ---- aggregate piece: S = g_0 + ... + g_{K-1}, ascending k, undivided ---------------------
 template <int KA>
-__device__ __forceinline__ void agg_piece(const ExArgs& a, unsigned long long lo, unsigned long long hi)
+__device__ __noinline__ void agg_piece(const ExArgs& a, unsigned long long lo, unsigned long long hi)
 {
     // eight gradient streams leave registers for one 4-vector per thread and step only
     constexpr int UA = KA > 4 ? 1 : kExU;
@@ -175,62 +182,87 @@ __device__ __forceinline__ void agg_piece(const ExArgs& a, unsigned long long lo
 }
 
 // ---- reduce piece: g = sum_r fl(S_r / T) in rank order; E / O = even / odd ranks ----------
+// All but one of the NR sums come over NVLink, whose round trip is several times HBM's: every
+// thread keeps sixteen 128-bit loads in flight (UR vectors x NR ranks) before it uses the first.
 template <int NR>
-__device__ __forceinline__ void red_piece(const ExArgs& a, unsigned long long lo, unsigned long long hi, Acc3& acc)
+__device__ __noinline__ void red_piece(const ExArgs& a, unsigned long long lo, unsigned long long hi, Acc3& acc)
 {
     const int n = NR > 0 ? NR : a.nranks;
     const unsigned long long nvec = (hi - lo) >> 2;
     const bool stat = a.stat != nullptr;
-    for (unsigned long long v = threadIdx.x; v < nvec; v += kThreads) {
-        const unsigned long long off = lo + 4 * v;
-        float4 g, e, o = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (NR > 0) {
-            float4 x[NR > 0 ? NR : 1];
+    if (NR > 0) {
+        constexpr int UR = NR > 0 ? (16 / NR > 0 ? 16 / NR : 1) : 1;
+        for (unsigned long long t0 = 0; t0 < nvec; t0 += (unsigned long long)kThreads * UR) {
+            float4 x[UR][NR > 0 ? NR : 1];
 #pragma unroll
-            for (int r = 0; r < NR; ++r) x[r] = ld4(a.px[r] + off);
-            e = x[0];
-            g = div4(x[0], a.divisor);
+            for (int u = 0; u < UR; ++u) {
+                const unsigned long long v = t0 + (unsigned long long)u * kThreads + threadIdx.x;
+                if (v < nvec) {
 #pragma unroll
-            for (int r = 1; r < NR; ++r) {
-                g = add4(g, div4(x[r], a.divisor));
-                if (r == 1) o = x[1]; else if (r & 1) o = add4(o, x[r]); else e = add4(e, x[r]);
+                    for (int r = 0; r < NR; ++r) x[u][r] = ld4(a.px[r] + lo + 4 * v);
+                }
             }
-        } else {
+#pragma unroll
+            for (int u = 0; u < UR; ++u) {
+                const unsigned long long v = t0 + (unsigned long long)u * kThreads + threadIdx.x;
+                if (v >= nvec) continue;
+                float4 e = x[u][0], o = make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 g = div4(x[u][0], a.divisor);
+#pragma unroll
+                for (int r = 1; r < NR; ++r) {
+                    g = add4(g, div4(x[u][r], a.divisor));
+                    if (r == 1) o = x[u][1]; else if (r & 1) o = add4(o, x[u][r]); else e = add4(e, x[u][r]);
+                }
+                st4(a.pg_local + lo + 4 * v, g);
+                if (stat) acc_vec(acc, div4(e, a.half_divisor), div4(o, a.half_divisor));
+            }
+        }
+    } else {
+        for (unsigned long long v = threadIdx.x; v < nvec; v += kThreads) {
+            const unsigned long long off = lo + 4 * v;
             const float4 x0 = ld4(a.px[0] + off);
-            e = x0;
-            g = div4(x0, a.divisor);
+            float4 e = x0, o = make_float4(0.f, 0.f, 0.f, 0.f);
+            float4 g = div4(x0, a.divisor);
             for (int r = 1; r < n; ++r) {
                 const float4 y = ld4(a.px[r] + off);
                 g = add4(g, div4(y, a.divisor));
                 if (r == 1) o = y; else if (r & 1) o = add4(o, y); else e = add4(e, y);
             }
+            st4(a.pg_local + off, g);
+            if (stat) acc_vec(acc, div4(e, a.half_divisor), div4(o, a.half_divisor));
         }
-        st4(a.pg_local + off, g);
-        if (stat) acc_vec(acc, div4(e, a.half_divisor), div4(o, a.half_divisor));
     }
 }
 
 // ---- update piece: gradient from the owner's shard, fused optimizer step, K stores --------
 template <int OPT>
-__device__ __forceinline__ void upd_piece(const ExArgs& a, const UpdHp& H, const float* gsrc,
+__device__ __noinline__ void upd_piece(const ExArgs& a, const UpdHp& H, const float* gsrc,
                                           unsigned long long lo, unsigned long long hi)
 {
     const unsigned long long nvec = (hi - lo) >> 2;
     const bool use_m = OPT == OPT_ADAM || (H.flags & F_MOMENTUM);
     const bool load_m = OPT == OPT_ADAM || ((H.flags & F_MOMENTUM) && !(H.flags & F_FIRST));
+    // the gradient mostly comes from another GPU: its loads run one tile ahead of the local streams
+    float4 gn[kExU];
+#pragma unroll
+    for (int u = 0; u < kExU; ++u) {
+        const unsigned long long x = (unsigned long long)u * kThreads + threadIdx.x;
+        if (x < nvec) gn[u] = ld4(gsrc + lo + 4 * x);
+    }
     for (unsigned long long t0 = 0; t0 < nvec; t0 += kTileVecs) {
         float4 g[kExU], p[kExU], m[kExU], v[kExU];
 #pragma unroll
         for (int u = 0; u < kExU; ++u) {
             const unsigned long long x = t0 + (unsigned long long)u * kThreads + threadIdx.x;
             m[u] = v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            g[u] = gn[u];
             if (x < nvec) {
                 const unsigned long long off = lo + 4 * x;
-                g[u] = ld4(gsrc + off);
                 p[u] = ld4(a.w[0] + off);
                 if (load_m) m[u] = ld4(a.m + off);
                 if (OPT == OPT_ADAM) v[u] = ld4(a.v + off);
             }
+            if (x + kTileVecs < nvec) gn[u] = ld4(gsrc + lo + 4 * (x + kTileVecs));
         }
         // segment of the tile's first element, uniform over the CTA, looked up under the loads
         int seg0 = 0, gi0 = 0;
@@ -274,7 +306,7 @@ template <int OPT, int KA, int NR>
 __device__ __forceinline__ void exchange_body(const ExArgs& a, unsigned ncta)
 {
     __shared__ UpdHp H;
-    __shared__ unsigned s_ticket;
+    __shared__ unsigned s_ticket[2];
     __shared__ double s_red[3][kWarps];
     const int n = NR > 0 ? NR : a.nranks;
     if (a.dyn) {
@@ -288,49 +320,43 @@ __device__ __forceinline__ void exchange_body(const ExArgs& a, unsigned ncta)
     // when the last CTA of the launch leaves, i.e. after every CTA has read it.
     const unsigned epoch = ld_volatile(a.ctrl + CTL_LAUNCHES) + 1u;
     const unsigned group_items = 2u * (unsigned)n + 1u;
-    const unsigned step_items = a.Q * group_items;
-    const unsigned total = (a.nchunks + 2u) * step_items;
+    const unsigned groups = a.window / (unsigned)n;       // groups of a step
+    const unsigned step_items = groups * group_items;
+    const unsigned total = (a.nsteps + 2u) * step_items;
     const unsigned long long end = a.base + a.n;
     const unsigned* status = a.ctrl + CTL_STATUS;
     unsigned* flags_local = a.flags[a.rank];
-    if (threadIdx.x == 0) s_ticket = atomicAdd(a.ctrl + CTL_QUEUE, 1u);
+    if (threadIdx.x == 0) s_ticket[0] = atomicAdd(a.ctrl + CTL_QUEUE, 1u);
     __syncthreads();
-    unsigned t = s_ticket;
-    while (t < total) {
-        __syncthreads();                                  // s_ticket has been read by every thread
+    unsigned t = s_ticket[0];
+    for (unsigned it = 0; t < total; ++it) {
         unsigned nxt = 0;
         if (threadIdx.x == 0) nxt = atomicAdd(a.ctrl + CTL_QUEUE, 1u);   // in flight while this item runs
         const unsigned step = t / step_items, j = t % step_items;
         const unsigned grp = j / group_items, i = j % group_items;
         int phase;
-        unsigned piece;                                   // piece index inside the chunk
-        long long c;
-        if (i == 0) { phase = PH_RED; c = (long long)step - 1; piece = (unsigned)a.rank * a.Q + grp; }
+        long long win;                                    // window the item's piece lies in
+        unsigned idx;                                     // piece index inside the window
+        if (i == 0) { phase = PH_RED; win = (long long)step - 1; idx = grp * (unsigned)n + (unsigned)a.rank; }
         else {
             const unsigned tt = i - 1u;
-            piece = grp * (unsigned)n + (tt >> 1);
-            if (tt & 1u) { phase = PH_UPD; c = (long long)step - 2; } else { phase = PH_AGG; c = (long long)step; }
+            idx = grp * (unsigned)n + (tt >> 1);
+            if (tt & 1u) { phase = PH_UPD; win = (long long)step - 2; } else { phase = PH_AGG; win = (long long)step; }
         }
         bool ok = true;
-        if (c >= 0 && c < (long long)a.nchunks) {
-            const unsigned slot = a.slot_base + (unsigned)c;
-            const int owner = (int)(piece / a.Q);
-            unsigned long long lo = a.base + (unsigned long long)c * a.chunk_elems + (unsigned long long)piece * kPieceElems;
-            unsigned long long hi = lo + kPieceElems;
-            if (lo > end) lo = end;
+        int signal = 0;                                   // what the signalling thread publishes after the item
+        unsigned slot = 0;
+        int owner = 0;
+        const unsigned long long P = (unsigned long long)(win < 0 ? 0 : win) * a.window + idx;
+        if (win >= 0 && win < (long long)a.nsteps && P < a.npieces) {
+            slot = a.slot_base + (unsigned)P;
+            owner = (int)(P % (unsigned)n);               // pieces are dealt to the ranks in turn
+            const unsigned long long lo = a.base + P * a.piece;
+            unsigned long long hi = lo + a.piece;
             if (hi > end) hi = end;
             if (phase == PH_AGG) {
                 agg_piece<KA>(a, lo, hi);
-                __syncthreads();
-                if (threadIdx.x == 0) {
-                    __threadfence_system();
-                    unsigned* cnt = a.agg_cnt + slot * kExMaxRanks + owner;
-                    if (atomicAdd(cnt, 1u) == a.Q - 1u) {          // last piece of (chunk, shard): tell the owner
-                        *cnt = 0u;
-                        __threadfence_system();
-                        st_release_sys(a.flags[owner] + agg_flag_idx(slot, a.rank), epoch);
-                    }
-                }
+                signal = PH_AGG;
             } else if (phase == PH_RED) {
                 if (threadIdx.x < n)
                     ok = wait_epoch(flags_local + agg_flag_idx(slot, threadIdx.x), epoch, a.wait_ns, status);
@@ -341,24 +367,14 @@ __device__ __forceinline__ void exchange_body(const ExArgs& a, unsigned ncta)
                 if (a.stat) {
                     const Acc3 r = block_sum(acc, s_red);
                     if (threadIdx.x == 0) {
-                        double* ps = a.piece_stat + 3ull * ((unsigned long long)slot * a.Q + grp);
+                        double* ps = a.piece_stat + 3ull * slot;
                         ps[0] = r.d; ps[1] = r.a; ps[2] = r.b;
                     }
                 }
-                __syncthreads();
-                if (ok && threadIdx.x == 0) {
-                    __threadfence_system();
-                    unsigned* cnt = a.red_cnt + slot;
-                    if (atomicAdd(cnt, 1u) == a.Q - 1u) {          // this rank's shard of the chunk is reduced
-                        *cnt = 0u;
-                        __threadfence_system();
-                        for (int r = 0; r < n; ++r)
-                            st_release_sys(a.flags[r] + red_flag_idx(a.max_slots, slot, a.rank), epoch);
-                    }
-                }
+                if (ok) signal = PH_RED;
             } else {
                 if (threadIdx.x == 0)
-                    ok = wait_epoch(flags_local + red_flag_idx(a.max_slots, slot, owner), epoch, a.wait_ns, status);
+                    ok = wait_epoch(flags_local + red_flag_idx(a.max_slots, slot), epoch, a.wait_ns, status);
                 ok = __syncthreads_and(ok);
                 if (ok) {
                     upd_piece<OPT>(a, H, a.pg[owner], lo, hi);
@@ -367,11 +383,22 @@ __device__ __forceinline__ void exchange_body(const ExArgs& a, unsigned ncta)
                 }
             }
         }
-        if (threadIdx.x == 0) s_ticket = (!ok || ld_volatile(status) != 0u) ? 0xffffffffu : nxt;
-        __syncthreads();
-        t = s_ticket;
+        // the slot alternates, so the thread that writes the next ticket never overtakes a reader
+        if (threadIdx.x == 0) s_ticket[(it + 1) & 1] = ok ? nxt : 0xffffffffu;
+        __syncthreads();                                  // every store of the item has been issued
+        t = s_ticket[(it + 1) & 1];
+        // One thread (not the one that draws tickets and polls) publishes the piece: the release
+        // orders the CTA's stores, which the barrier made visible to it, before the flag.
+        if (threadIdx.x == 32 && signal) {
+            if (signal == PH_AGG) {
+                st_release_sys(a.flags[owner] + agg_flag_idx(slot, a.rank), epoch);
+            } else {
+                __threadfence_system();
+                for (int r = 0; r < n; ++r) st_relaxed_sys(a.flags[r] + red_flag_idx(a.max_slots, slot), epoch);
+            }
+        }
     }
-    // the last CTA to leave adds this launch's piece sums in slot order, rewinds the queue and
+    // the last CTA to leave adds this launch's piece sums in piece order, rewinds the queue and
     // advances the launch counter
     __shared__ int is_last;
     __syncthreads();
@@ -384,13 +411,11 @@ __device__ __forceinline__ void exchange_body(const ExArgs& a, unsigned ncta)
     __threadfence();
     if (a.stat) {
         Acc3 s = {0.0, 0.0, 0.0};
-        const unsigned long long first = (unsigned long long)a.slot_base * a.Q;
-        const unsigned long long cnt = (unsigned long long)a.nchunks * a.Q;
         if (ld_volatile(status) == 0u) {
-            for (unsigned long long q = threadIdx.x; q < cnt; q += kThreads) {
-                s.d += __ldcg(a.piece_stat + 3 * (first + q) + 0);
-                s.a += __ldcg(a.piece_stat + 3 * (first + q) + 1);
-                s.b += __ldcg(a.piece_stat + 3 * (first + q) + 2);
+            for (unsigned long long q = (unsigned long long)a.rank + (unsigned long long)n * threadIdx.x; q < a.npieces;
+                 q += (unsigned long long)n * kThreads) {
+                const double* ps = a.piece_stat + 3ull * (a.slot_base + q);
+                s.d += __ldcg(ps + 0); s.a += __ldcg(ps + 1); s.b += __ldcg(ps + 2);
             }
         }
         s = block_sum(s, s_red);
@@ -403,10 +428,22 @@ __device__ __forceinline__ void exchange_body(const ExArgs& a, unsigned ncta)
     }
 }
 
-// Two CTAs per SM: the update item keeps two tiles of four streams in registers.
-template <int OPT, int KA, int NR>
-__global__ void __launch_bounds__(kThreads, 2) exchange_kernel(const ExArgs a)
+// The argument block goes to shared memory once: the three piece bodies are separate functions
+// (each with a register allocation of its own — inlined together they spill) that read it
+// through a pointer.  Two CTAs per SM: an update piece keeps two tiles of its streams in registers.
+__device__ __forceinline__ void stage_args(ExArgs* dst, const ExArgs* src)
 {
+    const unsigned int* s = reinterpret_cast<const unsigned int*>(src);
+    unsigned int* d = reinterpret_cast<unsigned int*>(dst);
+    for (unsigned int i = threadIdx.x; i < sizeof(ExArgs) / 4; i += blockDim.x) d[i] = s[i];
+    __syncthreads();
+}
+
+template <int OPT, int KA, int NR>
+__global__ void __launch_bounds__(kThreads, 2) exchange_kernel(const ExArgs arg)
+{
+    __shared__ ExArgs a;
+    stage_args(&a, &arg);
     exchange_body<OPT, KA, NR>(a, gridDim.x);
 }
 
@@ -417,12 +454,7 @@ template <int OPT, int KA, int NR>
 __global__ void __launch_bounds__(kThreads, 2) exchange_emu_kernel(const ExArgs* ranks)
 {
     __shared__ ExArgs a;
-    {
-        const unsigned int* src = reinterpret_cast<const unsigned int*>(ranks + blockIdx.y);
-        unsigned int* dst = reinterpret_cast<unsigned int*>(&a);
-        for (unsigned int i = threadIdx.x; i < sizeof(ExArgs) / 4; i += blockDim.x) dst[i] = src[i];
-    }
-    __syncthreads();
+    stage_args(&a, ranks + blockIdx.y);
     exchange_body<OPT, KA, NR>(a, gridDim.x);
 }
 
@@ -494,7 +526,7 @@ __global__ void __launch_bounds__(32) exchange_cosine_emu_kernel(const ExStatArg
 struct jabas_exchange {
     jabas_ctx_t* ctx = nullptr;
     int nranks = 0, rank = 0;
-    unsigned max_slots = 0, Q = 0;
+    unsigned max_slots = 0, window = 0, piece = JABAS_EXCHANGE_PIECE;
     const float* px[kExMaxRanks] = {};
     const float* pg[kExMaxRanks] = {};
     unsigned int* flags[kExMaxRanks] = {};
@@ -554,13 +586,15 @@ int jabas_exchange_create(jabas_ctx_t* ctx, const jabas_exchange_desc_t* d, jaba
     if (d->nranks < 2 || d->nranks > kExMaxRanks) return fail(JABAS_EINVAL, "exchange: 2..8 ranks");
     if (d->rank < 0 || d->rank >= d->nranks) return fail(JABAS_EINVAL, "exchange: rank out of range");
     if (d->max_slots < 1 || d->max_slots > (1u << 20)) return fail(JABAS_EINVAL, "exchange: max_slots out of range");
-    if (d->pieces_per_shard < 1 || d->pieces_per_shard > 4096)
-        return fail(JABAS_EINVAL, "exchange: pieces_per_shard must be in [1, 4096]");
+    if (d->window_pieces > (1u << 20)) return fail(JABAS_EINVAL, "exchange: window_pieces out of range");
+    if (d->piece_elems && (d->piece_elems % 1024u || d->piece_elems > (1u << 22)))
+        return fail(JABAS_EINVAL, "exchange: piece_elems must be a multiple of 1024, at most 2^22 (0: default)");
     if (!d->px || !d->pg || !d->flags) return fail(JABAS_EINVAL, "exchange: null buffer table");
     jabas_exchange_t* ex = new (std::nothrow) jabas_exchange_t();
     if (!ex) return fail(JABAS_ENOMEM, "out of host memory");
     ex->ctx = ctx; ex->nranks = d->nranks; ex->rank = d->rank; ex->max_slots = d->max_slots;
-    ex->Q = d->pieces_per_shard;
+    ex->window = d->window_pieces;
+    ex->piece = d->piece_elems ? d->piece_elems : JABAS_EXCHANGE_PIECE;
     for (int r = 0; r < d->nranks; ++r) {
         if (!d->px[r] || !d->pg[r] || !d->flags[r] || !aligned16(d->px[r]) || !aligned16(d->pg[r]) ||
             !aligned16(d->flags[r])) {
@@ -569,9 +603,8 @@ int jabas_exchange_create(jabas_ctx_t* ctx, const jabas_exchange_desc_t* d, jaba
         }
         ex->px[r] = d->px[r]; ex->pg[r] = d->pg[r]; ex->flags[r] = d->flags[r];
     }
-    const size_t words = CTL_WORDS + (size_t)ex->max_slots * kExMaxRanks + ex->max_slots;
-    const size_t stat_off = (words * 4 + 255) / 256 * 256;
-    ex->local_bytes = stat_off + sizeof(double) * 3 * (size_t)ex->max_slots * ex->Q;
+    const size_t stat_off = ((size_t)CTL_WORDS * 4 + 255) / 256 * 256;
+    ex->local_bytes = stat_off + sizeof(double) * 3 * (size_t)ex->max_slots;
     cudaError_t e = cudaMalloc(&ex->d_local, ex->local_bytes);
     if (e == cudaSuccess) e = cudaMemset(ex->d_local, 0, ex->local_bytes);
     if (e != cudaSuccess) {
@@ -617,7 +650,7 @@ int jabas_exchange_status(jabas_exchange_t* ex, uint32_t* status, uint32_t* laun
     return JABAS_OK;
 }
 
-static int fill_args(jabas_exchange_t* ex, const jabas_exchange_bufs_t& b, ExArgs& a, uint64_t n, uint64_t base,
+static int fill_args(jabas_exchange_t* ex, unsigned grid_ctas, const jabas_exchange_bufs_t& b, ExArgs& a, uint64_t n, uint64_t base,
                      uint32_t slot_base, float divisor, float half_divisor, const jabas_layout_t* layout,
                      const jabas_group_t* groups, int ngroups, const jabas_sgd_hp_t* sgd,
                      const jabas_adam_hp_t* adam)
@@ -648,22 +681,22 @@ static int fill_args(jabas_exchange_t* ex, const jabas_exchange_bufs_t& b, ExArg
     a.px_local = const_cast<float*>(ex->px[ex->rank]);
     a.pg_local = const_cast<float*>(ex->pg[ex->rank]);
     a.ctrl = ex->d_local;
-    a.agg_cnt = ex->d_local + CTL_WORDS;
-    a.red_cnt = a.agg_cnt + (size_t)ex->max_slots * kExMaxRanks;
-    const size_t words = CTL_WORDS + (size_t)ex->max_slots * kExMaxRanks + ex->max_slots;
-    a.piece_stat = reinterpret_cast<double*>(reinterpret_cast<char*>(ex->d_local) + (words * 4 + 255) / 256 * 256);
+    a.piece_stat = reinterpret_cast<double*>(reinterpret_cast<char*>(ex->d_local) + ((size_t)CTL_WORDS * 4 + 255) / 256 * 256);
     a.base = base; a.n = n;
     a.wait_ns = (unsigned long long)(ctx->peer_wait_ms * 1e6);
-    a.Q = ex->Q;
-    const unsigned long long chunk = (unsigned long long)ex->nranks * ex->Q * kPieceElems;
-    if (chunk > 0xffffffffull) return fail(JABAS_EINVAL, "exchange: chunk too large");
-    a.chunk_elems = (unsigned)chunk;
-    const unsigned long long nchunks = (n + chunk - 1) / chunk;
-    if ((unsigned long long)slot_base + nchunks > ex->max_slots)
+    a.piece = ex->piece;
+    a.npieces = (n + ex->piece - 1) / ex->piece;
+    if ((unsigned long long)slot_base + a.npieces > ex->max_slots)
         return fail(JABAS_EINVAL, "exchange: the range needs more flag slots than the exchange was created with");
-    if ((nchunks + 2) * (unsigned long long)ex->Q * (2ull * ex->nranks + 1) >= 0xfffffff0ull)
+    // pieces per pipeline step: as asked, or so that a step holds about 1.5 items per CTA of the grid
+    unsigned long long window = ex->window;
+    if (window == 0) window = (3ull * grid_ctas * ex->nranks) / (2ull * (2ull * ex->nranks + 1));
+    window = window / ex->nranks * ex->nranks;
+    if (window < (unsigned long long)ex->nranks) window = ex->nranks;
+    const unsigned long long nsteps = (a.npieces + window - 1) / window;
+    if ((nsteps + 2) * (window / ex->nranks) * (2ull * ex->nranks + 1) >= 0x7ffffff0ull)
         return fail(JABAS_EINVAL, "exchange: too many work items for one launch");
-    a.nchunks = (unsigned)nchunks; a.slot_base = slot_base; a.max_slots = ex->max_slots;
+    a.window = (unsigned)window; a.nsteps = (unsigned)nsteps; a.slot_base = slot_base; a.max_slots = ex->max_slots;
     a.K = b.Kg; a.Kw = b.K; a.nranks = ex->nranks; a.rank = ex->rank;
     a.divisor = divisor; a.half_divisor = half_divisor;
     if (layout) {
@@ -731,10 +764,10 @@ int jabas_exchange_step_f32(jabas_exchange_t* const* exs, const jabas_exchange_b
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (nlocal == 1) {
         ExArgs a;
-        if ((rc = fill_args(ex0, bufs[0], a, n, base, slot_base, divisor, half_divisor, layout, groups, ngroups, sgd, adam)))
-            return rc;
-        const unsigned long long items = (unsigned long long)(a.nchunks + 2) * a.Q * (2ull * a.nranks + 1);
         unsigned long long grid = (unsigned long long)ctx->sm_count * per_sm;
+        if ((rc = fill_args(ex0, (unsigned)grid, bufs[0], a, n, base, slot_base, divisor, half_divisor, layout, groups, ngroups, sgd, adam)))
+            return rc;
+        const unsigned long long items = (unsigned long long)(a.nsteps + 2) * (a.window / a.nranks) * (2ull * a.nranks + 1);
         if (grid > items) grid = items;
         kern<<<(unsigned)grid, kThreads, 0, st>>>(a);
         JB_CUDA(cudaGetLastError());
@@ -742,18 +775,18 @@ int jabas_exchange_step_f32(jabas_exchange_t* const* exs, const jabas_exchange_b
     }
     // all ranks on this GPU, one launch: every CTA must be resident, because ranks wait on one another
     std::vector<ExArgs> h((size_t)nlocal);
+    const unsigned gx = (unsigned)((ctx->sm_count * per_sm) / nlocal);
+    if (gx < 1) return fail(JABAS_EINVAL, "exchange: the GPU cannot hold one CTA per rank");
     for (int r = 0; r < nlocal; ++r) {
         if (!exs[r] || exs[r]->ctx != ctx || exs[r]->nranks != nlocal || exs[r]->rank != r)
             return fail(JABAS_EINVAL, "exchange: the single-GPU form takes the ranks 0..n-1 of one context, in order");
         if (bufs[r].Kg != bufs[0].Kg) return fail(JABAS_EINVAL, "exchange: every rank must have the same number of VSWs here");
-        if ((rc = fill_args(exs[r], bufs[r], h[r], n, base, slot_base, divisor, half_divisor, layout, groups, ngroups, sgd, adam)))
+        if ((rc = fill_args(exs[r], gx, bufs[r], h[r], n, base, slot_base, divisor, half_divisor, layout, groups, ngroups, sgd, adam)))
             return rc;
     }
     if (!ex0->d_emu) JB_CUDA(cudaMalloc(&ex0->d_emu, sizeof(ExArgs) * kExMaxRanks));
     JB_CUDA(cudaMemcpyAsync(ex0->d_emu, h.data(), sizeof(ExArgs) * nlocal, cudaMemcpyHostToDevice, st));
     JB_CUDA(cudaStreamSynchronize(st));          // h leaves scope; this form is for tests
-    unsigned gx = (unsigned)((ctx->sm_count * per_sm) / nlocal);
-    if (gx < 1) return fail(JABAS_EINVAL, "exchange: the GPU cannot hold one CTA per rank");
     emu<<<dim3(gx, (unsigned)nlocal), kThreads, 0, st>>>(ex0->d_emu);
     JB_CUDA(cudaGetLastError());
     return JABAS_OK;

@@ -61,7 +61,8 @@ class GradientPath:
                  pair_group=None, first_subgroup_src_rank: int = 0, second_subgroup_src_rank: int = 1,
                  similarity: bool = True, similarity_mode: str = "fused", backend=None,
                  collective: str = "nccl", share_weights: bool = False, staging: str = "register",
-                 peer_form: str = "pipeline", peer_wait_ms: Optional[float] = None):
+                 peer_form: str = "pipeline", peer_wait_ms: Optional[float] = None,
+                 exchange_piece: Optional[int] = None, exchange_window: Optional[int] = None):
         if backend is None:
             from . import ops as backend          # the CUDA library; raises without a GPU
         self.ops = backend
@@ -132,6 +133,8 @@ class GradientPath:
         if self.peer_direct and self.world != 2 and self.collective == "peer":
             raise ValueError("peer_form='direct' needs exactly two ranks")
         self.exchange = None
+        self.exchange_piece = exchange_piece          # elements of one work item of the pipelined exchange
+        self.exchange_window = exchange_window        # pieces per pipeline step (None: sized from the grid)
         if self.collective == "peer":
             if self.peer_form == "pipeline":
                 self._setup_pipeline_exchange()
@@ -192,18 +195,22 @@ class GradientPath:
         """Buffers of the pipelined exchange, all of them symmetric (allocated and exchanged by
         torch symmetric memory, addressed by this library's kernels): ``px`` takes this rank's
         undivided local sum, ``pgrad`` the shards of the averaged gradient this rank reduces, and
-        a block of epoch flags that the other ranks store into.  Chunks of about 2^20 elements."""
+        a block of per-piece epoch flags that the other ranks store into."""
         import torch.distributed._symmetric_memory as symm_mem
         n, world = self.layout.total, self.world
         if world > 8:
             raise ValueError("the pipelined exchange serves up to 8 ranks (one NVSwitch domain)")
         group = self.pg if self.pg is not None else dist.group.WORLD
-        piece = self.ops.EXCHANGE_PIECE
-        q = max(1, (1 << 20) // (world * piece))
-        chunk = world * q * piece
-        per_bucket = [-(-self._bucket_span(b)[1] // chunk) for b in range(self.layout.num_buckets)]
+        import os
+        # tuning knobs (environment, for sweeps): elements per work item, pieces per pipeline step
+        piece = int(self.exchange_piece or os.environ.get("JABAS_EXCHANGE_PIECE", 0) or self.ops.EXCHANGE_PIECE)
+        if self.exchange_window is None and os.environ.get("JABAS_EXCHANGE_SLACK"):
+            sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+            slack = float(os.environ["JABAS_EXCHANGE_SLACK"])
+            self.exchange_window = max(world, int(slack * 2 * sms * world / (2 * world + 1)) // world * world)
+        per_bucket = [-(-self._bucket_span(b)[1] // piece) for b in range(self.layout.num_buckets)]
         self._slot_base = [sum(per_bucket[:b]) for b in range(len(per_bucket))]
-        max_slots = max(-(-n // chunk), sum(per_bucket), 1)
+        max_slots = max(-(-n // piece), sum(per_bucket), 1)
         words = self.ops.exchange_flag_words(max_slots)
         self.px = symm_mem.empty(n, dtype=torch.float32, device=self.device)
         self.pgrad = symm_mem.empty(n, dtype=torch.float32, device=self.device)
@@ -217,7 +224,8 @@ class GradientPath:
         self.exchange = self.ops.Exchange(self.ctx, world, self.rank,
                                           [int(p) for p in self._px_h.buffer_ptrs],
                                           [int(p) for p in self._pg_h.buffer_ptrs],
-                                          [int(p) for p in self._fl_h.buffer_ptrs], max_slots, q)
+                                          [int(p) for p in self._fl_h.buffer_ptrs], max_slots, int(self.exchange_window or 0),
+                                          piece)
 
     def _bucket_span(self, b: Optional[int]):
         """(first element, length) of a launch over bucket ``b`` (None: the whole flat buffer); a

@@ -341,7 +341,7 @@ EXCHANGE_PIECE = _lib.EXCHANGE_PIECE
 
 
 def exchange_flag_words(max_slots: int) -> int:
-    """uint32 words of one rank's flag block for an exchange with ``max_slots`` chunk slots."""
+    """uint32 words of one rank's flag block for an exchange with ``max_slots`` piece slots."""
     return int(_lib.load().jabas_exchange_flag_words(int(max_slots)))
 
 
@@ -353,19 +353,19 @@ class Exchange:
     before the first launch on any rank."""
 
     def __init__(self, ctx: Context, nranks: int, rank: int, px: Sequence[int], pg: Sequence[int],
-                 flags: Sequence[int], max_slots: int, pieces_per_shard: int):
+                 flags: Sequence[int], max_slots: int, window_pieces: int = 0, piece_elems: int = EXCHANGE_PIECE):
         self.ctx, self.nranks, self.rank = ctx, int(nranks), int(rank)
-        self.max_slots, self.Q = int(max_slots), int(pieces_per_shard)
-        self.chunk_elems = self.nranks * self.Q * EXCHANGE_PIECE
+        self.max_slots, self.window, self.piece = int(max_slots), int(window_pieces), int(piece_elems)
         self._px, self._pg, self._fl = _ptr_array(px), _ptr_array(pg), _ptr_array(flags)
-        desc = _lib.ExchangeDesc(self.nranks, self.rank, self._px, self._pg, self._fl, self.max_slots, self.Q)
+        desc = _lib.ExchangeDesc(self.nranks, self.rank, self._px, self._pg, self._fl, self.max_slots, self.window,
+                                 self.piece, 0)
         h = ctypes.c_void_p()
         _lib.check(ctx._lib.jabas_exchange_create(ctx._h, ctypes.byref(desc), ctypes.byref(h)))
         self._h = h
 
     def slots_for(self, n: int) -> int:
-        """Chunk slots a launch over ``n`` elements occupies."""
-        return -(-int(n) // self.chunk_elems)
+        """Piece slots a launch over ``n`` elements occupies."""
+        return -(-int(n) // self.piece)
 
     def status(self):
         """(status word, completed launches); synchronises the device.  Status 0: no wait ran out."""

@@ -15,13 +15,12 @@ from oracle import gradpath as O
 
 pytestmark = pytest.mark.gpu
 
-PIECE = 8192
+PIECE = 8192          # a small work item keeps the multi-chunk cases small
 
 
-def _setup(ops, ctx, n_ranks, K, total, q, max_slots=None, seed=0, kw=2):
+def _setup(ops, ctx, n_ranks, K, total, window, max_slots=None, seed=0, kw=2):
     rng = np.random.default_rng(seed)
-    chunk = n_ranks * q * PIECE
-    max_slots = max_slots or max(1, -(-total // chunk)) + 4
+    max_slots = max_slots or max(1, -(-total // PIECE)) + 4
     words = ops.exchange_flag_words(max_slots)
     dev = ctx.device
     f32 = dict(dtype=torch.float32, device=dev)
@@ -29,7 +28,7 @@ def _setup(ops, ctx, n_ranks, K, total, q, max_slots=None, seed=0, kw=2):
     pg = [torch.zeros(total, **f32) for _ in range(n_ranks)]
     fl = [torch.zeros(words, dtype=torch.int32, device=dev) for _ in range(n_ranks)]
     exs = [ops.Exchange(ctx, n_ranks, r, [t.data_ptr() for t in px], [t.data_ptr() for t in pg],
-                        [t.data_ptr() for t in fl], max_slots, q) for r in range(n_ranks)]
+                        [t.data_ptr() for t in fl], max_slots, window, PIECE) for r in range(n_ranks)]
     w0 = rng.standard_normal(total).astype(np.float32)
     ranks = []
     for r in range(n_ranks):
@@ -102,20 +101,21 @@ def ctx():
     c.close()
 
 
-@pytest.mark.parametrize("n_ranks,K,kind,total,q", [
-    (2, 4, "sgd", 3 * 2 * 8192 + 4096 + 8, 1),      # 3 chunks and a ragged one, Q = 1
-    (2, 1, "adamw", 40, 2),                         # less than one piece
-    (4, 2, "sgd", 5 * 4 * 2 * 8192 + 12, 2),        # 5 chunks + 12 elements, Q = 2
-    (4, 3, "adamw", 2 * 4 * 8192 + 8192 * 3, 1),    # generic K, last chunk covers three shards only
-    (8, 4, "sgd", 4 * 8 * 8192 + 5 * 8192 + 100, 1),
-    (8, 8, "adamw", 2 * 8 * 2 * 8192 + 4, 2),
-    (8, 2, "adam", 8 * 8192, 1),
-    (6, 2, "sgd", 3 * 6 * 8192 + 64, 1),            # generic rank count
-    (2, 16, "sgd", 2 * 8192 + 256, 1),              # generic K = 16
+@pytest.mark.parametrize("n_ranks,K,kind,total,window", [
+    (2, 4, "sgd", 3 * 2 * 8192 + 4096 + 8, 2),      # 4 steps of one group, ragged last piece
+    (2, 1, "adamw", 40, 4),                         # less than one piece
+    (4, 2, "sgd", 5 * 4 * 2 * 8192 + 12, 8),        # 5 full windows of two groups + 12 elements
+    (4, 3, "adamw", 2 * 4 * 8192 + 8192 * 3, 4),    # generic K, last window holds three pieces only
+    (8, 4, "sgd", 4 * 8 * 8192 + 5 * 8192 + 100, 8),
+    (8, 8, "adamw", 2 * 8 * 2 * 8192 + 4, 16),
+    (8, 2, "adam", 8 * 8192, 0),                    # window sized from the grid: one step
+    (6, 2, "sgd", 3 * 6 * 8192 + 64, 6),            # generic rank count
+    (2, 16, "sgd", 2 * 8192 + 256, 2),              # generic K = 16
+    (4, 4, "sgd", 150 * 8192 + 1024, 0),            # many pieces, automatic window
 ])
-def test_exchange_single_gpu_all_ranks_bit_exact(ctx, n_ranks, K, kind, total, q):
+def test_exchange_single_gpu_all_ranks_bit_exact(ctx, n_ranks, K, kind, total, window):
     from jabas_b200 import ops
-    exs, ranks, keep, w0, rng = _setup(ops, ctx, n_ranks, K, total, q, seed=n_ranks * 100 + K)
+    exs, ranks, keep, w0, rng = _setup(ops, ctx, n_ranks, K, total, window, seed=n_ranks * 100 + K)
     T = n_ranks * K
     # two param groups in alternating runs of odd length: tiles straddle segment boundaries
     segments, pos, gi = [], 0, 0
@@ -149,19 +149,17 @@ def test_exchange_single_gpu_all_ranks_bit_exact(ctx, n_ranks, K, kind, total, q
             g_exp, stat = _expected(host, T, "adam", common, gs, segments, w, m, v)
         cos_exp = O.cosine_from_stat(stat)
         px, pg, _ = keep
-        chunk = n_ranks * q * PIECE
-        shard = q * PIECE
         for r, rk in enumerate(ranks):
             for k, wt in enumerate(rk["weights"]):
                 assert np.array_equal(wt.cpu().numpy(), w), (step, r, k)
             assert np.array_equal(rk["m"].cpu().numpy(), m), (step, r)
             if kind != "sgd":
                 assert np.array_equal(rk["v"].cpu().numpy(), v), (step, r)
-            # this rank's shards of the averaged gradient
+            # the pieces of the averaged gradient that this rank reduces (dealt in turn)
             got = pg[r].cpu().numpy()
-            for c0 in range(0, total, chunk):
-                lo, hi = min(total, c0 + r * shard), min(total, c0 + (r + 1) * shard)
-                assert np.array_equal(got[lo:hi], g_exp[lo:hi]), (step, r, c0)
+            for P in range(r, -(-total // PIECE), n_ranks):
+                lo, hi = P * PIECE, min(total, (P + 1) * PIECE)
+                assert np.array_equal(got[lo:hi], g_exp[lo:hi]), (step, r, P)
             st = rk["stat"].cpu().numpy()
             _close_stat(st, stat)
             assert abs(float(rk["cos"]) - cos_exp) <= 1e-5
@@ -176,11 +174,11 @@ def test_exchange_per_bucket_launches_share_one_statistic(ctx):
     """Launches over disjoint ranges with disjoint slots, as the comm hooks issue them per DDP
     bucket, followed by one statistic exchange: same result as one launch over everything."""
     from jabas_b200 import ops
-    n_ranks, K, q = 4, 2, 1
-    chunk = n_ranks * q * PIECE
+    n_ranks, K = 4, 2
+    chunk = n_ranks * PIECE
     spans = [(0, chunk + 4096), (chunk + 4096, 3 * chunk + 32), (4 * chunk + 4128, 512)]
     total = spans[-1][0] + spans[-1][1]
-    exs, ranks, keep, w0, rng = _setup(ops, ctx, n_ranks, K, total, q, max_slots=16, seed=9)
+    exs, ranks, keep, w0, rng = _setup(ops, ctx, n_ranks, K, total, 4, max_slots=32, seed=9)
     T = n_ranks * K
     groups = [dict(lr=0.1, weight_decay=1e-4)]
     w, m, v = w0.copy(), np.zeros(total, np.float32), np.zeros(total, np.float32)
@@ -191,7 +189,7 @@ def test_exchange_per_bucket_launches_share_one_statistic(ctx):
         slot = 0
         for base, length in spans:
             _run(ops, exs, ranks, length, base, slot, T, "sgd", groups, None, step)
-            slot += -(-length // chunk)
+            slot += -(-length // PIECE)
         ops.exchange_cosine(exs, [r["stat"] for r in ranks], [r["cos"] for r in ranks])
         torch.cuda.synchronize()
         assert all(ex.status()[0] == 0 for ex in exs)
@@ -212,8 +210,8 @@ def test_exchange_wait_runs_out_when_a_rank_never_signals():
     from jabas_b200 import ops
     c = ops.Context(0)
     c.set_wait_limits(peer_ms=5.0)
-    n_ranks, K, q, total = 2, 2, 1, 3 * 2 * 8192
-    exs, ranks, keep, w0, rng = _setup(ops, c, n_ranks, K, total, q, seed=3)
+    n_ranks, K, total = 2, 2, 3 * 2 * 8192
+    exs, ranks, keep, w0, rng = _setup(ops, c, n_ranks, K, total, 2, seed=3)
     _fill_grads(ranks, rng, total)
     groups = [dict(lr=0.1, weight_decay=0.0)]
     t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
@@ -254,7 +252,7 @@ def test_exchange_wait_runs_out_when_a_rank_never_signals():
 
 def test_exchange_rejects_bad_arguments(ctx):
     from jabas_b200 import ops
-    exs, ranks, keep, w0, rng = _setup(ops, ctx, 2, 2, 4096, 1, max_slots=1)
+    exs, ranks, keep, w0, rng = _setup(ops, ctx, 2, 2, 4096, 2, max_slots=1)
     groups = [dict(lr=0.1, weight_decay=0.0)]
     with pytest.raises(ops.JabasError):                      # n not a multiple of 4
         _run(ops, exs, ranks, 4094, 0, 0, 4, "sgd", groups, None, 0)
@@ -262,7 +260,7 @@ def test_exchange_rejects_bad_arguments(ctx):
         _run(ops, exs, ranks, 4096, 0, 1, 4, "sgd", groups, None, 0)
     with pytest.raises(ops.JabasError):                      # neither one rank nor all of them
         bad = ops.Exchange(ctx, 4, 0, [t.data_ptr() for t in keep[0]] * 2, [t.data_ptr() for t in keep[1]] * 2,
-                           [t.data_ptr() for t in keep[2]] * 2, 1, 1)
+                           [t.data_ptr() for t in keep[2]] * 2, 1, 0, PIECE)
         _run(ops, [bad, bad], ranks, 4096, 0, 0, 4, "sgd", groups, None, 0)
     for ex in exs:
         ex.close()
