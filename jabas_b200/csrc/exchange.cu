@@ -32,6 +32,7 @@
 // gradients and weights.  Plain peer loads and stores only: no multicast, no TMA.
 #include "common.cuh"
 
+#include <algorithm>
 #include <new>
 #include <vector>
 
@@ -58,6 +59,8 @@ struct ExArgs {
     unsigned long long npieces;         // pieces of the launch
     unsigned int piece, window, nsteps, slot_base, max_slots;   // piece: elements of an item; window: pieces per step
     int nseg, K, Kw, nranks, rank;
+    int opt;                            // OPT_SGD / OPT_ADAM
+    int ring_stages, ring_slots;        // shared-memory ring: stages, and 4 KB stream slots per stage
     float divisor, half_divisor;
     const UpdHp* dyn;
     UpdHp hp;
@@ -67,11 +70,25 @@ struct ExArgs {
 
 namespace {
 
-constexpr int kExU = 2;                                  // 4-vectors per thread and inner step
-constexpr unsigned kTileVecs = kThreads * kExU;
+// A CTA is 8 consumer warps and one producer warp.  The producer (one lane) draws tickets, waits
+// for the item's flags and brings the item on chip tile by tile with bulk copies (TMA, no
+// multicast; the source may be another GPU's memory) into a ring of shared-memory stages; it runs
+// up to a ring ahead of the consumers, ACROSS items, so neither the flag polls nor the first-byte
+// latency of an item (several microseconds over NVLink) ever leave the memory pipes idle.  The
+// consumers read a stage into registers, free it, do the arithmetic and the stores, and publish
+// the item's flag after its last tile — independently of the producer, which may by then be
+// blocked on a flag of a later item (so that wait can never stall what it waits for).
+constexpr int kConsumers = kThreads;                     // 256
+constexpr int kExThreads = kThreads + 32;                // + the producer warp
+constexpr int kTileVecs = kThreads;                      // one 4-vector per consumer thread and stream
+constexpr unsigned kTileBytes = kTileVecs * 16;          // 4 KB per stream and stage
+constexpr unsigned kTileElems = kTileVecs * 4;
+constexpr int kExMaxStages = 8;
+constexpr int kExMaxSlots = 8;                           // streams of a stage: K gradients, n sums, or g/p/m/v
+constexpr int kRingBudgetBytes = 96 * 1024;              // dynamic shared memory per CTA (two CTAs per SM)
 
 enum { CTL_QUEUE = 0, CTL_DONE = 32, CTL_LAUNCHES = 64, CTL_STATUS = 96, CTL_STAT_EPOCH = 128, CTL_WORDS = 160 };
-enum { PH_AGG = 1, PH_RED = 2, PH_UPD = 3, PH_STAT = 4 };
+enum { PH_STOP = 0, PH_AGG = 1, PH_RED = 2, PH_UPD = 3, PH_STAT = 4, PH_RING = 5 };
 
 // flag block of a rank: [max_slots][8] aggregate flags (one per source rank), [max_slots] reduce
 // flags, then (on a 32-byte boundary) 8 statistic slots of 8 words
@@ -87,6 +104,13 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p)
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ unsigned ld_relaxed_sys(const unsigned* p)
+{
+    unsigned v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v)
 {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -99,6 +123,8 @@ __device__ __forceinline__ unsigned ld_volatile(const unsigned* p)
 {
     return *reinterpret_cast<const volatile unsigned*>(p);
 }
+// barrier among the 256 consumer threads only (the producer warp never joins it)
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // true once *f has reached `epoch`; false when `limit_ns` of wall time passed first (or another
 // CTA of the launch already gave up).  The poll count is capped as well, so the loop ends even
@@ -121,8 +147,29 @@ __device__ __forceinline__ bool wait_epoch(const unsigned* f, unsigned epoch, un
     return false;
 }
 
-// A wait ran out: record where (first one wins) and push the ticket counter past the end of the
-// queue, so that every CTA's next draw ends its loop without a per-item look at the status word.
+// All n flags of a piece: the polls of one round are issued back to back (relaxed), one fence
+// orders the data reads behind them once every flag has been seen.
+__device__ __forceinline__ bool wait_epoch_n(const unsigned* f, int n, unsigned epoch, unsigned long long limit_ns,
+                                             const unsigned* status)
+{
+    unsigned long long t0 = 0;
+    for (unsigned long long polls = 0;; ++polls) {
+        bool all = true;
+#pragma unroll
+        for (int r = 0; r < kExMaxRanks; ++r)
+            if (r < n) all = all && ((int)(ld_relaxed_sys(f + r) - epoch) >= 0);
+        if (all) { fence_acq_rel_sys(); return true; }
+        if (polls == 0) t0 = gtime_ns();
+        __nanosleep(40);
+        if ((polls & 7) == 7) {
+            if (gtime_ns() - t0 > limit_ns || polls > limit_ns / 64 + 4096) return false;
+            if (ld_volatile(status) != 0u) return false;
+        }
+    }
+}
+
+// A wait ran out: record where (first one wins) and set the top bit of the ticket counter, so
+// that every later draw lies past the end of the queue.
 constexpr unsigned kQueueAbort = 0x80000000u;
 __device__ __forceinline__ void record_timeout(const ExArgs& a, int phase, unsigned slot)
 {
@@ -130,295 +177,300 @@ __device__ __forceinline__ void record_timeout(const ExArgs& a, int phase, unsig
     atomicOr(a.ctrl + CTL_QUEUE, kQueueAbort);
 }
 
-// ---- aggregate piece: S = g_0 + ... + g_{K-1}, ascending k, undivided ---------------------
-template <int KA>
-__device__ __noinline__ void agg_piece(const ExArgs& a, unsigned long long lo, unsigned long long hi)
-{
-    // eight gradient streams leave registers for one 4-vector per thread and step only
-    constexpr int UA = KA > 4 ? 1 : kExU;
-    const unsigned long long nvec = (hi - lo) >> 2;
-    for (unsigned long long t0 = 0; t0 < nvec; t0 += (unsigned long long)kThreads * UA) {
-        if (KA > 0) {
-            float4 x[UA][KA > 0 ? KA : 1];
-#pragma unroll
-            for (int u = 0; u < UA; ++u) {
-                const unsigned long long v = t0 + (unsigned long long)u * kThreads + threadIdx.x;
-                if (v < nvec) {
-#pragma unroll
-                    for (int k = 0; k < KA; ++k) x[u][k] = ld4(a.gk[k] + lo + 4 * v);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < UA; ++u) {
-                const unsigned long long v = t0 + (unsigned long long)u * kThreads + threadIdx.x;
-                if (v < nvec) {
-                    float4 s = x[u][0];
-#pragma unroll
-                    for (int k = 1; k < KA; ++k) s = add4(s, x[u][k]);
-                    st4(a.px_local + lo + 4 * v, s);
-                }
-            }
-        } else {
-            float4 s[UA];
-#pragma unroll
-            for (int u = 0; u < UA; ++u) {
-                const unsigned long long v = t0 + (unsigned long long)u * kThreads + threadIdx.x;
-                if (v < nvec) s[u] = ld4(a.gk[0] + lo + 4 * v);
-            }
-            for (int k = 1; k < a.K; ++k) {
-#pragma unroll
-                for (int u = 0; u < UA; ++u) {
-                    const unsigned long long v = t0 + (unsigned long long)u * kThreads + threadIdx.x;
-                    if (v < nvec) s[u] = add4(s[u], ld4(a.gk[k] + lo + 4 * v));
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < UA; ++u) {
-                const unsigned long long v = t0 + (unsigned long long)u * kThreads + threadIdx.x;
-                if (v < nvec) st4(a.px_local + lo + 4 * v, s[u]);
-            }
-        }
-    }
-}
+struct TileDesc {
+    unsigned long long lo;      // first element of the tile in the flat buffers
+    unsigned nvec;              // 4-vectors in the tile (<= 256)
+    int phase;                  // PH_STOP ends the consumers' loop
+    int owner;
+    unsigned slot;
+    int last;                   // last tile of its item
+    int pad;
+};
 
-// ---- reduce piece: g = sum_r fl(S_r / T) in rank order; E / O = even / odd ranks ----------
-// All but one of the NR sums come over NVLink, whose round trip is several times HBM's: every
-// thread keeps sixteen 128-bit loads in flight (UR vectors x NR ranks) before it uses the first.
-template <int NR>
-__device__ __noinline__ void red_piece(const ExArgs& a, unsigned long long lo, unsigned long long hi, Acc3& acc)
-{
-    const int n = NR > 0 ? NR : a.nranks;
-    const unsigned long long nvec = (hi - lo) >> 2;
-    const bool stat = a.stat != nullptr;
-    if (NR > 0) {
-        constexpr int UR = NR > 0 ? (16 / NR > 0 ? 16 / NR : 1) : 1;
-        for (unsigned long long t0 = 0; t0 < nvec; t0 += (unsigned long long)kThreads * UR) {
-            float4 x[UR][NR > 0 ? NR : 1];
-#pragma unroll
-            for (int u = 0; u < UR; ++u) {
-                const unsigned long long v = t0 + (unsigned long long)u * kThreads + threadIdx.x;
-                if (v < nvec) {
-#pragma unroll
-                    for (int r = 0; r < NR; ++r) x[u][r] = ld4(a.px[r] + lo + 4 * v);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < UR; ++u) {
-                const unsigned long long v = t0 + (unsigned long long)u * kThreads + threadIdx.x;
-                if (v >= nvec) continue;
-                float4 e = x[u][0], o = make_float4(0.f, 0.f, 0.f, 0.f);
-                float4 g = div4(x[u][0], a.divisor);
-#pragma unroll
-                for (int r = 1; r < NR; ++r) {
-                    g = add4(g, div4(x[u][r], a.divisor));
-                    if (r == 1) o = x[u][1]; else if (r & 1) o = add4(o, x[u][r]); else e = add4(e, x[u][r]);
-                }
-                st4(a.pg_local + lo + 4 * v, g);
-                if (stat) acc_vec(acc, div4(e, a.half_divisor), div4(o, a.half_divisor));
-            }
-        }
-    } else {
-        for (unsigned long long v = threadIdx.x; v < nvec; v += kThreads) {
-            const unsigned long long off = lo + 4 * v;
-            const float4 x0 = ld4(a.px[0] + off);
-            float4 e = x0, o = make_float4(0.f, 0.f, 0.f, 0.f);
-            float4 g = div4(x0, a.divisor);
-            for (int r = 1; r < n; ++r) {
-                const float4 y = ld4(a.px[r] + off);
-                g = add4(g, div4(y, a.divisor));
-                if (r == 1) o = y; else if (r & 1) o = add4(o, y); else e = add4(e, y);
-            }
-            st4(a.pg_local + off, g);
-            if (stat) acc_vec(acc, div4(e, a.half_divisor), div4(o, a.half_divisor));
-        }
-    }
-}
+struct ExShared {
+    ExArgs a;
+    UpdHp H;
+    unsigned long long full[kExMaxStages];
+    unsigned long long empty[kExMaxStages];
+    TileDesc desc[kExMaxStages];
+    double red[3][kWarps];
+    int is_last;
+    volatile int producer_done;
+};
 
-// ---- update piece: gradient from the owner's shard, fused optimizer step, K stores --------
-template <int OPT>
-__device__ __noinline__ void upd_piece(const ExArgs& a, const UpdHp& H, const float* gsrc,
-                                          unsigned long long lo, unsigned long long hi)
+// ---- producer: one lane ---------------------------------------------------------------------
+__device__ __noinline__ void producer_loop(ExShared& S, unsigned char* ring, unsigned epoch)
 {
-    const unsigned long long nvec = (hi - lo) >> 2;
-    const bool use_m = OPT == OPT_ADAM || (H.flags & F_MOMENTUM);
-    const bool load_m = OPT == OPT_ADAM || ((H.flags & F_MOMENTUM) && !(H.flags & F_FIRST));
-    // the gradient mostly comes from another GPU: its loads run one tile ahead of the local streams
-    float4 gn[kExU];
-#pragma unroll
-    for (int u = 0; u < kExU; ++u) {
-        const unsigned long long x = (unsigned long long)u * kThreads + threadIdx.x;
-        if (x < nvec) gn[u] = ld4(gsrc + lo + 4 * x);
-    }
-    for (unsigned long long t0 = 0; t0 < nvec; t0 += kTileVecs) {
-        float4 g[kExU], p[kExU], m[kExU], v[kExU];
-#pragma unroll
-        for (int u = 0; u < kExU; ++u) {
-            const unsigned long long x = t0 + (unsigned long long)u * kThreads + threadIdx.x;
-            m[u] = v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            g[u] = gn[u];
-            if (x < nvec) {
-                const unsigned long long off = lo + 4 * x;
-                p[u] = ld4(a.w[0] + off);
-                if (load_m) m[u] = ld4(a.m + off);
-                if (OPT == OPT_ADAM) v[u] = ld4(a.v + off);
-            }
-            if (x + kTileVecs < nvec) gn[u] = ld4(gsrc + lo + 4 * (x + kTileVecs));
-        }
-        // segment of the tile's first element, uniform over the CTA, looked up under the loads
-        int seg0 = 0, gi0 = 0;
-        bool uniform = true;
-        if (a.segs) {
-            const unsigned long long e0 = lo + 4 * t0;
-            unsigned long long e1 = e0 + 4ull * kTileVecs;
-            if (e1 > hi) e1 = hi;
-            seg0 = seg_find(a.segs, a.nseg, e0);
-            uniform = __ldg(&a.segs[seg0].end) >= e1;
-            gi0 = (int)__ldg(&a.segs[seg0].group);
-        }
-#pragma unroll
-        for (int u = 0; u < kExU; ++u) {
-            const unsigned long long x = t0 + (unsigned long long)u * kThreads + threadIdx.x;
-            if (x >= nvec) continue;
-            const unsigned long long off = lo + 4 * x;
-            if (uniform) {
-                upd_math4<OPT>(H, H.grp[gi0], (H.wd_mask >> gi0) & 1u, g[u], p[u], m[u], v[u]);
-            } else {
-                int s = seg0;
-                auto one = [&](int c, float gx, float& px, float& mx, float& vx) {
-                    while (__ldg(&a.segs[s].end) <= off + c) ++s;
-                    const int gi = (int)__ldg(&a.segs[s].group);
-                    upd_math<OPT>(H, H.grp[gi], (H.wd_mask >> gi) & 1u, gx, px, mx, vx);
-                };
-                one(0, g[u].x, p[u].x, m[u].x, v[u].x);
-                one(1, g[u].y, p[u].y, m[u].y, v[u].y);
-                one(2, g[u].z, p[u].z, m[u].z, v[u].z);
-                one(3, g[u].w, p[u].w, m[u].w, v[u].w);
-            }
-            for (int k = 0; k < a.Kw; ++k) st4(a.w[k] + off, p[u]);
-            if (use_m) st4(a.m + off, m[u]);
-            if (OPT == OPT_ADAM) st4(a.v + off, v[u]);
-        }
-    }
-}
-
-// One rank's share of a launch.  `ncta` CTAs of the grid (blockIdx.x) serve this rank.
-template <int OPT, int KA, int NR>
-__device__ __forceinline__ void exchange_body(const ExArgs& a, unsigned ncta)
-{
-    __shared__ UpdHp H;
-    __shared__ unsigned s_ticket[2];
-    __shared__ double s_red[3][kWarps];
-    const int n = NR > 0 ? NR : a.nranks;
-    if (a.dyn) {
-        const unsigned int* src = reinterpret_cast<const unsigned int*>(a.dyn);
-        unsigned int* dst = reinterpret_cast<unsigned int*>(&H);
-        for (unsigned int i = threadIdx.x; i < sizeof(UpdHp) / 4; i += blockDim.x) dst[i] = __ldg(src + i);
-    } else if (threadIdx.x == 0) {
-        H = a.hp;
-    }
-    // Every CTA reads the launch counter before it draws its first ticket; the counter moves only
-    // when the last CTA of the launch leaves, i.e. after every CTA has read it.
-    const unsigned epoch = ld_volatile(a.ctrl + CTL_LAUNCHES) + 1u;
+    const ExArgs& a = S.a;
+    const int n = a.nranks;
     const unsigned group_items = 2u * (unsigned)n + 1u;
-    const unsigned groups = a.window / (unsigned)n;       // groups of a step
-    const unsigned step_items = groups * group_items;
+    const unsigned step_items = (a.window / (unsigned)n) * group_items;
     const unsigned total = (a.nsteps + 2u) * step_items;
     const unsigned long long end = a.base + a.n;
     const unsigned* status = a.ctrl + CTL_STATUS;
-    unsigned* flags_local = a.flags[a.rank];
-    if (threadIdx.x == 0) s_ticket[0] = atomicAdd(a.ctrl + CTL_QUEUE, 1u);
-    __syncthreads();
-    unsigned t = s_ticket[0];
-    for (unsigned it = 0; t < total; ++it) {
-        unsigned nxt = 0;
-        if (threadIdx.x == 0) nxt = atomicAdd(a.ctrl + CTL_QUEUE, 1u);   // in flight while this item runs
+    const unsigned* flags_local = a.flags[a.rank];
+    const bool load_m = a.opt == OPT_ADAM || ((S.H.flags & F_MOMENTUM) && !(S.H.flags & F_FIRST));
+    const size_t stage_bytes = (size_t)a.ring_slots * kTileBytes;
+    int stage = 0;
+    unsigned parity = 0;            // phase of the empty barriers this lane waits for next
+    bool ok = true;
+    unsigned t = atomicAdd(a.ctrl + CTL_QUEUE, 1u);
+    while (ok && t < total) {
+        const unsigned nxt = atomicAdd(a.ctrl + CTL_QUEUE, 1u);      // resolves while this item is issued
         const unsigned step = t / step_items, j = t % step_items;
         const unsigned grp = j / group_items, i = j % group_items;
         int phase;
-        long long win;                                    // window the item's piece lies in
-        unsigned idx;                                     // piece index inside the window
+        long long win;
+        unsigned idx;
         if (i == 0) { phase = PH_RED; win = (long long)step - 1; idx = grp * (unsigned)n + (unsigned)a.rank; }
         else {
             const unsigned tt = i - 1u;
             idx = grp * (unsigned)n + (tt >> 1);
             if (tt & 1u) { phase = PH_UPD; win = (long long)step - 2; } else { phase = PH_AGG; win = (long long)step; }
         }
-        bool ok = true;
-        int signal = 0;                                   // what the signalling thread publishes after the item
-        unsigned slot = 0;
-        int owner = 0;
         const unsigned long long P = (unsigned long long)(win < 0 ? 0 : win) * a.window + idx;
         if (win >= 0 && win < (long long)a.nsteps && P < a.npieces) {
-            slot = a.slot_base + (unsigned)P;
-            owner = (int)(P % (unsigned)n);               // pieces are dealt to the ranks in turn
+            const unsigned slot = a.slot_base + (unsigned)P;
+            const int owner = (int)(P % (unsigned)n);
             const unsigned long long lo = a.base + P * a.piece;
             unsigned long long hi = lo + a.piece;
             if (hi > end) hi = end;
-            if (phase == PH_AGG) {
-                agg_piece<KA>(a, lo, hi);
-                signal = PH_AGG;
-            } else if (phase == PH_RED) {
-                if (threadIdx.x < n)
-                    ok = wait_epoch(flags_local + agg_flag_idx(slot, threadIdx.x), epoch, a.wait_ns, status);
-                ok = __syncthreads_and(ok);
-                Acc3 acc = {0.0, 0.0, 0.0};
-                if (ok) red_piece<NR>(a, lo, hi, acc);
-                else if (threadIdx.x == 0) record_timeout(a, PH_RED, slot);
-                if (a.stat) {
-                    const Acc3 r = block_sum(acc, s_red);
-                    if (threadIdx.x == 0) {
-                        double* ps = a.piece_stat + 3ull * slot;
-                        ps[0] = r.d; ps[1] = r.a; ps[2] = r.b;
-                    }
+            if (phase == PH_RED) {
+                ok = wait_epoch_n(flags_local + agg_flag_idx(slot, 0), n, epoch, a.wait_ns, status);
+                if (!ok) record_timeout(a, PH_RED, slot);
+            } else if (phase == PH_UPD) {
+                ok = wait_epoch(flags_local + red_flag_idx(a.max_slots, slot), epoch, a.wait_ns, status);
+                if (!ok) record_timeout(a, PH_UPD, slot);
+            }
+            for (unsigned long long e0 = lo; ok && e0 < hi; e0 += kTileElems) {
+                if (!mbar_wait_bounded(&S.empty[stage], parity ^ 1u, 2 * a.wait_ns + 10000000ull)) {
+                    record_timeout(a, PH_RING, slot);
+                    ok = false;
+                    break;
                 }
-                if (ok) signal = PH_RED;
-            } else {
-                if (threadIdx.x == 0)
-                    ok = wait_epoch(flags_local + red_flag_idx(a.max_slots, slot), epoch, a.wait_ns, status);
-                ok = __syncthreads_and(ok);
-                if (ok) {
-                    upd_piece<OPT>(a, H, a.pg[owner], lo, hi);
-                } else if (threadIdx.x == 0) {
-                    record_timeout(a, PH_UPD, slot);
+                const unsigned long long left = hi - e0;
+                const unsigned nvec = left >= kTileElems ? (unsigned)kTileVecs : (unsigned)(left >> 2);
+                const unsigned bytes = nvec * 16u;
+                TileDesc& d = S.desc[stage];
+                d.lo = e0; d.nvec = nvec; d.phase = phase; d.owner = owner; d.slot = slot;
+                d.last = e0 + kTileElems >= hi;
+                unsigned char* sb = ring + (size_t)stage * stage_bytes;
+                fence_proxy_async_smem();
+                if (phase == PH_AGG) {
+                    mbar_expect_tx(&S.full[stage], bytes * (unsigned)a.K);
+                    for (int k = 0; k < a.K; ++k) bulk_load(sb + k * kTileBytes, a.gk[k] + e0, bytes, &S.full[stage]);
+                } else if (phase == PH_RED) {
+                    mbar_expect_tx(&S.full[stage], bytes * (unsigned)n);
+                    for (int r = 0; r < n; ++r) bulk_load(sb + r * kTileBytes, a.px[r] + e0, bytes, &S.full[stage]);
+                } else {
+                    const unsigned ns = 2u + (load_m ? 1u : 0u) + (a.opt == OPT_ADAM ? 1u : 0u);
+                    mbar_expect_tx(&S.full[stage], bytes * ns);
+                    bulk_load(sb, a.pg[owner] + e0, bytes, &S.full[stage]);
+                    bulk_load(sb + kTileBytes, a.w[0] + e0, bytes, &S.full[stage]);
+                    if (load_m) bulk_load(sb + 2 * kTileBytes, a.m + e0, bytes, &S.full[stage]);
+                    if (a.opt == OPT_ADAM) bulk_load(sb + 3 * kTileBytes, a.v + e0, bytes, &S.full[stage]);
                 }
+                if (++stage == a.ring_stages) { stage = 0; parity ^= 1u; }
             }
         }
-        // the slot alternates, so the thread that writes the next ticket never overtakes a reader
-        if (threadIdx.x == 0) s_ticket[(it + 1) & 1] = ok ? nxt : 0xffffffffu;
-        __syncthreads();                                  // every store of the item has been issued
-        t = s_ticket[(it + 1) & 1];
-        // One thread (not the one that draws tickets and polls) publishes the piece: the release
-        // orders the CTA's stores, which the barrier made visible to it, before the flag.
-        if (threadIdx.x == 32 && signal) {
-            if (signal == PH_AGG) {
-                st_release_sys(a.flags[owner] + agg_flag_idx(slot, a.rank), epoch);
-            } else {
-                __threadfence_system();
-                for (int r = 0; r < n; ++r) st_relaxed_sys(a.flags[r] + red_flag_idx(a.max_slots, slot), epoch);
-            }
-        }
+        t = nxt;
     }
+    // end of the queue (or a wait ran out): one last descriptor tells the consumers to leave
+    if (mbar_wait_bounded(&S.empty[stage], parity ^ 1u, 2 * a.wait_ns + 10000000ull)) {
+        S.desc[stage].phase = PH_STOP;
+        mbar_arrive(&S.full[stage]);
+    }
+    S.producer_done = 1;
+}
+
+// CTA-wide (consumers only) sum, valid in consumer thread 0
+__device__ __forceinline__ Acc3 consumer_sum(Acc3 v, double (*sm)[kWarps])
+{
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    consumer_sync();
+    if (lane == 0) { sm[0][warp] = v.d; sm[1][warp] = v.a; sm[2][warp] = v.b; }
+    consumer_sync();
+    Acc3 r = {0.0, 0.0, 0.0};
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) { r.d += sm[0][w]; r.a += sm[1][w]; r.b += sm[2][w]; }
+    }
+    return r;
+}
+
+// ---- consumers: 256 threads, one 4-vector per thread, stream and tile --------------------------
+template <int OPT>
+__device__ __forceinline__ void consumer_loop(ExShared& S, const unsigned char* ring, unsigned epoch)
+{
+    const ExArgs& a = S.a;
+    const UpdHp& H = S.H;
+    const int n = a.nranks;
+    const bool use_m = OPT == OPT_ADAM || (H.flags & F_MOMENTUM);
+    const bool load_m = OPT == OPT_ADAM || ((H.flags & F_MOMENTUM) && !(H.flags & F_FIRST));
+    const bool stat = a.stat != nullptr;
+    const size_t stage_bytes = (size_t)a.ring_slots * kTileBytes;
+    const unsigned tid = threadIdx.x;
+    int stage = 0;
+    unsigned parity = 0;
+    Acc3 acc = {0.0, 0.0, 0.0};
+    for (;;) {
+        if (!mbar_wait_bounded(&S.full[stage], parity, 4 * a.wait_ns + 20000000ull)) {
+            if (tid == 0) record_timeout(a, PH_RING, 0);
+            break;
+        }
+        const TileDesc d = S.desc[stage];
+        if (d.phase == PH_STOP) break;
+        const float4* sb = reinterpret_cast<const float4*>(ring + (size_t)stage * stage_bytes);
+        const bool mine = tid < d.nvec;
+        const unsigned long long off = d.lo + 4ull * tid;
+        if (d.phase == PH_AGG) {
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (mine) {
+                s = sb[tid];
+                for (int k = 1; k < a.K; ++k) s = add4(s, sb[k * kTileVecs + tid]);
+            }
+            __syncwarp();
+            if ((tid & 31) == 0) mbar_arrive(&S.empty[stage]);       // the stage may be refilled
+            if (mine) st4(a.px_local + off, s);
+        } else if (d.phase == PH_RED) {
+            float4 g = make_float4(0.f, 0.f, 0.f, 0.f), e = g, o = g;
+            if (mine) {
+                e = sb[tid];
+                g = div4(e, a.divisor);
+                for (int r = 1; r < n; ++r) {
+                    const float4 y = sb[r * kTileVecs + tid];
+                    g = add4(g, div4(y, a.divisor));
+                    if (r == 1) o = y; else if (r & 1) o = add4(o, y); else e = add4(e, y);
+                }
+            }
+            __syncwarp();
+            if ((tid & 31) == 0) mbar_arrive(&S.empty[stage]);
+            if (mine) {
+                st4(a.pg_local + off, g);
+                if (stat) acc_vec(acc, div4(e, a.half_divisor), div4(o, a.half_divisor));
+            }
+        } else {
+            float4 g, p, m, v;
+            g = p = m = v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (mine) {
+                g = sb[tid];
+                p = sb[kTileVecs + tid];
+                if (load_m) m = sb[2 * kTileVecs + tid];
+                if (OPT == OPT_ADAM) v = sb[3 * kTileVecs + tid];
+            }
+            __syncwarp();
+            if ((tid & 31) == 0) mbar_arrive(&S.empty[stage]);
+            // segment of the tile's first element, uniform over the CTA
+            int seg0 = 0, gi0 = 0;
+            bool uniform = true;
+            if (a.segs) {
+                const unsigned long long e1 = d.lo + 4ull * d.nvec;
+                seg0 = seg_find(a.segs, a.nseg, d.lo);
+                uniform = __ldg(&a.segs[seg0].end) >= e1;
+                gi0 = (int)__ldg(&a.segs[seg0].group);
+            }
+            if (mine) {
+                if (uniform) {
+                    upd_math4<OPT>(H, H.grp[gi0], (H.wd_mask >> gi0) & 1u, g, p, m, v);
+                } else {
+                    int sgi = seg0;
+                    auto one = [&](int c, float gx, float& px, float& mx, float& vx) {
+                        while (__ldg(&a.segs[sgi].end) <= off + c) ++sgi;
+                        const int gi = (int)__ldg(&a.segs[sgi].group);
+                        upd_math<OPT>(H, H.grp[gi], (H.wd_mask >> gi) & 1u, gx, px, mx, vx);
+                    };
+                    one(0, g.x, p.x, m.x, v.x);
+                    one(1, g.y, p.y, m.y, v.y);
+                    one(2, g.z, p.z, m.z, v.z);
+                    one(3, g.w, p.w, m.w, v.w);
+                }
+                for (int k = 0; k < a.Kw; ++k) st4(a.w[k] + off, p);
+                if (use_m) st4(a.m + off, m);
+                if (OPT == OPT_ADAM) st4(a.v + off, v);
+            }
+        }
+        if (d.last && d.phase != PH_UPD) {
+            // the item is complete once every consumer has issued its stores: one thread publishes
+            // it, with release semantics that cover the stores the barrier made visible to it
+            if (d.phase == PH_RED && stat) {
+                const Acc3 r = consumer_sum(acc, S.red);
+                if (tid == 0) {
+                    double* ps = a.piece_stat + 3ull * d.slot;
+                    ps[0] = r.d; ps[1] = r.a; ps[2] = r.b;
+                }
+                acc.d = acc.a = acc.b = 0.0;
+            }
+            consumer_sync();
+            if (tid == 32) {
+                if (d.phase == PH_AGG) {
+                    st_release_sys(a.flags[d.owner] + agg_flag_idx(d.slot, a.rank), epoch);
+                } else {
+                    __threadfence_system();
+                    for (int r = 0; r < n; ++r) st_relaxed_sys(a.flags[r] + red_flag_idx(a.max_slots, d.slot), epoch);
+                }
+            }
+        }
+        if (++stage == a.ring_stages) { stage = 0; parity ^= 1u; }
+    }
+}
+
+// One rank's share of a launch.  `ncta` CTAs of the grid (blockIdx.x) serve this rank.
+template <int OPT>
+__device__ __forceinline__ void exchange_body(ExShared& S, unsigned char* ring, unsigned ncta)
+{
+    const ExArgs& a = S.a;
+    if (a.dyn) {
+        const unsigned int* src = reinterpret_cast<const unsigned int*>(a.dyn);
+        unsigned int* dst = reinterpret_cast<unsigned int*>(&S.H);
+        for (unsigned int i = threadIdx.x; i < sizeof(UpdHp) / 4; i += blockDim.x) dst[i] = __ldg(src + i);
+    } else {
+        const unsigned int* src = reinterpret_cast<const unsigned int*>(&a.hp);
+        unsigned int* dst = reinterpret_cast<unsigned int*>(&S.H);
+        for (unsigned int i = threadIdx.x; i < sizeof(UpdHp) / 4; i += blockDim.x) dst[i] = src[i];
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kExMaxStages; ++s) {
+            mbar_init(&S.full[s], 1);              // the producer's arrive (+ the copies' bytes)
+            mbar_init(&S.empty[s], kWarps);        // one arrive per consumer warp
+        }
+        S.producer_done = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // Every CTA reads the launch counter before its producer draws the first ticket; the counter
+    // moves only when the last CTA of the launch leaves, i.e. after every CTA has read it.
+    const unsigned epoch = ld_volatile(a.ctrl + CTL_LAUNCHES) + 1u;
+    __syncthreads();                               // the only barrier all 288 threads share
+    if (threadIdx.x >= kConsumers) {
+        if (threadIdx.x == kConsumers) producer_loop(S, ring, epoch);
+        return;
+    }
+    consumer_loop<OPT>(S, ring, epoch);
+    // Leaving.  Normally the stop descriptor was consumed and nothing is in flight.  After a wait
+    // that ran out, give the producer (bounded) time to stop issuing before the CTA's shared
+    // memory goes away.
+    consumer_sync();
+    if (threadIdx.x == 0) {
+        const unsigned long long t0 = gtime_ns();
+        while (!S.producer_done && gtime_ns() - t0 < 6 * a.wait_ns + 50000000ull) __nanosleep(200);
+        __threadfence();
+        S.is_last = atomicAdd(a.ctrl + CTL_DONE, 1u) == ncta - 1u;
+    }
+    consumer_sync();
+    if (!S.is_last) return;
     // the last CTA to leave adds this launch's piece sums in piece order, rewinds the queue and
     // advances the launch counter
-    __shared__ int is_last;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        is_last = atomicAdd(a.ctrl + CTL_DONE, 1u) == ncta - 1u;
-    }
-    __syncthreads();
-    if (!is_last) return;
     __threadfence();
     if (a.stat) {
         Acc3 s = {0.0, 0.0, 0.0};
-        if (ld_volatile(status) == 0u) {
-            for (unsigned long long q = (unsigned long long)a.rank + (unsigned long long)n * threadIdx.x; q < a.npieces;
-                 q += (unsigned long long)n * kThreads) {
+        if (ld_volatile(a.ctrl + CTL_STATUS) == 0u) {
+            for (unsigned long long q = (unsigned long long)a.rank + (unsigned long long)a.nranks * threadIdx.x;
+                 q < a.npieces; q += (unsigned long long)a.nranks * kConsumers) {
                 const double* ps = a.piece_stat + 3ull * (a.slot_base + q);
                 s.d += __ldcg(ps + 0); s.a += __ldcg(ps + 1); s.b += __ldcg(ps + 2);
             }
         }
-        s = block_sum(s, s_red);
+        s = consumer_sum(s, S.red);
         if (threadIdx.x == 0) { a.stat[0] += s.d; a.stat[1] += s.a; a.stat[2] += s.b; }
     }
     if (threadIdx.x == 0) {
@@ -428,9 +480,6 @@ __device__ __forceinline__ void exchange_body(const ExArgs& a, unsigned ncta)
     }
 }
 
-// The argument block goes to shared memory once: the three piece bodies are separate functions
-// (each with a register allocation of its own — inlined together they spill) that read it
-// through a pointer.  Two CTAs per SM: an update piece keeps two tiles of its streams in registers.
 __device__ __forceinline__ void stage_args(ExArgs* dst, const ExArgs* src)
 {
     const unsigned int* s = reinterpret_cast<const unsigned int*>(src);
@@ -439,23 +488,25 @@ __device__ __forceinline__ void stage_args(ExArgs* dst, const ExArgs* src)
     __syncthreads();
 }
 
-template <int OPT, int KA, int NR>
-__global__ void __launch_bounds__(kThreads, 2) exchange_kernel(const ExArgs arg)
+template <int OPT>
+__global__ void __launch_bounds__(kExThreads, 2) exchange_kernel(const ExArgs arg)
 {
-    __shared__ ExArgs a;
-    stage_args(&a, &arg);
-    exchange_body<OPT, KA, NR>(a, gridDim.x);
+    extern __shared__ __align__(128) unsigned char ring[];
+    __shared__ ExShared S;
+    stage_args(&S.a, &arg);
+    exchange_body<OPT>(S, ring, gridDim.x);
 }
 
 // Several ranks' exchanges in ONE launch on ONE GPU (blockIdx.y = rank): kernels that wait on
 // one another may not run as separate launches on a GPU, so single-GPU tests of the protocol
 // use this form, with the grid sized so that every CTA is resident.
-template <int OPT, int KA, int NR>
-__global__ void __launch_bounds__(kThreads, 2) exchange_emu_kernel(const ExArgs* ranks)
+template <int OPT>
+__global__ void __launch_bounds__(kExThreads, 2) exchange_emu_kernel(const ExArgs* ranks)
 {
-    __shared__ ExArgs a;
-    stage_args(&a, ranks + blockIdx.y);
-    exchange_body<OPT, KA, NR>(a, gridDim.x);
+    extern __shared__ __align__(128) unsigned char ring[];
+    __shared__ ExShared S;
+    stage_args(&S.a, ranks + blockIdx.y);
+    exchange_body<OPT>(S, ring, gridDim.x);
 }
 
 // ---- statistic across ranks: publish, wait, sum in rank order, finalize ---------------------
@@ -540,36 +591,6 @@ namespace {
 
 typedef void (*ExKernel)(const ExArgs);
 typedef void (*ExEmuKernel)(const ExArgs*);
-
-template <int OPT, int KA, int NR>
-void pick(ExKernel* k, ExEmuKernel* e)
-{
-    *k = exchange_kernel<OPT, KA, NR>;
-    *e = exchange_emu_kernel<OPT, KA, NR>;
-}
-
-template <int OPT, int KA>
-void pick_nr(int n, ExKernel* k, ExEmuKernel* e)
-{
-    switch (n) {
-    case 2: pick<OPT, KA, 2>(k, e); break;
-    case 4: pick<OPT, KA, 4>(k, e); break;
-    case 8: pick<OPT, KA, 8>(k, e); break;
-    default: pick<OPT, KA, 0>(k, e); break;
-    }
-}
-
-template <int OPT>
-void pick_ka(int K, int n, ExKernel* k, ExEmuKernel* e)
-{
-    switch (K) {
-    case 1: pick_nr<OPT, 1>(n, k, e); break;
-    case 2: pick_nr<OPT, 2>(n, k, e); break;
-    case 4: pick_nr<OPT, 4>(n, k, e); break;
-    case 8: pick_nr<OPT, 8>(n, k, e); break;
-    default: pick_nr<OPT, 0>(n, k, e); break;
-    }
-}
 
 }  // namespace
 
@@ -741,10 +762,14 @@ int jabas_exchange_step_f32(jabas_exchange_t* const* exs, const jabas_exchange_b
     int rc = jb_ctx_bind(ex0->ctx);
     if (rc) return rc;
     if (n == 0) return JABAS_OK;
-    ExKernel kern = nullptr;
-    ExEmuKernel emu = nullptr;
-    if (sgd) pick_ka<OPT_SGD>(bufs[0].Kg, ex0->nranks, &kern, &emu);
-    else pick_ka<OPT_ADAM>(bufs[0].Kg, ex0->nranks, &kern, &emu);
+    ExKernel kern = sgd ? exchange_kernel<OPT_SGD> : exchange_kernel<OPT_ADAM>;
+    ExEmuKernel emu = sgd ? exchange_emu_kernel<OPT_SGD> : exchange_emu_kernel<OPT_ADAM>;
+    if (bufs[0].Kg > kExMaxSlots) return fail(JABAS_EINVAL, "exchange: at most 8 VSW gradients per launch");
+    // ring: one 4 KB slot per stream of the widest phase, as many stages as fit the budget
+    const int slots = std::max(std::max(bufs[0].Kg, ex0->nranks), sgd ? 3 : 4);
+    int stages = kRingBudgetBytes / (slots * (int)kTileBytes);
+    if (stages > kExMaxStages) stages = kExMaxStages;
+    const size_t dyn_smem = (size_t)stages * slots * kTileBytes;
     jabas_ctx_t* ctx = ex0->ctx;
     int per_sm = 0;
     {
@@ -753,8 +778,13 @@ int jabas_exchange_step_f32(jabas_exchange_t* const* exs, const jabas_exchange_b
         auto it = ctx->occ.find(key);
         if (it != ctx->occ.end()) per_sm = it->second;
         if (per_sm == 0) {
-            cudaError_t e = nlocal == 1 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, 0)
-                                        : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, emu, kThreads, 0);
+            // occupancy for the full ring budget: the grid does not depend on the launch's stream count
+            cudaError_t e = nlocal == 1
+                ? cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBudgetBytes)
+                : cudaFuncSetAttribute(emu, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBudgetBytes);
+            if (e == cudaSuccess)
+                e = nlocal == 1 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kExThreads, kRingBudgetBytes)
+                                : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, emu, kExThreads, kRingBudgetBytes);
             if (e != cudaSuccess) return fail(JABAS_ECUDA, cudaGetErrorString(e));
             if (per_sm < 1) per_sm = 1;
             if (per_sm > kMaxCtasPerSm) per_sm = kMaxCtasPerSm;
@@ -769,7 +799,8 @@ int jabas_exchange_step_f32(jabas_exchange_t* const* exs, const jabas_exchange_b
             return rc;
         const unsigned long long items = (unsigned long long)(a.nsteps + 2) * (a.window / a.nranks) * (2ull * a.nranks + 1);
         if (grid > items) grid = items;
-        kern<<<(unsigned)grid, kThreads, 0, st>>>(a);
+        a.ring_stages = stages; a.ring_slots = slots; a.opt = sgd ? OPT_SGD : OPT_ADAM;
+        kern<<<(unsigned)grid, kExThreads, dyn_smem, st>>>(a);
         JB_CUDA(cudaGetLastError());
         return JABAS_OK;
     }
@@ -783,11 +814,12 @@ int jabas_exchange_step_f32(jabas_exchange_t* const* exs, const jabas_exchange_b
         if (bufs[r].Kg != bufs[0].Kg) return fail(JABAS_EINVAL, "exchange: every rank must have the same number of VSWs here");
         if ((rc = fill_args(exs[r], gx, bufs[r], h[r], n, base, slot_base, divisor, half_divisor, layout, groups, ngroups, sgd, adam)))
             return rc;
+        h[r].ring_stages = stages; h[r].ring_slots = slots; h[r].opt = sgd ? OPT_SGD : OPT_ADAM;
     }
     if (!ex0->d_emu) JB_CUDA(cudaMalloc(&ex0->d_emu, sizeof(ExArgs) * kExMaxRanks));
     JB_CUDA(cudaMemcpyAsync(ex0->d_emu, h.data(), sizeof(ExArgs) * nlocal, cudaMemcpyHostToDevice, st));
     JB_CUDA(cudaStreamSynchronize(st));          // h leaves scope; this form is for tests
-    emu<<<dim3(gx, (unsigned)nlocal), kThreads, 0, st>>>(ex0->d_emu);
+    emu<<<dim3(gx, (unsigned)nlocal), kExThreads, dyn_smem, st>>>(ex0->d_emu);
     JB_CUDA(cudaGetLastError());
     return JABAS_OK;
 }

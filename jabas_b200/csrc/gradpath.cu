@@ -40,53 +40,6 @@ constexpr int kStageTileVecs = kThreads;                 // one 4-vector per thr
 constexpr unsigned kStageTileBytes = kStageTileVecs * 16; // 4 KB per stream and stage
 constexpr int kStageBudgetBytes = 72 * 1024;             // dynamic shared memory asked per CTA
 
-__device__ __forceinline__ unsigned smem_u32(const void* p)
-{
-    return (unsigned)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(unsigned long long* b, unsigned count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* b, unsigned bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* b, unsigned parity)
-{
-    unsigned ok;
-    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-                 : "=r"(ok)
-                 : "r"(smem_u32(b)), "r"(parity)
-                 : "memory");
-    return ok != 0;
-}
-// false: the copies of this stage did not land within `limit_ns` nanoseconds of wall time
-// (the limit is a time, not a poll count, so it does not depend on how long one poll takes)
-__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* b, unsigned parity, unsigned long long limit_ns)
-{
-    if (mbar_try_wait(b, parity)) return true;
-    const unsigned long long t0 = gtime_ns();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 32; ++i)
-            if (mbar_try_wait(b, parity)) return true;
-        if (gtime_ns() - t0 > limit_ns) return false;
-    }
-}
-__device__ __forceinline__ void bulk_load(void* dst_smem, const void* src, unsigned bytes, unsigned long long* b)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_u32(dst_smem)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(b))
-                 : "memory");
-}
-// orders this thread's earlier generic-proxy accesses to shared memory before later async-proxy ones
-__device__ __forceinline__ void fence_proxy_async_smem()
-{
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
 
 // One partial per CTA; the last CTA to arrive adds them in CTA order into stat3.
 __device__ __forceinline__ void stat_finish(Acc3 acc, StatWs ws, double* stat3)

@@ -110,7 +110,7 @@ def ctx():
     (8, 8, "adamw", 2 * 8 * 2 * 8192 + 4, 16),
     (8, 2, "adam", 8 * 8192, 0),                    # window sized from the grid: one step
     (6, 2, "sgd", 3 * 6 * 8192 + 64, 6),            # generic rank count
-    (2, 16, "sgd", 2 * 8192 + 256, 2),              # generic K = 16
+    (2, 7, "sgd", 2 * 8192 + 256, 2),               # odd K
     (4, 4, "sgd", 150 * 8192 + 1024, 0),            # many pieces, automatic window
 ])
 def test_exchange_single_gpu_all_ranks_bit_exact(ctx, n_ranks, K, kind, total, window):
@@ -258,6 +258,9 @@ def test_exchange_rejects_bad_arguments(ctx):
         _run(ops, exs, ranks, 4094, 0, 0, 4, "sgd", groups, None, 0)
     with pytest.raises(ops.JabasError):                      # more slots than the exchange owns
         _run(ops, exs, ranks, 4096, 0, 1, 4, "sgd", groups, None, 0)
+    with pytest.raises(ops.JabasError):                      # more VSW gradients than a ring stage has slots
+        many = [dict(grads=[r["grads"][0]] * 9, weights=r["weights"], m=r["m"], v=r["v"], stat=None) for r in ranks]
+        ops.exchange_step(exs, many, 4096, 0, 0, 18.0, 9.0, groups, kind="sgd", momentum=0.9)
     with pytest.raises(ops.JabasError):                      # neither one rank nor all of them
         bad = ops.Exchange(ctx, 4, 0, [t.data_ptr() for t in keep[0]] * 2, [t.data_ptr() for t in keep[1]] * 2,
                            [t.data_ptr() for t in keep[2]] * 2, 1, 0, PIECE)
