@@ -84,6 +84,9 @@ def parse_args():
     ap.add_argument("--min-timed-ms", type=float, default=500.0,
                     help="repeat the --steps-long sample until this much device time has been measured")
     ap.add_argument("--cpu-steps", type=int, default=None)
+    ap.add_argument("--stream-study", action="store_true",
+                    help="instead of the benchmark: forward+backward of ResNet-50 for K x LBS images as one model, K "
+                         "models serially, K models on K streams (one thread / K threads); prints one JSON line")
     return ap.parse_args()
 
 
@@ -870,9 +873,82 @@ def measure_allreduce(D, layout):
     return out
 
 
+def stream_study(args):
+    """Does running the K VSWs on K streams buy anything?  Forward + backward only (stock PyTorch
+    kernels), torchvision ResNet-50 fp32/TF32, K x LBS synthetic images, device and wall time."""
+    import threading
+    import torch
+    import torchvision
+    K, lbs = args.vsw or 4, 64
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    models = [torchvision.models.resnet50().to(dev).train() for _ in range(K)]
+    crit = torch.nn.CrossEntropyLoss()
+    x = torch.randn(K * lbs, 3, 224, 224, device=dev)
+    y = torch.randint(0, 1000, (K * lbs,), device=dev)
+    xs, ys = torch.chunk(x, K), torch.chunk(y, K)
+    streams = [torch.cuda.Stream() for _ in range(K)]
+
+    def fb(m, a, b):
+        crit(m(a), b).backward()
+
+    def one_model():
+        fb(models[0], x, y)
+
+    def serial():
+        for k in range(K):
+            fb(models[k], xs[k], ys[k])
+
+    def k_streams():
+        cur = torch.cuda.current_stream()
+        for k in range(K):
+            streams[k].wait_stream(cur)
+            with torch.cuda.stream(streams[k]):
+                fb(models[k], xs[k], ys[k])
+        for s in streams:
+            cur.wait_stream(s)
+
+    def k_threads():
+        cur = torch.cuda.current_stream()
+
+        def run(k):
+            torch.cuda.set_device(dev)
+            streams[k].wait_stream(cur)
+            with torch.cuda.stream(streams[k]):
+                fb(models[k], xs[k], ys[k])
+        ts = [threading.Thread(target=run, args=(k,)) for k in range(K)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+        for s in streams:
+            cur.wait_stream(s)
+
+    def timed(fn, n=8):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        a.record()
+        for _ in range(n):
+            fn()
+        z.record()
+        torch.cuda.synchronize()
+        return {"device_ms": a.elapsed_time(z) / n, "wall_ms": (time.perf_counter() - t0) / n * 1e3}
+    out = {"study": "vsw stream concurrency", "model": "torchvision resnet50 fp32 (TF32 convolutions)", "vsw": K,
+           "local_batch": lbs}
+    for name, fn in (("one_model_whole_batch", one_model), ("k_models_one_stream", serial),
+                     ("k_models_k_streams_one_thread", k_streams), ("k_models_k_streams_k_threads", k_threads)):
+        out[name] = timed(fn)
+    print(json.dumps(out), flush=True)
+
+
 if __name__ == "__main__":
     a = parse_args()
-    if a.impl == "reference":
+    if a.stream_study:
+        stream_study(a)
+    elif a.impl == "reference":
         run_reference(a)
     else:
         run_ours(a)

@@ -287,7 +287,7 @@ JABAS_API int jabas_peer_reduce_f32(jabas_ctx_t* ctx, const float* const* xs, in
  * launches of one iteration that cover different ranges (one per DDP bucket) use disjoint slots.
  * Every rank must issue the same sequence of launches.  Launches of one exchange must not overlap
  * on the GPU (keep them on one stream). */
-#define JABAS_EXCHANGE_PIECE 8192u       /* default elements of one work item, per stream */
+#define JABAS_EXCHANGE_PIECE 16384u      /* default elements of one work item, per stream */
 typedef struct jabas_exchange jabas_exchange_t;
 typedef struct {
     int nranks;                     /* 2..8 */

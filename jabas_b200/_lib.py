@@ -28,7 +28,7 @@ EXPORTS = (
     "jabas_exchange_cosine",
 )
 
-EXCHANGE_PIECE = 8192          # JABAS_EXCHANGE_PIECE
+EXCHANGE_PIECE = 16384         # JABAS_EXCHANGE_PIECE
 
 
 class Seg(ctypes.Structure):

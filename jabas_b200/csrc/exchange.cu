@@ -709,9 +709,11 @@ static int fill_args(jabas_exchange_t* ex, unsigned grid_ctas, const jabas_excha
     a.npieces = (n + ex->piece - 1) / ex->piece;
     if ((unsigned long long)slot_base + a.npieces > ex->max_slots)
         return fail(JABAS_EINVAL, "exchange: the range needs more flag slots than the exchange was created with");
-    // pieces per pipeline step: as asked, or so that a step holds about 1.5 items per CTA of the grid
+    // pieces per pipeline step: as asked, or so that a step holds about four items per CTA of the
+    // grid — a consumer item then stands four rounds of tickets behind its producer item, which
+    // has finished by then on every rank (measured: waits vanish from about three rounds on)
     unsigned long long window = ex->window;
-    if (window == 0) window = (3ull * grid_ctas * ex->nranks) / (2ull * (2ull * ex->nranks + 1));
+    if (window == 0) window = (4ull * grid_ctas * ex->nranks) / (2ull * ex->nranks + 1);
     window = window / ex->nranks * ex->nranks;
     if (window < (unsigned long long)ex->nranks) window = ex->nranks;
     const unsigned long long nsteps = (a.npieces + window - 1) / window;

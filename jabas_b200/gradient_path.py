@@ -63,6 +63,14 @@ class GradientPath:
                  collective: str = "nccl", share_weights: bool = False, staging: str = "register",
                  peer_form: str = "pipeline", peer_wait_ms: Optional[float] = None,
                  exchange_piece: Optional[int] = None, exchange_window: Optional[int] = None):
+        if collective not in ("nccl", "peer"):
+            raise ValueError("collective must be 'nccl' or 'peer'")
+        if collective == "peer" and staging != "register":
+            # a launch that reads another GPU's memory through per-thread loads or the exchange's own
+            # TMA ring never goes through the update kernels' bulk-staged form
+            raise ValueError("staging='bulk' cannot be combined with collective='peer'")
+        if peer_form not in ("pipeline", "pull", "scatter", "direct"):
+            raise ValueError("peer_form must be 'pipeline', 'pull', 'scatter' or 'direct'")
         if backend is None:
             from . import ops as backend          # the CUDA library; raises without a GPU
         self.ops = backend
@@ -108,14 +116,6 @@ class GradientPath:
         else:
             self.weights = [torch.zeros(n, **f32) for _ in range(self.K)]
         self.grads = [torch.zeros(n, **f32) for _ in range(self.K)]
-        if collective not in ("nccl", "peer"):
-            raise ValueError("collective must be 'nccl' or 'peer'")
-        if collective == "peer" and staging != "register":
-            # a launch that reads another GPU's memory always loads straight into registers
-            raise ValueError("staging='bulk' cannot be combined with collective='peer': kernels that read "
-                             "peer-mapped memory use per-thread loads")
-        if peer_form not in ("pipeline", "pull", "scatter", "direct"):
-            raise ValueError("peer_form must be 'pipeline', 'pull', 'scatter' or 'direct'")
         self.collective = collective if self.world > 1 else "nccl"
         self.half = torch.zeros(n, **f32) if (self.similarity and self.world > 1
                                               and self.collective == "nccl") else None
@@ -285,6 +285,10 @@ class GradientPath:
         scatter = not direct and self.peer_form == "scatter"
         if scatter:
             self.ops.vsw_aggregate_scatter(self.ctx, self.grads, self._scatter_ptrs, self.shard_len, n, 1.0)
+        elif direct:
+            # each rank's sum is divided by T BEFORE the two are added, as everywhere else on the
+            # path (the reference's div_(T) before the SUM allreduce): g = fl(S0/T) + fl(S1/T)
+            self.ops.vsw_aggregate(self.ctx, self.grads, self.px[:n], float(self.T))
         else:
             self.ops.vsw_aggregate(self.ctx, self.grads, self.px[:n], 1.0)         # undivided local sum
         self._ev_end("aggregate", None, ev)
@@ -293,7 +297,9 @@ class GradientPath:
             # Two GPUs: the update kernel itself reads both ranks' sums (the remote one over
             # NVLink, hidden under its own HBM traffic), averages, takes the statistic from
             # the two ranks = the two halves, and updates: no reduce-scatter pass at all.
-            self.fused_local_step(None, sources=self.px_ptrs)
+            # the sums arrive divided by T: the kernel adds them as they are (divisor 1) and gets the
+            # halves E, O = S_r / (T/2) by dividing the divided sums by 1/2 (exact)
+            self.fused_local_step(None, sources=self.px_ptrs, divisor=1.0, half_divisor=0.5)
             dist.all_reduce(self._tok, group=self.pg)      # nobody overwrites its sum while a peer still reads it
             self.launches += 1
             if sim:
@@ -588,7 +594,8 @@ class GradientPath:
         """One GPU and few enough VSWs: aggregation and update can be one kernel."""
         return self.world == 1 and self.K <= getattr(self.ops, "MAX_FUSED_VSW", 0)
 
-    def fused_local_step(self, b: Optional[int] = None, keep_grad: bool = False, sources=None) -> None:
+    def fused_local_step(self, b: Optional[int] = None, keep_grad: bool = False, sources=None,
+                         divisor: Optional[float] = None, half_divisor: Optional[float] = None) -> None:
         """Single-GPU path in ONE launch over bucket ``b`` (None: the whole flat model):
         sum the K VSW gradients in registers, divide by T, update, write the new weights to
         all K replicas, accumulate the VSW-parity statistic.  The averaged gradient is only
@@ -606,20 +613,21 @@ class GradientPath:
             gs = [g[begin:end] for g in self.grads]
         ws = self._replicas(begin, end)
         kw = dict(layout=self.dev_layout, base=begin, grad_out=gs[0] if keep_grad else None)
+        divisor = float(self.T) if divisor is None else float(divisor)
         if self._sim_step:
-            kw.update(half_divisor=self.T / 2, stat=self.stat)
+            kw.update(half_divisor=self.T / 2 if half_divisor is None else half_divisor, stat=self.stat)
         if self._dyn is not None:
             kw["dynamic"] = self._dyn
         o = self.opt
         ev = self._ev_begin()
         if o.kind == "sgd":
-            self.ops.vsw_sgd_momentum(self.ctx, gs, float(self.T), ws,
+            self.ops.vsw_sgd_momentum(self.ctx, gs, divisor, ws,
                                       None if self.m is None else self.m[begin:end], o.groups,
                                       momentum=o.momentum, dampening=o.dampening, nesterov=o.nesterov,
                                       first_step=(self.steps == 0), **kw)
         else:
             groups = [dict(gr, step=self.steps + 1) for gr in o.groups]
-            self.ops.vsw_adam(self.ctx, gs, float(self.T), ws, self.m[begin:end], self.v[begin:end], groups,
+            self.ops.vsw_adam(self.ctx, gs, divisor, ws, self.m[begin:end], self.v[begin:end], groups,
                               beta1=o.betas[0], beta2=o.betas[1], eps=o.eps,
                               decoupled=(o.kind == "adamw"), **kw)
         self._ev_end("fused_step", b, ev)

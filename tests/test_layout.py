@@ -67,3 +67,18 @@ def test_layout_invariants(params, cap_mb):
     # regrouping rebuilds only the segments
     lay.set_groups([0] * len(params))
     assert lay.segments == [(0, lay.total, 0)]
+
+
+def test_engine_refuses_bulk_staging_with_the_peer_exchange():
+    """Kernels that read another GPU's memory never take the update kernels' bulk-staged form: the
+    combination is refused when the engine is constructed, before any device work."""
+    import pytest
+    from jabas_b200.gradient_path import GradientPath
+    from jabas_b200.layout import build_layout
+    layout = build_layout(["w"], [(64,)], [0])
+    with pytest.raises(ValueError, match="bulk"):
+        GradientPath(layout, 2, "cpu", None, total_num_decoupled_workers=2, collective="peer", staging="bulk",
+                     backend=object())
+    with pytest.raises(ValueError, match="peer_form"):
+        GradientPath(layout, 2, "cpu", None, total_num_decoupled_workers=2, collective="peer", peer_form="ring",
+                     backend=object())

@@ -189,7 +189,7 @@ def _engine_rank(rank, world, port, collective, kind, K, q, direct=None):
 
 @pytest.mark.parametrize("collective,kind,K,direct", [
     ("peer", "sgd", 4, "pipeline"), ("peer", "adamw", 2, "pipeline"), ("peer", "adam", 1, "pipeline"),
-    ("peer", "sgd", 4, "direct"), ("peer", "adamw", 1, "pull"), ("peer", "sgd", 2, "scatter"),
+    ("peer", "sgd", 4, "direct"), ("peer", "sgd", 3, "direct"), ("peer", "adamw", 1, "pull"), ("peer", "sgd", 2, "scatter"),
     ("nccl", "sgd", 2, None)])
 def test_engine_exchange_modes_match_reference_path(collective, kind, K, direct):
     """The gradient path at engine level on 2 (or, when visible, 4) GPUs: the peer-memory
