@@ -454,6 +454,15 @@ def time_engine(D, eng, args, steps, warmup, min_total_ms, use_graph, overlap, p
             "step_fn": step_fn, "eager_fn": eager_fn}
 
 
+def exchange_ok_everywhere(D, eng) -> None:
+    """Raise on EVERY rank if a bounded wait of the pipelined exchange ran out on ANY rank, so that
+    all ranks leave the measurement together (a one-sided exception would strand the others in
+    their next collective)."""
+    status = eng.exchange.status()[0] if getattr(eng, "exchange", None) is not None else 0
+    if not D.all_ok(status == 0):
+        raise RuntimeError(f"pipelined exchange: a bounded wait ran out on some rank (this rank's status {status:#x})")
+
+
 def hbm_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -540,13 +549,26 @@ def run_ours(args):
         sampler.start()
         time.sleep(0.2)
     T = time_engine(D, eng, args, args.steps, args.warmup, args.min_timed_ms, use_graph, overlap, per_bucket)
+    if world > 1 and eng.exchange is not None:
+        status = eng.exchange.status()[0]
+        if not D.all_ok(status == 0):
+            # a bounded wait of the pipelined exchange ran out on some rank (a rank fell more than the
+            # wait limit behind): the measurement is void; every rank redoes it over NCCL and says so
+            collective, collective_note = "nccl", f"pipelined exchange gave up (status {status:#x} on rank {rank}); NCCL"
+            T.pop("step_fn", None); T.pop("eager_fn", None)
+            eng.close()
+            del eng
+            gc.collect()
+            torch.cuda.empty_cache()
+            eng = build_engine(D, args, layout, K, opt, "nccl")
+            seed_engine(D, eng, K, args.share_weights)
+            T = time_engine(D, eng, args, args.steps, args.warmup, args.min_timed_ms, use_graph, overlap, per_bucket)
     clocks = sampler.stop() if rank == 0 else None
     ms_step = T["ms_per_step"]
     step_fn = T["step_fn"]
     cos = float(eng.cos)
     if args.staging == "bulk" and eng.ctx.staging_timeouts() != 0:
         raise RuntimeError("bulk staging: a wait for a copy ran out; the timed steps are incomplete")
-    eng.check_exchange()
     alg = eng.algorithmic_bytes(similarity)
     peak, peak_src = hbm_peak()
     roof = roofline_of(eng, T, alg, world, peak, peak_src)
@@ -699,7 +721,7 @@ def parity_check(D, args, layout, K, opt, collective):
             ref.grads[k].copy_(eng.grads[k].cpu())
         cos = float(eng.run_iteration())
         torch.cuda.synchronize()
-        eng.check_exchange()
+        exchange_ok_everywhere(D, eng)
         cos_ref = ref.run_iteration()
         w, wr = eng.weights[K - 1].cpu(), ref.weights[0]
         rel = float(((w - wr).abs() / wr.abs().clamp_min(1e-3)).max())
@@ -733,7 +755,7 @@ def run_extra_config(D, args, name, vsw, okind, collective):
         steps = 20 if layout.num_params < (1 << 28) else 8
         T = time_engine(D, eng, args, steps, 3, 150.0, not args.no_graph, True, None)
         clocks = sampler.stop() if D.rank == 0 else None
-        eng.check_exchange()
+        exchange_ok_everywhere(D, eng)
         sim = eng.similarity
         alg = eng.algorithmic_bytes(sim)
         peak, peak_src = hbm_peak()
@@ -815,7 +837,7 @@ def measure_training_iteration(D, K, lbs, collective, iters=8):
         for _ in range(3):
             full()
         ms = timed(full, iters)
-        tr.reducer.engine.check_exchange()
+        exchange_ok_everywhere(D, tr.reducer.engine)
         cos = float(tr.cos_placeholder)
         real_accum = tr.accum_step
         tr.accum_step = 1 << 30

@@ -129,7 +129,7 @@ JABAS_API int jabas_ctx_staging_timeouts(jabas_ctx_t* ctx, uint32_t* count);
 
 /* Wall-time limits of the two kinds of device-side wait in this library, in milliseconds:
  * a CTA's wait for a bulk copy into its shared-memory ring (default 50), and a CTA's wait for
- * another GPU's progress inside the pipelined exchange (jabas_exchange_*; default 1000, which
+ * another GPU's progress inside the pipelined exchange (jabas_exchange_*; default 5000, which
  * has to absorb the skew between ranks).  A wait that runs out never traps: the kernel records
  * it and returns.  No reference counterpart. */
 JABAS_API int jabas_ctx_set_wait_limits(jabas_ctx_t* ctx, double staging_ms, double peer_ms);
@@ -325,6 +325,13 @@ JABAS_API int jabas_exchange_reset(jabas_exchange_t* ex);
  * the phase that gave up: 2 reduce, 3 update, 4 statistic, bits 0..23 the piece slot) and, optionally,
  * of the number of completed launches. */
 JABAS_API int jabas_exchange_status(jabas_exchange_t* ex, uint32_t* status, uint32_t* launches);
+
+/* Tracing (off by default; device_buf NULL turns it off).  Launches made while a buffer is set write
+ * six uint64 per drawn ticket t < tickets at device_buf[6t]: (phase << 56 | CTA << 32 | piece), the
+ * GPU's global-timer nanoseconds when the producer drew the ticket, when the item's flags had been
+ * seen, when its last tile had been issued, when the consumers had stored its last tile, and one
+ * spare word.  Tickets that hold no work stay untouched.  For timelines of the pipeline. */
+JABAS_API int jabas_exchange_set_trace(jabas_exchange_t* ex, uint64_t* device_buf, uint64_t tickets);
 
 /* One launch over elements [base, base + n) (both multiples of 4).  Exactly one of sgd / adam is
  * non-NULL; groups / layout as in jabas_sgd_momentum_f32.  nlocal == 1: exs[0] / bufs[0] are this

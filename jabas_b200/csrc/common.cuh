@@ -70,7 +70,7 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kMaxCtasPerSm = 8;
 
 constexpr double kDefaultStagingWaitMs = 50.0;   // a 4 KB copy from local HBM takes microseconds
-constexpr double kDefaultPeerWaitMs = 1000.0;    // waits on another GPU's progress absorb rank skew
+constexpr double kDefaultPeerWaitMs = 5000.0;    // waits on another GPU's progress absorb rank skew
 
 inline int fail(int code, const std::string& msg) { return jb_fail(code, msg); }
 

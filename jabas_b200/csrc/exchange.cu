@@ -14,7 +14,8 @@
 // items of window s, this rank's reduce items of window s-1 and the update items of window s-2,
 // interleaved (one reduce item, then aggregate and update items in turn), so that at any moment
 // the resident CTAs work on NVLink-bound and HBM-bound items together and the two resources
-// overlap.  CTAs draw items with an atomic ticket, in queue order.
+// overlap (the aggregate items run one window further ahead than this sketch says, see
+// producer_loop).  CTAs draw items with an atomic ticket, in queue order.
 //
 // Dependencies are per-piece flags, not collectives: an aggregate item stores the launch's epoch
 // into the flag block of the piece's owner; the owner's reduce item waits for the n flags of its
@@ -58,11 +59,14 @@ struct ExArgs {
     unsigned long long wait_ns;
     unsigned long long npieces;         // pieces of the launch
     unsigned int piece, window, nsteps, slot_base, max_slots;   // piece: elements of an item; window: pieces per step
+    unsigned int total_tickets;         // length of the queue
     int nseg, K, Kw, nranks, rank;
     int opt;                            // OPT_SGD / OPT_ADAM
     int ring_stages, ring_slots;        // shared-memory ring: stages, and 4 KB stream slots per stage
     float divisor, half_divisor;
     const UpdHp* dyn;
+    unsigned long long* trace;          // nullable: 6 words per ticket (see jabas_exchange_set_trace)
+    unsigned long long trace_cap;       // tickets the trace buffer holds
     UpdHp hp;
 };
 
@@ -70,16 +74,20 @@ struct ExArgs {
 
 namespace {
 
-// A CTA is 8 consumer warps and one producer warp.  The producer (one lane) draws tickets, waits
+// A CTA is 8 consumer warps, one producer warp and one publisher warp (one active lane each).  The producer (one lane) draws tickets, waits
 // for the item's flags and brings the item on chip tile by tile with bulk copies (TMA, no
 // multicast; the source may be another GPU's memory) into a ring of shared-memory stages; it runs
 // up to a ring ahead of the consumers, ACROSS items, so neither the flag polls nor the first-byte
 // latency of an item (several microseconds over NVLink) ever leave the memory pipes idle.  The
-// consumers read a stage into registers, free it, do the arithmetic and the stores, and publish
-// the item's flag after its last tile — independently of the producer, which may by then be
-// blocked on a flag of a later item (so that wait can never stall what it waits for).
+// consumers read a stage into registers, free it, do the arithmetic and the stores, and after an
+// item's last tile hand the item to the publisher — independently of the producer, which may by
+// then be blocked on a flag of a later item (so that wait can never stall what it waits for).
+// The publisher does the system-scope release and the flag stores: the release has to wait until
+// the item's stores have drained (measured: 6-11 us under full HBM load), which would otherwise
+// stall a consumer warp, and with it the ring, once per item.
 constexpr int kConsumers = kThreads;                     // 256
-constexpr int kExThreads = kThreads + 32;                // + the producer warp
+constexpr int kExThreads = kThreads + 64;                // + the producer warp + the publisher warp
+constexpr int kMailSlots = 8;
 constexpr int kTileVecs = kThreads;                      // one 4-vector per consumer thread and stream
 constexpr unsigned kTileBytes = kTileVecs * 16;          // 4 KB per stream and stage
 constexpr unsigned kTileElems = kTileVecs * 4;
@@ -147,18 +155,17 @@ __device__ __forceinline__ bool wait_epoch(const unsigned* f, unsigned epoch, un
     return false;
 }
 
-// All n flags of a piece: the polls of one round are issued back to back (relaxed), one fence
-// orders the data reads behind them once every flag has been seen.
+// All n flags of a piece.  Every poll is an acquire LOAD (measured: 0.3 us each under full load);
+// a relaxed poll followed by one system-scope acquire FENCE cost 11 us per item, because the
+// fence waits for the SM's outstanding stores to drain although the polling lane has none.
 __device__ __forceinline__ bool wait_epoch_n(const unsigned* f, int n, unsigned epoch, unsigned long long limit_ns,
                                              const unsigned* status)
 {
     unsigned long long t0 = 0;
+    int r = 0;                                   // flags 0..r-1 have been seen
     for (unsigned long long polls = 0;; ++polls) {
-        bool all = true;
-#pragma unroll
-        for (int r = 0; r < kExMaxRanks; ++r)
-            if (r < n) all = all && ((int)(ld_relaxed_sys(f + r) - epoch) >= 0);
-        if (all) { fence_acq_rel_sys(); return true; }
+        while (r < n && (int)(ld_acquire_sys(f + r) - epoch) >= 0) ++r;
+        if (r == n) return true;
         if (polls == 0) t0 = gtime_ns();
         __nanosleep(40);
         if ((polls & 7) == 7) {
@@ -184,12 +191,20 @@ struct TileDesc {
     int owner;
     unsigned slot;
     int last;                   // last tile of its item
-    int pad;
+    unsigned ticket;
+};
+
+struct Mail {
+    unsigned slot, ticket;
+    int owner, phase;           // PH_AGG / PH_RED: publish that piece; PH_STOP: leave
 };
 
 struct ExShared {
     ExArgs a;
     UpdHp H;
+    Mail mail[kMailSlots];
+    unsigned mail_head;         // written by consumer thread 0 (release), read by the publisher (acquire)
+    volatile unsigned mail_tail;
     unsigned long long full[kExMaxStages];
     unsigned long long empty[kExMaxStages];
     TileDesc desc[kExMaxStages];
@@ -204,8 +219,24 @@ __device__ __noinline__ void producer_loop(ExShared& S, unsigned char* ring, uns
     const ExArgs& a = S.a;
     const int n = a.nranks;
     const unsigned group_items = 2u * (unsigned)n + 1u;
-    const unsigned step_items = (a.window / (unsigned)n) * group_items;
-    const unsigned total = (a.nsteps + 2u) * step_items;
+    // The queue opens with the aggregate items of window 0 alone; after that, step s holds the
+    // aggregate items of window s+1, the reduce items of window s-1 and the update items of window
+    // s-2.  Aggregation has no dependencies, so it runs a window further ahead than the pipeline
+    // needs: a reduce item's flags take about 30 us from the draw of the matching aggregate item
+    // (issue, drain of the stores behind the system-scope release, NVLink), and without the lead
+    // the reduce items of the first window would be drawn before that.
+    // Steps hold only the phases that have a window to work on (the first and the last two steps
+    // lack some), so no ticket is drawn for nothing: a ticket costs an atomic's round trip.
+    const unsigned prologue = a.npieces < a.window ? (unsigned)a.npieces : a.window;
+    const unsigned groups = a.window / (unsigned)n;
+    const unsigned nsteps = a.nsteps;
+    auto has_r = [&](unsigned st) { return st >= 1u && st <= nsteps; };
+    auto has_a = [&](unsigned st) { return st + 1u < nsteps; };
+    auto has_u = [&](unsigned st) { return st >= 2u && st <= nsteps + 1u; };
+    auto group_len = [&](unsigned st) {
+        return (has_r(st) ? 1u : 0u) + (has_a(st) ? (unsigned)n : 0u) + (has_u(st) ? (unsigned)n : 0u);
+    };
+    const unsigned total = a.total_tickets;
     const unsigned long long end = a.base + a.n;
     const unsigned* status = a.ctrl + CTL_STATUS;
     const unsigned* flags_local = a.flags[a.rank];
@@ -217,16 +248,42 @@ __device__ __noinline__ void producer_loop(ExShared& S, unsigned char* ring, uns
     unsigned t = atomicAdd(a.ctrl + CTL_QUEUE, 1u);
     while (ok && t < total) {
         const unsigned nxt = atomicAdd(a.ctrl + CTL_QUEUE, 1u);      // resolves while this item is issued
-        const unsigned step = t / step_items, j = t % step_items;
-        const unsigned grp = j / group_items, i = j % group_items;
         int phase;
         long long win;
         unsigned idx;
-        if (i == 0) { phase = PH_RED; win = (long long)step - 1; idx = grp * (unsigned)n + (unsigned)a.rank; }
+        if (t < prologue) { phase = PH_AGG; win = 0; idx = t; }
         else {
-            const unsigned tt = i - 1u;
-            idx = grp * (unsigned)n + (tt >> 1);
-            if (tt & 1u) { phase = PH_UPD; win = (long long)step - 2; } else { phase = PH_AGG; win = (long long)step; }
+            unsigned tq = t - prologue, step = 0;
+            bool found = false;
+            for (; step < 2u; ++step) {                        // the first two steps are short
+                const unsigned len = groups * group_len(step);
+                if (tq < len) { found = true; break; }
+                tq -= len;
+            }
+            if (!found && nsteps >= 4u) {                      // steps 2 .. nsteps-2 hold all three phases
+                const unsigned len = groups * group_items, nfull = nsteps - 3u;
+                if (tq < nfull * len) { step = 2u + tq / len; tq %= len; found = true; }
+                else { tq -= nfull * len; step = nsteps - 1u; }
+            }
+            for (; !found && step < nsteps + 2u; ++step) {     // the last steps are short again
+                const unsigned len = groups * group_len(step);
+                if (tq < len) { found = true; break; }
+                tq -= len;
+            }
+            const unsigned glen = group_len(step);
+            const unsigned grp = tq / glen;
+            unsigned i = tq % glen;
+            if (has_r(step) && i == 0u) { phase = PH_RED; win = (long long)step - 1; idx = grp * (unsigned)n + (unsigned)a.rank; }
+            else {
+                if (has_r(step)) --i;
+                if (has_a(step) && has_u(step)) {
+                    idx = grp * (unsigned)n + (i >> 1);
+                    if (i & 1u) { phase = PH_UPD; win = (long long)step - 2; } else { phase = PH_AGG; win = (long long)step + 1; }
+                } else {
+                    idx = grp * (unsigned)n + i;
+                    if (has_a(step)) { phase = PH_AGG; win = (long long)step + 1; } else { phase = PH_UPD; win = (long long)step - 2; }
+                }
+            }
         }
         const unsigned long long P = (unsigned long long)(win < 0 ? 0 : win) * a.window + idx;
         if (win >= 0 && win < (long long)a.nsteps && P < a.npieces) {
@@ -235,6 +292,8 @@ __device__ __noinline__ void producer_loop(ExShared& S, unsigned char* ring, uns
             const unsigned long long lo = a.base + P * a.piece;
             unsigned long long hi = lo + a.piece;
             if (hi > end) hi = end;
+            unsigned long long* tr = (a.trace && t < a.trace_cap) ? a.trace + 6ull * t : nullptr;
+            if (tr) { tr[0] = ((unsigned long long)phase << 56) | ((unsigned long long)blockIdx.x << 32) | (unsigned)P; tr[1] = gtime_ns(); }
             if (phase == PH_RED) {
                 ok = wait_epoch_n(flags_local + agg_flag_idx(slot, 0), n, epoch, a.wait_ns, status);
                 if (!ok) record_timeout(a, PH_RED, slot);
@@ -242,6 +301,7 @@ __device__ __noinline__ void producer_loop(ExShared& S, unsigned char* ring, uns
                 ok = wait_epoch(flags_local + red_flag_idx(a.max_slots, slot), epoch, a.wait_ns, status);
                 if (!ok) record_timeout(a, PH_UPD, slot);
             }
+            if (tr) tr[2] = gtime_ns();
             for (unsigned long long e0 = lo; ok && e0 < hi; e0 += kTileElems) {
                 if (!mbar_wait_bounded(&S.empty[stage], parity ^ 1u, 2 * a.wait_ns + 10000000ull)) {
                     record_timeout(a, PH_RING, slot);
@@ -254,6 +314,7 @@ __device__ __noinline__ void producer_loop(ExShared& S, unsigned char* ring, uns
                 TileDesc& d = S.desc[stage];
                 d.lo = e0; d.nvec = nvec; d.phase = phase; d.owner = owner; d.slot = slot;
                 d.last = e0 + kTileElems >= hi;
+                d.ticket = t;
                 unsigned char* sb = ring + (size_t)stage * stage_bytes;
                 fence_proxy_async_smem();
                 if (phase == PH_AGG) {
@@ -272,6 +333,7 @@ __device__ __noinline__ void producer_loop(ExShared& S, unsigned char* ring, uns
                 }
                 if (++stage == a.ring_stages) { stage = 0; parity ^= 1u; }
             }
+            if (tr) tr[3] = gtime_ns();
         }
         t = nxt;
     }
@@ -281,6 +343,78 @@ __device__ __noinline__ void producer_loop(ExShared& S, unsigned char* ring, uns
         mbar_arrive(&S.full[stage]);
     }
     S.producer_done = 1;
+}
+
+__device__ __forceinline__ unsigned ld_acquire_cta_shared(const unsigned* p)
+{
+    unsigned v;
+    asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_cta_shared(unsigned* p, unsigned v)
+{
+    asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+
+// consumer thread 0, after the consumers' barrier that follows an item's last stores
+__device__ __forceinline__ void mail_push(ExShared& S, int phase, int owner, unsigned slot, unsigned ticket)
+{
+    const unsigned head = S.mail_head;
+    while (head - S.mail_tail >= (unsigned)kMailSlots) __nanosleep(20);
+    Mail& m = S.mail[head % kMailSlots];
+    m.slot = slot; m.ticket = ticket; m.owner = owner; m.phase = phase;
+    st_release_cta_shared(&S.mail_head, head + 1u);      // orders the entry (and, through the barrier, the item's stores)
+}
+
+// ---- publisher: one lane ----------------------------------------------------------------------
+__device__ __noinline__ void publisher_loop(ExShared& S, unsigned epoch)
+{
+    const ExArgs& a = S.a;
+    const int n = a.nranks;
+    unsigned tail = 0;
+    unsigned long long idle_since = 0;
+    for (;;) {
+        const unsigned head = ld_acquire_cta_shared(&S.mail_head);
+        if (head == tail) {
+            // nothing to publish: the consumers always end with a stop entry; the time limit only
+            // guards against that never coming
+            if (idle_since == 0) idle_since = gtime_ns();
+            else if (gtime_ns() - idle_since > 8 * a.wait_ns + 100000000ull) return;
+            __nanosleep(50);
+            continue;
+        }
+        idle_since = 0;
+        // Everything that is waiting goes out behind ONE system-scope fence: the fence has to wait
+        // for the items' stores to drain, and entries pile up meanwhile.  The acquire above and the
+        // consumers' barrier before each push put every store of these items before the fence.
+        Mail batch[kMailSlots];
+        int nb = 0;
+        bool stop = false;
+        while (tail != head && nb < kMailSlots) {
+            batch[nb] = S.mail[tail % kMailSlots];
+            ++tail;
+            if (batch[nb].phase == PH_STOP) { stop = true; break; }
+            ++nb;
+        }
+        S.mail_tail = tail;
+        if (nb > 0) {
+            fence_acq_rel_sys();
+            for (int b = 0; b < nb; ++b) {
+                const Mail& m = batch[b];
+                if (m.phase == PH_AGG) {
+                    st_relaxed_sys(a.flags[m.owner] + agg_flag_idx(m.slot, a.rank), epoch);
+                } else {
+                    for (int r = 0; r < n; ++r) st_relaxed_sys(a.flags[r] + red_flag_idx(a.max_slots, m.slot), epoch);
+                }
+            }
+            if (a.trace) {
+                const unsigned long long now = gtime_ns();
+                for (int b = 0; b < nb; ++b)
+                    if (batch[b].ticket < a.trace_cap) a.trace[6ull * batch[b].ticket + 5] = now;
+            }
+        }
+        if (stop) return;
+    }
 }
 
 // CTA-wide (consumers only) sum, valid in consumer thread 0
@@ -390,6 +524,7 @@ __device__ __forceinline__ void consumer_loop(ExShared& S, const unsigned char* 
                 if (OPT == OPT_ADAM) st4(a.v + off, v);
             }
         }
+        if (d.last && a.trace && tid == 64 && d.ticket < a.trace_cap) a.trace[6ull * d.ticket + 4] = gtime_ns();
         if (d.last && d.phase != PH_UPD) {
             // the item is complete once every consumer has issued its stores: one thread publishes
             // it, with release semantics that cover the stores the barrier made visible to it
@@ -402,14 +537,7 @@ __device__ __forceinline__ void consumer_loop(ExShared& S, const unsigned char* 
                 acc.d = acc.a = acc.b = 0.0;
             }
             consumer_sync();
-            if (tid == 32) {
-                if (d.phase == PH_AGG) {
-                    st_release_sys(a.flags[d.owner] + agg_flag_idx(d.slot, a.rank), epoch);
-                } else {
-                    __threadfence_system();
-                    for (int r = 0; r < n; ++r) st_relaxed_sys(a.flags[r] + red_flag_idx(a.max_slots, d.slot), epoch);
-                }
-            }
+            if (tid == 0) mail_push(S, d.phase, d.owner, d.slot, d.ticket);
         }
         if (++stage == a.ring_stages) { stage = 0; parity ^= 1u; }
     }
@@ -435,17 +563,21 @@ __device__ __forceinline__ void exchange_body(ExShared& S, unsigned char* ring, 
             mbar_init(&S.empty[s], kWarps);        // one arrive per consumer warp
         }
         S.producer_done = 0;
+        S.mail_head = 0;
+        S.mail_tail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // Every CTA reads the launch counter before its producer draws the first ticket; the counter
     // moves only when the last CTA of the launch leaves, i.e. after every CTA has read it.
     const unsigned epoch = ld_volatile(a.ctrl + CTL_LAUNCHES) + 1u;
-    __syncthreads();                               // the only barrier all 288 threads share
+    __syncthreads();                               // the only barrier all 320 threads share
     if (threadIdx.x >= kConsumers) {
         if (threadIdx.x == kConsumers) producer_loop(S, ring, epoch);
+        else if (threadIdx.x == kConsumers + 32) publisher_loop(S, epoch);
         return;
     }
     consumer_loop<OPT>(S, ring, epoch);
+    if (threadIdx.x == 0) mail_push(S, PH_STOP, 0, 0, 0);
     // Leaving.  Normally the stop descriptor was consumed and nothing is in flight.  After a wait
     // that ran out, give the producer (bounded) time to stop issuing before the CTA's shared
     // memory goes away.
@@ -575,6 +707,8 @@ __global__ void __launch_bounds__(32) exchange_cosine_emu_kernel(const ExStatArg
 }  // namespace
 
 struct jabas_exchange {
+    unsigned long long* trace = nullptr;
+    unsigned long long trace_cap = 0;
     jabas_ctx_t* ctx = nullptr;
     int nranks = 0, rank = 0;
     unsigned max_slots = 0, window = 0, piece = JABAS_EXCHANGE_PIECE;
@@ -659,6 +793,14 @@ int jabas_exchange_reset(jabas_exchange_t* ex)
     return JABAS_OK;
 }
 
+int jabas_exchange_set_trace(jabas_exchange_t* ex, uint64_t* device_buf, uint64_t tickets)
+{
+    if (!ex) return fail(JABAS_EINVAL, "exchange is null");
+    ex->trace = reinterpret_cast<unsigned long long*>(device_buf);
+    ex->trace_cap = device_buf ? tickets : 0;
+    return JABAS_OK;
+}
+
 int jabas_exchange_status(jabas_exchange_t* ex, uint32_t* status, uint32_t* launches)
 {
     if (!ex || !status) return fail(JABAS_EINVAL, "exchange or status is null");
@@ -702,6 +844,7 @@ static int fill_args(jabas_exchange_t* ex, unsigned grid_ctas, const jabas_excha
     a.px_local = const_cast<float*>(ex->px[ex->rank]);
     a.pg_local = const_cast<float*>(ex->pg[ex->rank]);
     a.ctrl = ex->d_local;
+    a.trace = ex->trace; a.trace_cap = ex->trace_cap;
     a.piece_stat = reinterpret_cast<double*>(reinterpret_cast<char*>(ex->d_local) + ((size_t)CTL_WORDS * 4 + 255) / 256 * 256);
     a.base = base; a.n = n;
     a.wait_ns = (unsigned long long)(ctx->peer_wait_ms * 1e6);
@@ -717,9 +860,21 @@ static int fill_args(jabas_exchange_t* ex, unsigned grid_ctas, const jabas_excha
     window = window / ex->nranks * ex->nranks;
     if (window < (unsigned long long)ex->nranks) window = ex->nranks;
     const unsigned long long nsteps = (a.npieces + window - 1) / window;
-    if ((nsteps + 2) * (window / ex->nranks) * (2ull * ex->nranks + 1) >= 0x7ffffff0ull)
+    if (window + (nsteps + 2) * (window / ex->nranks) * (2ull * ex->nranks + 1) >= 0x7ffffff0ull)
         return fail(JABAS_EINVAL, "exchange: too many work items for one launch");
     a.window = (unsigned)window; a.nsteps = (unsigned)nsteps; a.slot_base = slot_base; a.max_slots = ex->max_slots;
+    {
+        // length of the queue: the aggregate items of window 0, then per step only the phases that
+        // have a window (see producer_loop)
+        unsigned long long tickets = a.npieces < window ? a.npieces : window;
+        const unsigned long long groups = window / ex->nranks;
+        for (unsigned long long st = 0; st < nsteps + 2; ++st) {
+            const unsigned long long len = ((st >= 1 && st <= nsteps) ? 1 : 0) + ((st + 1 < nsteps) ? ex->nranks : 0) +
+                                           ((st >= 2 && st <= nsteps + 1) ? ex->nranks : 0);
+            tickets += groups * len;
+        }
+        a.total_tickets = (unsigned)tickets;
+    }
     a.K = b.Kg; a.Kw = b.K; a.nranks = ex->nranks; a.rank = ex->rank;
     a.divisor = divisor; a.half_divisor = half_divisor;
     if (layout) {
@@ -799,8 +954,7 @@ int jabas_exchange_step_f32(jabas_exchange_t* const* exs, const jabas_exchange_b
         unsigned long long grid = (unsigned long long)ctx->sm_count * per_sm;
         if ((rc = fill_args(ex0, (unsigned)grid, bufs[0], a, n, base, slot_base, divisor, half_divisor, layout, groups, ngroups, sgd, adam)))
             return rc;
-        const unsigned long long items = (unsigned long long)(a.nsteps + 2) * (a.window / a.nranks) * (2ull * a.nranks + 1);
-        if (grid > items) grid = items;
+        if (grid > a.total_tickets) grid = a.total_tickets;
         a.ring_stages = stages; a.ring_slots = slots; a.opt = sgd ? OPT_SGD : OPT_ADAM;
         kern<<<(unsigned)grid, kExThreads, dyn_smem, st>>>(a);
         JB_CUDA(cudaGetLastError());

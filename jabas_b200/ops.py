@@ -105,7 +105,7 @@ class Context:
         _lib.check(self._lib.jabas_ctx_staging_timeouts(self._h, ctypes.byref(c)))
         return int(c.value)
 
-    def set_wait_limits(self, staging_ms: float = 50.0, peer_ms: float = 1000.0) -> None:
+    def set_wait_limits(self, staging_ms: float = 50.0, peer_ms: float = 5000.0) -> None:
         """Wall-time limits of the device-side waits: for a bulk copy into the shared-memory ring
         and for another GPU's progress inside the pipelined exchange.  A wait that runs out is
         reported (``staging_timeouts`` / ``Exchange.status``), never trapped."""
@@ -375,6 +375,15 @@ class Exchange:
 
     def reset(self) -> None:
         _lib.check(self.ctx._lib.jabas_exchange_reset(self._h))
+
+    def set_trace(self, buf: Optional[torch.Tensor]) -> None:
+        """Timeline tracing: ``buf`` is an int64 CUDA tensor of 6 words per ticket (None: off)."""
+        if buf is None:
+            _lib.check(self.ctx._lib.jabas_exchange_set_trace(self._h, None, 0))
+        else:
+            assert buf.dtype == torch.int64 and buf.is_cuda and buf.is_contiguous()
+            _lib.check(self.ctx._lib.jabas_exchange_set_trace(self._h, buf.data_ptr(), buf.numel() // 6))
+        self._trace = buf
 
     def close(self) -> None:
         if getattr(self, "_h", None):
