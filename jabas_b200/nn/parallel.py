@@ -182,44 +182,62 @@ class VSWReducer:
 
     def _flatten_buffers(self, k: int, module: nn.Module) -> None:
         """Module BUFFERS (BatchNorm running statistics, step counters) of VSW ``k`` become views
-        of one flat byte buffer per VSW, every buffer on a 16-byte boundary, so that all of them
-        are synchronised by one copy kernel (and one broadcast) instead of one op per buffer."""
+        of one flat buffer per dtype and VSW, every buffer on a 16-byte boundary, so that all of
+        them are synchronised by one copy kernel (and one broadcast) per dtype instead of one op
+        per buffer.  One flat buffer per DTYPE: ``torch.save`` refuses tensors that view one
+        storage as different types, and ``state_dict()`` must stay saveable as it is."""
         named = [(n, b) for n, b in module.named_buffers() if b is not None]
-        sizes = [(b.numel() * b.element_size() + 15) // 16 * 16 for _, b in named]
-        total = max(16, sum(sizes))
-        flat = torch.zeros(total, dtype=torch.uint8, device=self.device)
-        pos = 0
-        for (name, buf), size in zip(named, sizes):
-            nbytes = buf.numel() * buf.element_size()
-            view = flat[pos:pos + nbytes].view(buf.dtype).view(buf.shape)
-            with torch.no_grad():
-                view.copy_(buf)
-            # same tensor object, new storage: the buffer keeps a version counter of its own (a
-            # view would share the flat buffer's, and BatchNorm's in-place update of one layer's
-            # statistics would invalidate the ones another layer saved for backward)
-            buf.data = view
-            pos += size
+        by_dtype = {}
+        for name, buf in named:
+            by_dtype.setdefault(buf.dtype, []).append(buf)
+        flats = []
+        for dtype in sorted(by_dtype, key=str):
+            bufs = by_dtype[dtype]
+            item = bufs[0].element_size()
+            align = max(1, 16 // item)
+            sizes = [(b.numel() + align - 1) // align * align for b in bufs]
+            total = max(align, sum(sizes))
+            total = (total * item + 15) // 16 * 16 // item
+            flat = torch.zeros(total, dtype=dtype, device=self.device)
+            pos = 0
+            for buf, size in zip(bufs, sizes):
+                view = flat[pos:pos + buf.numel()].view(buf.shape)
+                with torch.no_grad():
+                    view.copy_(buf)
+                # same tensor object, new storage: the buffer keeps a version counter of its own (a
+                # view would share the flat buffer's, and BatchNorm's in-place update of one layer's
+                # statistics would invalidate the ones another layer saved for backward)
+                buf.data = view
+                pos += size
+            flats.append(flat)
         while len(self.buffers_flat) <= k:
             self.buffers_flat.append(None)
-        self.buffers_flat[k] = flat
+        self.buffers_flat[k] = flats
         self.num_module_buffers = len(named)
+
+    @staticmethod
+    def _as_f32(t: torch.Tensor) -> torch.Tensor:
+        """A flat buffer of any dtype as float32 words, for the bit-copy kernel."""
+        return t.view(torch.uint8).view(torch.float32)
 
     def sync_buffers(self, group=None) -> None:
         """Module buffers of every VSW on every rank <- rank 0's main replica (VSW 0), the
         ``broadcast_buffers=True`` behaviour of DistributedDataParallel that the reference's
         patched wrapper keeps (it receives ``sync_buffer_barrier`` for exactly this step,
-        jabas/train/trainer.py:515-521, 584-588): one broadcast of the flat buffer between ranks
-        and one replicate kernel between the VSWs, on the current stream."""
-        flats = [f for f in self.buffers_flat[:self.K] if f is not None]
-        if not self.num_module_buffers or not flats:
+        jabas/train/trainer.py:515-521, 584-588): per dtype one broadcast of the flat buffer
+        between ranks and one replicate kernel between the VSWs, on the current stream."""
+        sets = [f for f in self.buffers_flat[:self.K] if f]
+        if not self.num_module_buffers or not sets:
             return
         import torch.distributed as dist
-        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
-            dist.broadcast(flats[0], 0, group=group)
-        if len(flats) > 1:
-            eng = self.engine
-            eng.ops.replicate(eng.ctx, flats[0].view(torch.float32), [f.view(torch.float32) for f in flats[1:]])
-            eng.launches += 1
+        multi = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        eng = self.engine
+        for g, main in enumerate(sets[0]):
+            if multi:
+                dist.broadcast(main, 0, group=group)
+            if len(sets) > 1:
+                eng.ops.replicate(eng.ctx, self._as_f32(main), [self._as_f32(fs[g]) for fs in sets[1:]])
+                eng.launches += 1
 
     def resize(self, new_k: int, total_num_models: int) -> None:
         """Grow or shrink the set of VSWs.  Wrappers of removed VSWs are dropped here; the

@@ -64,7 +64,8 @@ def _rank_main(rank, world, port, mode, kind, wsm, q, collective="nccl"):
         tr.reducer.sync_buffers()
         torch.cuda.synchronize()
         sums = [None] * world
-        dist.all_gather_object(sums, [int(f.to(torch.int64).sum()) for f in tr.reducer.buffers_flat])
+        dist.all_gather_object(sums, [sum(int(f.view(torch.uint8).to(torch.int64).sum()) for f in fs)
+                                      for fs in tr.reducer.buffers_flat])
         if len({tuple(s) for s in sums}) != 1 or len(set(sums[0])) != 1:
             worst_w = float("inf")
         q.put((rank, worst_w, worst_c, tr.reducer.engine.launches))
