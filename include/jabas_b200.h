@@ -326,6 +326,12 @@ JABAS_API int jabas_exchange_reset(jabas_exchange_t* ex);
  * of the number of completed launches. */
 JABAS_API int jabas_exchange_status(jabas_exchange_t* ex, uint32_t* status, uint32_t* launches);
 
+/* Largest grid of the following launches (0, the default: every CTA the GPU can hold).  A launch
+ * that shares the GPU with other work — the per-bucket launches fired during backward — should
+ * leave shared memory and warp slots to it: CTAs of the exchange that wait for another rank hold
+ * 96 KB of shared memory each while they wait.  One CTA per SM is a good limit there. */
+JABAS_API int jabas_exchange_set_grid_limit(jabas_exchange_t* ex, uint32_t max_ctas);
+
 /* Tracing (off by default; device_buf NULL turns it off).  Launches made while a buffer is set write
  * six uint64 per drawn ticket t < tickets at device_buf[6t]: (phase << 56 | CTA << 32 | piece), the
  * GPU's global-timer nanoseconds when the producer drew the ticket, when the item's flags had been

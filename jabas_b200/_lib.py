@@ -25,7 +25,7 @@ EXPORTS = (
     "jabas_ctx_set_staging", "jabas_ctx_staging_timeouts", "jabas_ctx_set_wait_limits",
     "jabas_ctx_inject_staging_stall", "jabas_exchange_flag_words", "jabas_exchange_create",
     "jabas_exchange_destroy", "jabas_exchange_reset", "jabas_exchange_status", "jabas_exchange_step_f32",
-    "jabas_exchange_cosine", "jabas_exchange_set_trace",
+    "jabas_exchange_cosine", "jabas_exchange_set_trace", "jabas_exchange_set_grid_limit",
 )
 
 EXCHANGE_PIECE = 16384         # JABAS_EXCHANGE_PIECE
@@ -113,6 +113,7 @@ def load() -> ctypes.CDLL:
                                             ctypes.POINTER(Group), i32, ctypes.POINTER(SgdHp),
                                             ctypes.POINTER(AdamHp), vp]
     lib.jabas_exchange_set_trace.argtypes = [vp, vp, u64]
+    lib.jabas_exchange_set_grid_limit.argtypes = [vp, u32]
     lib.jabas_exchange_cosine.argtypes = [pvp, pvp, pvp, i32, f64, vp]
     lib.jabas_layout_create.argtypes = [vp, ctypes.POINTER(Seg), i32, u64, pvp]
     lib.jabas_layout_destroy.argtypes = [vp]

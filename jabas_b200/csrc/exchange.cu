@@ -709,6 +709,7 @@ __global__ void __launch_bounds__(32) exchange_cosine_emu_kernel(const ExStatArg
 struct jabas_exchange {
     unsigned long long* trace = nullptr;
     unsigned long long trace_cap = 0;
+    unsigned grid_limit = 0;             // 0: every resident CTA of the GPU
     jabas_ctx_t* ctx = nullptr;
     int nranks = 0, rank = 0;
     unsigned max_slots = 0, window = 0, piece = JABAS_EXCHANGE_PIECE;
@@ -790,6 +791,13 @@ int jabas_exchange_reset(jabas_exchange_t* ex)
     if (rc) return rc;
     JB_CUDA(cudaDeviceSynchronize());
     JB_CUDA(cudaMemset(ex->d_local, 0, ex->local_bytes));
+    return JABAS_OK;
+}
+
+int jabas_exchange_set_grid_limit(jabas_exchange_t* ex, uint32_t max_ctas)
+{
+    if (!ex) return fail(JABAS_EINVAL, "exchange is null");
+    ex->grid_limit = max_ctas;
     return JABAS_OK;
 }
 
@@ -952,6 +960,7 @@ int jabas_exchange_step_f32(jabas_exchange_t* const* exs, const jabas_exchange_b
     if (nlocal == 1) {
         ExArgs a;
         unsigned long long grid = (unsigned long long)ctx->sm_count * per_sm;
+        if (ex0->grid_limit && grid > ex0->grid_limit) grid = ex0->grid_limit;
         if ((rc = fill_args(ex0, (unsigned)grid, bufs[0], a, n, base, slot_base, divisor, half_divisor, layout, groups, ngroups, sgd, adam)))
             return rc;
         if (grid > a.total_tickets) grid = a.total_tickets;

@@ -221,6 +221,9 @@ class GradientPath:
         self._fl_h = symm_mem.rendezvous(self.xflags, group)
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.pg)                   # every rank's flag block is zero before any launch
+        self._bucket_grid_limit = int(os.environ.get("JABAS_EXCHANGE_BUCKET_CTAS", 0)) or \
+            torch.cuda.get_device_properties(self.device).multi_processor_count
+        self._grid_limit_set = 0
         self.exchange = self.ops.Exchange(self.ctx, world, self.rank,
                                           [int(p) for p in self._px_h.buffer_ptrs],
                                           [int(p) for p in self._pg_h.buffer_ptrs],
@@ -253,6 +256,11 @@ class GradientPath:
         else:
             kw.update(beta1=o.betas[0], beta2=o.betas[1], eps=o.eps)
             groups = [dict(gr, step=self.steps + 1) for gr in o.groups]
+        # a per-bucket launch runs beside backward: one CTA per SM leaves the rest of each SM to it
+        limit = 0 if b is None else self._bucket_grid_limit
+        if limit != self._grid_limit_set:
+            self.exchange.set_grid_limit(limit)
+            self._grid_limit_set = limit
         ev = self._ev_begin()
         self.ops.exchange_step([self.exchange], [bufs], length, begin, 0 if b is None else self._slot_base[b],
                                float(self.T), self.T / 2, groups, **kw)

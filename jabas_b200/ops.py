@@ -376,6 +376,10 @@ class Exchange:
     def reset(self) -> None:
         _lib.check(self.ctx._lib.jabas_exchange_reset(self._h))
 
+    def set_grid_limit(self, max_ctas: int) -> None:
+        """Largest grid of the following launches (0: the whole GPU)."""
+        _lib.check(self.ctx._lib.jabas_exchange_set_grid_limit(self._h, int(max_ctas)))
+
     def set_trace(self, buf: Optional[torch.Tensor]) -> None:
         """Timeline tracing: ``buf`` is an int64 CUDA tensor of 6 words per ticket (None: off)."""
         if buf is None:
