@@ -60,8 +60,9 @@ def parse_args():
     ap.add_argument("--similarity-mode", default="fused", choices=["fused", "pair_exchange"])
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="N > 1: cross-GPU exchange by this library's kernels over NVLink peer memory, or by NCCL")
-    ap.add_argument("--peer-form", default="pipeline", choices=["pipeline", "pull", "scatter", "direct"],
-                    help="collective=peer: one pipelined kernel (default) or the three-kernel forms")
+    ap.add_argument("--peer-form", default="pipeline", choices=["pipeline", "direct"],
+                    help="collective=peer: one pipelined kernel (default), or, on two GPUs, an aggregate kernel and "
+                         "an update kernel that reads both ranks' sums")
     ap.add_argument("--no-similarity", action="store_true",
                     help="skip the two-half statistic (forced when T is odd, e.g. one GPU with one VSW)")
     ap.add_argument("--no-overlap", action="store_true")

@@ -58,17 +58,6 @@ typedef struct {
     uint32_t reserved;
 } jabas_seg_t;
 
-/* Where an update reads its gradient from when the world-averaged gradient lives, shard by
- * shard, in the ranks' peer-mapped buffers (see jabas_peer_reduce_f32): element i of the flat
- * buffer is read from bufs[min(i / shard_len, n-1)][i].  Pointers are device pointers valid on
- * the calling GPU (peer mappings for the other ranks); the array itself is host memory. */
-typedef struct {
-    const float* const* bufs;
-    int      n;
-    int      reserved;
-    uint64_t shard_len;     /* elements, multiple of 4 */
-} jabas_peer_src_t;
-
 /* Per-launch hyper-parameters of one param group: `param_groups[i]['lr']` is mutated
  * every iteration by the reference (jabas/train/trainer.py:693-700). */
 typedef struct {
@@ -87,8 +76,9 @@ typedef struct {
                                  multiplied by it before the update (jabas_clip_coef)       */
     const jabas_dynhp_t* dynamic; /* nullable: the kernel reads lr / weight decay / flags from
                                  this device-resident block (see jabas_dynhp_create)        */
-    const jabas_peer_src_t* peer_grad; /* nullable: read the gradient from peer shards; `g` may
-                                 then be NULL and `base` indexes the full-length buffers    */
+    int    remote_sources;    /* 1: some gradient pointer of the call is another GPU's memory (peer
+                                 mapping): the kernel then loads per thread, never by bulk copy  */
+    int    reserved;
 } jabas_sgd_hp_t;
 
 typedef struct {
@@ -99,7 +89,8 @@ typedef struct {
     int    reserved;
     const float* grad_scale;  /* as in jabas_sgd_hp_t */
     const jabas_dynhp_t* dynamic; /* as in jabas_sgd_hp_t */
-    const jabas_peer_src_t* peer_grad; /* as in jabas_sgd_hp_t */
+    int    remote_sources;    /* as in jabas_sgd_hp_t */
+    int    reserved2;
 } jabas_adam_hp_t;
 
 JABAS_API int         jabas_version(void);
@@ -115,7 +106,7 @@ JABAS_API int jabas_ctx_destroy(jabas_ctx_t* ctx);
  *  - JABAS_STAGING_REGISTER (default): per-thread 128-bit loads straight into registers;
  *  - JABAS_STAGING_BULK: TMA bulk copies (cp.async.bulk) of 4 KB per stream into a multi-stage
  *    shared-memory ring, completion on mbarriers.  Results are bit-identical (the statistic to
- *    fp64 summation order).  Launches whose gradient comes from peer shards keep the register
+ *    fp64 summation order).  Launches with hp->remote_sources set keep the register
  *    form.  Every wait on a copy is bounded by wall time (the GPU's global timer, 50 ms by
  *    default); a wait that runs out ends the CTA's loop early, at the same tile for all of its
  *    threads, and is counted (the launch's outputs are then incomplete).
@@ -175,17 +166,6 @@ JABAS_API int jabas_vsw_aggregate_f32(jabas_ctx_t* ctx, const float* const* grad
                             float* half_out, uint64_t n, float divisor, float half_divisor,
                             double* stat3, void* stream);
 
-/* Local aggregation whose result is scattered, shard by shard, into the ranks that will
- * reduce it: element i of  (g[0] + ... + g[K-1]) / divisor  is stored to
- * slots[i / shard_len][i % shard_len].  slots[j] is this rank's staging slot inside rank j's
- * peer-mapped buffer, so the reduce-scatter traffic crosses NVLink as plain stores while the
- * kernel streams the K local gradients from HBM; the owner then reduces its n slots locally
- * (jabas_peer_reduce_f32 with local pointers).  First stage of the cross-GPU exchange that
- * replaces the allreduces of jabas/ddp_comm_hooks/similarity_allreduce.py:30,42. */
-JABAS_API int jabas_vsw_aggregate_scatter_f32(jabas_ctx_t* ctx, const float* const* grads, int K,
-                                    float* const* slots, int nranks, uint64_t shard_len, uint64_t n,
-                                    float divisor, void* stream);
-
 /* x /= divisor in place.  Replaces `div_(T/2)` at
  * jabas/ddp_comm_hooks/similarity_allreduce.py:32. */
 JABAS_API int jabas_div_f32(jabas_ctx_t* ctx, float* x, uint64_t n, float divisor, void* stream);
@@ -244,21 +224,6 @@ JABAS_API int jabas_vsw_adam_f32(jabas_ctx_t* ctx, const float* const* grads, in
  * F.cosine_similarity at jabas/train/trainer.py:478. */
 JABAS_API int jabas_dot_norms_f32(jabas_ctx_t* ctx, const float* a, const float* b, uint64_t n,
                         double* stat3, void* stream);
-
-/* The cross-GPU exchange as kernels over NVLink peer memory instead of a collective library
- * (replaces the world allreduce of jabas/ddp_comm_hooks/similarity_allreduce.py:42, the
- * sub-group allreduce of :30 and the pair exchange of jabas/train/trainer.py:470-483).
- * xs[r] (r = 0..n-1, rank order) is rank r's locally aggregated, UNDIVIDED gradient buffer,
- * mapped into this GPU's address space.  For this rank's shard [lo, hi):
- *   g_out[i] = sum_r xs[r][i] / divisor      (each term divided first, summed in rank order)
- *   stat3   += (<E,O>, |E|^2, |O|^2),  E / O = sum over even / odd ranks, / half_divisor
- * The caller must order the launch after every rank's aggregation and before any rank
- * overwrites its buffer (a barrier collective on the same stream on every rank does both),
- * then all-reduce stat3 (3 doubles) and read the reduced gradient through
- * jabas_*_hp_t.peer_grad.  NVLink bytes per GPU: 2(n-1)/n x 4 bytes per element. */
-JABAS_API int jabas_peer_reduce_f32(jabas_ctx_t* ctx, const float* const* xs, int n, float* g_out,
-                          uint64_t lo, uint64_t hi, float divisor, float half_divisor,
-                          double* stat3, void* stream);
 
 /* ---- The cross-GPU gradient path as ONE pipelined kernel per GPU --------------------------------
  *

@@ -21,7 +21,7 @@ EXPORTS = (
     "jabas_sgd_momentum_f32", "jabas_adam_f32", "jabas_dot_norms_f32", "jabas_cosine_finalize",
     "jabas_replicate_f32", "jabas_dot_norms_static_f32", "jabas_vsw_sgd_momentum_f32",
     "jabas_vsw_adam_f32", "jabas_sumsq_f32", "jabas_clip_coef", "jabas_dynhp_create",
-    "jabas_dynhp_destroy", "jabas_dynhp_push_sgd", "jabas_dynhp_push_adam", "jabas_peer_reduce_f32", "jabas_vsw_aggregate_scatter_f32",
+    "jabas_dynhp_destroy", "jabas_dynhp_push_sgd", "jabas_dynhp_push_adam",
     "jabas_ctx_set_staging", "jabas_ctx_staging_timeouts", "jabas_ctx_set_wait_limits",
     "jabas_ctx_inject_staging_stall", "jabas_exchange_flag_words", "jabas_exchange_create",
     "jabas_exchange_destroy", "jabas_exchange_reset", "jabas_exchange_status", "jabas_exchange_step_f32",
@@ -41,23 +41,18 @@ class Group(ctypes.Structure):
                 ("step", ctypes.c_int64), ("reserved", ctypes.c_int64)]
 
 
-class PeerSrc(ctypes.Structure):
-    _fields_ = [("bufs", ctypes.POINTER(ctypes.c_void_p)), ("n", ctypes.c_int), ("reserved", ctypes.c_int),
-                ("shard_len", ctypes.c_uint64)]
-
-
 class SgdHp(ctypes.Structure):
     _fields_ = [("momentum", ctypes.c_double), ("dampening", ctypes.c_double),
                 ("nesterov", ctypes.c_int), ("first_step", ctypes.c_int),
                 ("grad_scale", ctypes.c_void_p), ("dynamic", ctypes.c_void_p),
-                ("peer_grad", ctypes.POINTER(PeerSrc))]
+                ("remote_sources", ctypes.c_int), ("reserved", ctypes.c_int)]
 
 
 class AdamHp(ctypes.Structure):
     _fields_ = [("beta1", ctypes.c_double), ("beta2", ctypes.c_double), ("eps", ctypes.c_double),
                 ("decoupled", ctypes.c_int), ("reserved", ctypes.c_int),
                 ("grad_scale", ctypes.c_void_p), ("dynamic", ctypes.c_void_p),
-                ("peer_grad", ctypes.POINTER(PeerSrc))]
+                ("remote_sources", ctypes.c_int), ("reserved2", ctypes.c_int)]
 
 
 class ExchangeDesc(ctypes.Structure):
@@ -135,8 +130,6 @@ def load() -> ctypes.CDLL:
     lib.jabas_dynhp_destroy.argtypes = [vp]
     lib.jabas_dynhp_push_sgd.argtypes = [vp, ctypes.POINTER(Group), i32, ctypes.POINTER(SgdHp), vp]
     lib.jabas_dynhp_push_adam.argtypes = [vp, ctypes.POINTER(Group), i32, ctypes.POINTER(AdamHp), vp]
-    lib.jabas_vsw_aggregate_scatter_f32.argtypes = [vp, pvp, i32, pvp, i32, u64, u64, f32, vp]
-    lib.jabas_peer_reduce_f32.argtypes = [vp, pvp, i32, vp, u64, u64, f32, f32, vp, vp]
     lib.jabas_sumsq_f32.argtypes = [vp, vp, u64, vp, vp]
     lib.jabas_clip_coef.argtypes = [vp, vp, f64, vp, vp]
     lib.jabas_cosine_finalize.argtypes = [vp, vp, f64, vp, vp]

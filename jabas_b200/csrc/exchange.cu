@@ -112,12 +112,6 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p)
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ unsigned ld_relaxed_sys(const unsigned* p)
-{
-    unsigned v;
-    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 __device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v)
 {
@@ -897,7 +891,7 @@ static int fill_args(jabas_exchange_t* ex, unsigned grid_ctas, const jabas_excha
         if (sgd->momentum != 0.0 && !b.m) return fail(JABAS_EINVAL, "momentum != 0 needs a momentum buffer");
         if (sgd->nesterov && (sgd->momentum <= 0.0 || sgd->dampening != 0.0))
             return fail(JABAS_EINVAL, "nesterov needs momentum > 0 and dampening == 0");
-        if (sgd->grad_scale || sgd->peer_grad) return fail(JABAS_EINVAL, "exchange: grad_scale / peer_grad are not supported");
+        if (sgd->grad_scale) return fail(JABAS_EINVAL, "exchange: gradient-norm clipping (grad_scale) is not supported");
         if ((rc = jb_fill_sgd_hp(a.hp, groups, ngroups, sgd))) return rc;
         if (sgd->dynamic) {
             if (sgd->dynamic->kind != OPT_SGD) return fail(JABAS_EINVAL, "the dynamic block holds Adam hyper-parameters");
@@ -905,7 +899,7 @@ static int fill_args(jabas_exchange_t* ex, unsigned grid_ctas, const jabas_excha
         }
     } else {
         if (!b.m || !b.v) return fail(JABAS_EINVAL, "exp_avg and exp_avg_sq buffers are required");
-        if (adam->grad_scale || adam->peer_grad) return fail(JABAS_EINVAL, "exchange: grad_scale / peer_grad are not supported");
+        if (adam->grad_scale) return fail(JABAS_EINVAL, "exchange: gradient-norm clipping (grad_scale) is not supported");
         if ((rc = jb_fill_adam_hp(a.hp, groups, ngroups, adam))) return rc;
         if (adam->dynamic) {
             if (adam->dynamic->kind != OPT_ADAM) return fail(JABAS_EINVAL, "the dynamic block holds SGD hyper-parameters");

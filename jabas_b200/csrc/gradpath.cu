@@ -85,25 +85,7 @@ struct AggArgs {
     float divisor;
     float half_divisor;
     int K;
-    // scatter mode (nscatter > 0): element i goes to scatter[i / shard_len][i % shard_len] — the
-    // staging slot this rank owns inside the buffer of the rank that reduces that shard (peer
-    // memory, written over NVLink while the K local gradients stream in from HBM)
-    int nscatter;
-    unsigned long long shard_len;
-    float* scatter[JABAS_MAX_VSW];
 };
-
-__device__ __forceinline__ float* agg_dst(const AggArgs& a, unsigned long long idx)
-{
-    if (a.nscatter == 0) return a.out + idx;
-    const unsigned long long owner = idx / a.shard_len;
-    float* p = a.scatter[0];
-#pragma unroll
-    for (int r = 1; r < JABAS_MAX_VSW; ++r)
-        if (owner >= (unsigned long long)r && r < a.nscatter) p = a.scatter[r];
-    const unsigned long long o = owner < (unsigned long long)a.nscatter ? owner : (unsigned long long)(a.nscatter - 1);
-    return p + (idx - o * a.shard_len);
-}
 
 __host__ __device__ constexpr int agg_unroll(int K) { return K <= 2 ? 4 : (K <= 4 ? 2 : 1); }
 
@@ -123,7 +105,7 @@ __device__ __forceinline__ void agg_elem(const AggArgs& a, unsigned long long i,
         }
     }
     if (a.half) a.half[i] = s;
-    *agg_dst(a, i) = __fdiv_rn(s, a.divisor);
+    a.out[i] = __fdiv_rn(s, a.divisor);
     if (STAT) acc_one(acc, __fdiv_rn(e, a.half_divisor), __fdiv_rn(o, a.half_divisor));
 }
 
@@ -154,7 +136,7 @@ __global__ void __launch_bounds__(kThreads) agg_vec_kernel(const AggArgs a)
 #pragma unroll
                 for (int k = 1; k < K; ++k) s = add4(s, x[u][k]);
                 if (a.half) st4(a.half + 4 * v, s);
-                st4(agg_dst(a, 4 * v), div4(s, a.divisor));
+                st4(a.out + 4 * v, div4(s, a.divisor));
                 if (STAT) {
                     float4 e = x[u][0];
                     float4 o = K > 1 ? x[u][K > 1 ? 1 : 0] : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -193,8 +175,6 @@ struct UpdArgs {
     float divisor;                      // fused form: T
     int kagg;                           // 0: two-kernel form
     const float* grad_scale;            // nullable device scalar: g *= *grad_scale when it is < 1 (norm clipping)
-    int npeer;                          // > 0: element i of g is read from gk[i / shard_len][i] (peer memory)
-    unsigned long long shard_len;
     float* w[JABAS_MAX_VSW];
     float* m;
     float* v;
@@ -207,6 +187,7 @@ struct UpdArgs {
     int K;
     float half_divisor;
     const UpdHp* dyn;         // nullable: hyper-parameters live in device memory (CUDA-graph replay)
+    int no_bulk;              // a gradient source is another GPU's memory: per-thread loads only
     // bulk-staged form only: pipeline depth, stream slots per stage (sized for the launch's
     // largest stream count) and the device counter of waits that ran out
     int stages, stage_slots;
@@ -215,17 +196,6 @@ struct UpdArgs {
     unsigned int extra_tx;        // test seam: bytes a stage's barrier expects beyond what is copied
     UpdHp hp;                 // ... otherwise they travel in the argument block
 };
-
-// Base pointer of the rank that owns element `idx` of the reduced gradient (shards in rank order).
-__device__ __forceinline__ const float* peer_base(const UpdArgs& a, unsigned long long idx)
-{
-    unsigned long long owner = idx / a.shard_len;
-    const float* gp = a.gk[0];
-#pragma unroll
-    for (int r = 1; r < JABAS_MAX_VSW; ++r)
-        if (owner >= (unsigned long long)r && r < a.npeer) gp = a.gk[r];
-    return gp;
-}
 
 template <bool STAT>
 __device__ __forceinline__ void half_stat4(const UpdArgs& a, float4 g, float4 hs, Acc3& acc)
@@ -260,8 +230,6 @@ __device__ __forceinline__ void upd_elem(const UpdArgs& a, const UpdHp& H, unsig
         }
         g = __fdiv_rn(s, a.divisor);
         if (a.gout) a.gout[i] = g;
-    } else if (a.npeer > 0) {
-        g = peer_base(a, a.base + i)[a.base + i];
     } else {
         g = a.g[i];
     }
@@ -404,8 +372,6 @@ __global__ void __launch_bounds__(kThreads, BULK ? 3 : upd_min_ctas(KAGG)) upd_v
                     if (KAGG > 0) {
 #pragma unroll
                         for (int k = 0; k < KX; ++k) xk[u][k] = ld4(a.gk[k] + 4 * x);
-                    } else if (a.npeer > 0) {
-                        g[u] = ld4(peer_base(a, a.base + 4 * x) + a.base + 4 * x);
                     } else {
                         g[u] = ld4(a.g + 4 * x);
                     }
@@ -574,71 +540,6 @@ __global__ void clip_coef_kernel(const double* sumsq, float max_norm, float* out
     out[1] = total;
 }
 
-// Reduce-scatter over peer memory: this rank's shard [lo, hi) of the world-averaged gradient,
-// read straight from every rank's locally aggregated buffer over NVLink (plain loads, no
-// collective library).  Per element, in rank order:  g = sum_r fl(S_r / T)  — the reference's
-// div_(T) before the SUM allreduce — and the two halves E = sum over even ranks, O = sum over
-// odd ranks, divided by T/2, feed the cosine sums exactly as the pair exchange of
-// jabas/train/trainer.py:470-483 would.  Callers order this kernel after every rank's
-// aggregation with a collective barrier; nothing here waits on another GPU.
-struct PeerArgs {
-    const float* x[JABAS_MAX_VSW];      // one locally aggregated buffer per rank, rank order
-    float* gout;                        // this rank's reduced-gradient buffer (full-length base)
-    double* stat;
-    StatWs ws;
-    unsigned long long lo, hi;          // element range of this rank's shard, lo % 4 == 0
-    float divisor, half_divisor;
-    int n;
-};
-
-template <int NR, bool STAT>           // NR = 0: runtime rank count
-__global__ void __launch_bounds__(kThreads) peer_reduce_kernel(const PeerArgs a)
-{
-    const int n = NR > 0 ? NR : a.n;
-    const unsigned long long len = a.hi - a.lo, nvec = len >> 2;
-    Acc3 acc = {0.0, 0.0, 0.0};
-    for (unsigned long long v = (unsigned long long)blockIdx.x * kThreads + threadIdx.x; v < nvec;
-         v += (unsigned long long)gridDim.x * kThreads) {
-        const unsigned long long off = a.lo + 4 * v;
-        float4 x[NR > 0 ? NR : 1];
-        float4 g, e, o = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (NR > 0) {
-#pragma unroll
-            for (int r = 0; r < NR; ++r) x[r] = ld4(a.x[r] + off);
-            e = x[0];
-            g = div4(x[0], a.divisor);
-#pragma unroll
-            for (int r = 1; r < NR; ++r) {
-                g = add4(g, div4(x[r], a.divisor));
-                if (r == 1) o = x[1]; else if (r & 1) o = add4(o, x[r]); else e = add4(e, x[r]);
-            }
-        } else {
-            x[0] = ld4(a.x[0] + off);
-            e = x[0];
-            g = div4(x[0], a.divisor);
-            for (int r = 1; r < n; ++r) {
-                const float4 y = ld4(a.x[r] + off);
-                g = add4(g, div4(y, a.divisor));
-                if (r == 1) o = y; else if (r & 1) o = add4(o, y); else e = add4(e, y);
-            }
-        }
-        st4(a.gout + off, g);
-        if (STAT) acc_vec(acc, div4(e, a.half_divisor), div4(o, a.half_divisor));
-    }
-    if (blockIdx.x == 0 && threadIdx.x < (len & 3ull)) {       // ragged end of the last shard
-        const unsigned long long i = a.lo + (nvec << 2) + threadIdx.x;
-        float g = __fdiv_rn(a.x[0][i], a.divisor), e = a.x[0][i], o = 0.0f;
-        for (int r = 1; r < n; ++r) {
-            const float y = a.x[r][i];
-            g = __fadd_rn(g, __fdiv_rn(y, a.divisor));
-            if (r == 1) o = y; else if (r & 1) o = __fadd_rn(o, y); else e = __fadd_rn(e, y);
-        }
-        a.gout[i] = g;
-        if (STAT) acc_one(acc, __fdiv_rn(e, a.half_divisor), __fdiv_rn(o, a.half_divisor));
-    }
-    if (STAT) stat_finish(acc, a.ws, a.stat);
-}
-
 struct RepArgs {
     const float* src;
     float* dst[JABAS_MAX_VSW];
@@ -788,7 +689,7 @@ int upd_launch_vec(jabas_ctx_t* ctx, UpdArgs& a, cudaStream_t st)
         return fail(JABAS_EINVAL, "fused aggregate+update supports at most 8 VSWs");
     }
     int grid = 0, rc;
-    if (ctx->staging == JABAS_STAGING_BULK && a.npeer == 0) {
+    if (ctx->staging == JABAS_STAGING_BULK && !a.no_bulk) {
         // slots for the launch's largest stream count: gradients, p, m [, v] [, half]
         a.stage_slots = (KAGG > 0 ? KAGG : 1) + 2 + (OPT == OPT_ADAM ? 1 : 0) + ((a.stat && KAGG == 0) ? 1 : 0);
         a.stages = stage_count(a.stage_slots);
@@ -856,7 +757,6 @@ int upd_prepare(jabas_ctx_t* ctx, UpdArgs& a, bool* vec, const GradSrc& src, flo
     if (!w) return fail(JABAS_EINVAL, "w is null");
     if (K < 1 || K > JABAS_MAX_VSW) return fail(JABAS_EINVAL, "K must be in [1, JABAS_MAX_VSW]");
     const bool fused = src.grads != nullptr;
-    // (a null g is legal when the gradient comes from peer shards; checked by the callers)
     if (fused) {
         if (src.kg < 1 || src.kg > kMaxFusedVsw)
             return fail(JABAS_EINVAL, "fused aggregate+update supports 1..8 VSW gradients");
@@ -1107,45 +1007,6 @@ int jabas_vsw_aggregate_f32(jabas_ctx_t* ctx, const float* const* grads, int K, 
     return JABAS_OK;
 }
 
-int jabas_vsw_aggregate_scatter_f32(jabas_ctx_t* ctx, const float* const* grads, int K,
-                                    float* const* slots, int nranks, uint64_t shard_len, uint64_t n,
-                                    float divisor, void* stream)
-{
-    int rc = ctx_bind(ctx);
-    if (rc) return rc;
-    if (!grads || !slots) return fail(JABAS_EINVAL, "grads or slots is null");
-    if (K < 1 || K > JABAS_MAX_VSW) return fail(JABAS_EINVAL, "K must be in [1, JABAS_MAX_VSW]");
-    if (nranks < 1 || nranks > JABAS_MAX_VSW) return fail(JABAS_EINVAL, "nranks must be in [1, 16]");
-    if (shard_len == 0 || (shard_len & 3ull)) return fail(JABAS_EINVAL, "shard_len must be a positive multiple of 4");
-    if ((uint64_t)nranks * shard_len < n) return fail(JABAS_EINVAL, "nranks * shard_len must cover n");
-    if (!(divisor != 0.0f)) return fail(JABAS_EINVAL, "divisor must be non-zero");
-    if (n == 0) return JABAS_OK;
-    AggArgs a;
-    std::memset(&a, 0, sizeof(a));
-    bool vec = true;
-    for (int k = 0; k < K; ++k) {
-        if (!grads[k]) return fail(JABAS_EINVAL, "grads[k] is null");
-        a.g[k] = grads[k];
-        vec = vec && aligned16(grads[k]);
-    }
-    for (int r = 0; r < nranks; ++r) {
-        if (!slots[r]) return fail(JABAS_EINVAL, "slots[r] is null");
-        a.scatter[r] = slots[r];
-        vec = vec && aligned16(slots[r]);
-    }
-    a.nscatter = nranks; a.shard_len = shard_len; a.n = n; a.divisor = divisor; a.half_divisor = 1.0f; a.K = K;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (vec) {
-        if ((rc = agg_dispatch<1>(ctx, a, st))) return rc;
-    } else {
-        int grid = 0;
-        if ((rc = grid_for(ctx, agg_scalar_kernel<false>, n, kThreads, &grid))) return rc;
-        agg_scalar_kernel<false><<<grid, kThreads, 0, st>>>(a);
-    }
-    JB_CUDA(cudaGetLastError());
-    return JABAS_OK;
-}
-
 int jabas_div_f32(jabas_ctx_t* ctx, float* x, uint64_t n, float divisor, void* stream)
 {
     int rc = ctx_bind(ctx);
@@ -1158,24 +1019,6 @@ int jabas_div_f32(jabas_ctx_t* ctx, float* x, uint64_t n, float divisor, void* s
     if ((rc = grid_for(ctx, div_kernel, vec ? (n + 3) / 4 : n, kThreads, &grid))) return rc;
     div_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, n, divisor, vec);
     JB_CUDA(cudaGetLastError());
-    return JABAS_OK;
-}
-
-// Gradient read from the reduced shards that live in the ranks' peer-mapped buffers.
-static int set_peer_src(UpdArgs& a, const jabas_peer_src_t* ps, bool* vec)
-{
-    if (!ps) return JABAS_OK;
-    if (a.kagg > 0) return fail(JABAS_EINVAL, "peer_grad cannot be combined with the fused single-GPU form");
-    if (!ps->bufs || ps->n < 1 || ps->n > JABAS_MAX_VSW) return fail(JABAS_EINVAL, "peer_grad: 1..16 buffers");
-    if (ps->shard_len == 0 || (ps->shard_len & 3ull)) return fail(JABAS_EINVAL, "peer_grad: shard_len must be a positive multiple of 4");
-    a.npeer = ps->n;
-    a.shard_len = ps->shard_len;
-    for (int r = 0; r < ps->n; ++r) {
-        if (!ps->bufs[r]) return fail(JABAS_EINVAL, "peer_grad: null buffer");
-        a.gk[r] = ps->bufs[r];
-        *vec = *vec && aligned16(ps->bufs[r]);
-    }
-    *vec = *vec && ((a.base & 3ull) == 0);
     return JABAS_OK;
 }
 
@@ -1195,7 +1038,7 @@ static int sgd_impl(jabas_ctx_t* ctx, const GradSrc& src, float* const* w, int K
         return fail(JABAS_EINVAL, "nesterov needs momentum > 0 and dampening == 0");
     if (n == 0) return JABAS_OK;
     a.grad_scale = hp->grad_scale;
-    if ((rc = set_peer_src(a, hp->peer_grad, &vec))) return rc;
+    a.no_bulk = hp->remote_sources ? 1 : 0;
     if ((rc = jb_fill_sgd_hp(a.hp, groups, ngroups, hp))) return rc;
     if (hp->dynamic) {
         if (hp->dynamic->kind != OPT_SGD) return fail(JABAS_EINVAL, "the dynamic block holds Adam hyper-parameters");
@@ -1210,7 +1053,7 @@ int jabas_sgd_momentum_f32(jabas_ctx_t* ctx, const float* g, float* const* w, in
                            const float* half, float half_divisor, double* stat3, void* stream)
 {
     const GradSrc src = {g, nullptr, 0, 1.0f, nullptr};
-    if (!g && !(hp && hp->peer_grad)) return fail(JABAS_EINVAL, "g is null");
+    if (!g) return fail(JABAS_EINVAL, "g is null");
     return sgd_impl(ctx, src, w, K, m, n, base, layout, groups, ngroups, hp, half, half_divisor, stat3, stream);
 }
 
@@ -1239,7 +1082,7 @@ static int adam_impl(jabas_ctx_t* ctx, const GradSrc& src, float* const* w, int 
     if (!m || !v) return fail(JABAS_EINVAL, "exp_avg and exp_avg_sq buffers are required");
     if (n == 0) return JABAS_OK;
     a.grad_scale = hp->grad_scale;
-    if ((rc = set_peer_src(a, hp->peer_grad, &vec))) return rc;
+    a.no_bulk = hp->remote_sources ? 1 : 0;
     if ((rc = jb_fill_adam_hp(a.hp, groups, ngroups, hp))) return rc;
     if (hp->dynamic) {
         if (hp->dynamic->kind != OPT_ADAM) return fail(JABAS_EINVAL, "the dynamic block holds SGD hyper-parameters");
@@ -1254,7 +1097,7 @@ int jabas_adam_f32(jabas_ctx_t* ctx, const float* g, float* const* w, int K, flo
                    const float* half, float half_divisor, double* stat3, void* stream)
 {
     const GradSrc src = {g, nullptr, 0, 1.0f, nullptr};
-    if (!g && !(hp && hp->peer_grad)) return fail(JABAS_EINVAL, "g is null");
+    if (!g) return fail(JABAS_EINVAL, "g is null");
     return adam_impl(ctx, src, w, K, m, v, n, base, layout, groups, ngroups, hp, half, half_divisor, stat3, stream);
 }
 
@@ -1353,48 +1196,6 @@ int jabas_dot_norms_f32(jabas_ctx_t* ctx, const float* a, const float* b, uint64
     int grid = 0;
     if ((rc = grid_for(ctx, dot_norms_kernel<false>, vec ? (n + 3) / 4 : n, vec ? kThreads * 4 : kThreads, &grid))) return rc;
     dot_norms_kernel<false><<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(a, b, n, vec, ws, stat3);
-    JB_CUDA(cudaGetLastError());
-    return JABAS_OK;
-}
-
-int jabas_peer_reduce_f32(jabas_ctx_t* ctx, const float* const* xs, int n, float* g_out, uint64_t lo,
-                          uint64_t hi, float divisor, float half_divisor, double* stat3, void* stream)
-{
-    int rc = ctx_bind(ctx);
-    if (rc) return rc;
-    if (!xs || !g_out) return fail(JABAS_EINVAL, "xs or g_out is null");
-    if (n < 1 || n > JABAS_MAX_VSW) return fail(JABAS_EINVAL, "n must be in [1, 16]");
-    if (hi < lo || (lo & 3ull)) return fail(JABAS_EINVAL, "shard must start on a multiple of 4 elements");
-    if (!(divisor != 0.0f)) return fail(JABAS_EINVAL, "divisor must be non-zero");
-    if (stat3 && (n < 2 || !(half_divisor != 0.0f)))
-        return fail(JABAS_EINVAL, "the two-half statistic needs n >= 2 and a non-zero half_divisor");
-    if (hi == lo) return JABAS_OK;
-    PeerArgs a;
-    std::memset(&a, 0, sizeof(a));
-    if (!aligned16(g_out)) return fail(JABAS_EINVAL, "peer buffers must be 16-byte aligned");
-    for (int r = 0; r < n; ++r) {
-        if (!xs[r] || !aligned16(xs[r])) return fail(JABAS_EINVAL, "peer buffers must be non-null and 16-byte aligned");
-        a.x[r] = xs[r];
-    }
-    a.gout = g_out; a.stat = stat3; a.lo = lo; a.hi = hi; a.divisor = divisor;
-    a.half_divisor = half_divisor; a.n = n;
-    if (stat3 && (rc = ws_for(ctx, stream, &a.ws))) return rc;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    int grid = 0;
-    const unsigned long long nvec = ((hi - lo) >> 2) + 1;
-#define JB_PEER_LAUNCH(NR, ST)                                                                     \
-    do {                                                                                           \
-        if ((rc = grid_for(ctx, peer_reduce_kernel<NR, ST>, nvec, kThreads, &grid))) return rc;     \
-        peer_reduce_kernel<NR, ST><<<grid, kThreads, 0, st>>>(a);                                   \
-    } while (0)
-    if (stat3) {
-        if (n == 2) JB_PEER_LAUNCH(2, true); else if (n == 4) JB_PEER_LAUNCH(4, true);
-        else if (n == 8) JB_PEER_LAUNCH(8, true); else JB_PEER_LAUNCH(0, true);
-    } else {
-        if (n == 2) JB_PEER_LAUNCH(2, false); else if (n == 4) JB_PEER_LAUNCH(4, false);
-        else if (n == 8) JB_PEER_LAUNCH(8, false); else JB_PEER_LAUNCH(0, false);
-    }
-#undef JB_PEER_LAUNCH
     JB_CUDA(cudaGetLastError());
     return JABAS_OK;
 }

@@ -69,8 +69,8 @@ class GradientPath:
             # a launch that reads another GPU's memory through per-thread loads or the exchange's own
             # TMA ring never goes through the update kernels' bulk-staged form
             raise ValueError("staging='bulk' cannot be combined with collective='peer'")
-        if peer_form not in ("pipeline", "pull", "scatter", "direct"):
-            raise ValueError("peer_form must be 'pipeline', 'pull', 'scatter' or 'direct'")
+        if peer_form not in ("pipeline", "direct"):
+            raise ValueError("peer_form must be 'pipeline' or 'direct'")
         if backend is None:
             from . import ops as backend          # the CUDA library; raises without a GPU
         self.ops = backend
@@ -124,10 +124,10 @@ class GradientPath:
         #:              pieces from an ordered queue; ranks synchronise through epoch flags in peer
         #:              memory (bounded waits), so NVLink and HBM phases overlap chunk by chunk; works
         #:              per bucket (hooks during backward) and over the whole model
-        #:   "pull"     three kernels over the whole model separated by NCCL barriers: aggregate,
-        #:              reduce kernel that reads its shard from every rank, gathering update
-        #:   "scatter"  as "pull", but the aggregate kernel stores its sums into the owners' slots
-        #:   "direct"   two ranks only: the update kernel reads both ranks' sums itself
+        #:   "direct"   two ranks only, whole model at step time: an aggregate kernel, an NCCL barrier,
+        #:              and the fused update kernel reads both ranks' sums itself (the remote one over
+        #:              NVLink); 10 % faster than the pipeline on a ResNet-50-sized model, slower on
+        #:              large ones, and it cannot run per bucket
         self.peer_form = peer_form
         self.peer_direct = peer_form == "direct"
         if self.peer_direct and self.world != 2 and self.collective == "peer":
@@ -164,31 +164,17 @@ class GradientPath:
             self.set_optimizer(optimizer)
 
     def _setup_peer_exchange(self) -> None:
-        """Peer-memory exchange: two symmetric buffers per rank, mapped into every rank's
+        """The two-rank direct form: one symmetric buffer per rank, mapped into the other rank's
         address space over NVLink (torch symmetric memory does the allocation and the handle
         exchange; the data path is this library's kernels).  ``px`` receives the local sum of
-        the K VSW gradients, ``pg`` this rank's shard of the world-averaged gradient."""
+        the K VSW gradients, divided by T."""
         import torch.distributed._symmetric_memory as symm_mem
-        n, world = self.layout.total, self.world
+        n = self.layout.total
         group = self.pg if self.pg is not None else dist.group.WORLD
-        shard = -(-n // world)
-        self.shard_len = -(-shard // 32) * 32                       # 128-byte aligned shards
-        self.shard_lo = min(self.rank * self.shard_len, n)
-        self.shard_hi = min(self.shard_lo + self.shard_len, n)
-        # px: `world` staging slots of one shard each (slot r = rank r's contribution to the
-        # shard this rank reduces); the two-rank direct form uses it as one full-length buffer
-        self.px = symm_mem.empty(world * self.shard_len, dtype=torch.float32, device=self.device)
-        self.pgrad = symm_mem.empty(n, dtype=torch.float32, device=self.device)
-        self.px.zero_(); self.pgrad.zero_()
+        self.px = symm_mem.empty(n, dtype=torch.float32, device=self.device)
+        self.px.zero_()
         self._px_h = symm_mem.rendezvous(self.px, group)
-        self._pg_h = symm_mem.rendezvous(self.pgrad, group)
         self.px_ptrs = [int(p) for p in self._px_h.buffer_ptrs]
-        self.pg_ptrs = [int(p) for p in self._pg_h.buffer_ptrs]
-        # where this rank's partial sums go: its slot inside every owner's staging buffer
-        self._scatter_ptrs = [p + 4 * self.rank * self.shard_len for p in self.px_ptrs]
-        # the `world` local slots, addressed so that slot r holds elements [shard_lo, shard_hi)
-        self._slot_ptrs = [self.px.data_ptr() + 4 * (r * self.shard_len - self.shard_lo) for r in range(world)]
-        self._peer_grad = self.ops.PeerGrad(self.pg_ptrs, self.shard_len)
         self._tok = torch.zeros(1, dtype=torch.float32, device=self.device)
 
     def _setup_pipeline_exchange(self) -> None:
@@ -278,53 +264,27 @@ class GradientPath:
 
     def _peer_iteration(self) -> Optional[torch.Tensor]:
         """Whole flat model through the peer-memory exchange.  ``peer_form="pipeline"``: one
-        launch (plus the 32-thread statistic kernel).  The older forms, more than two ranks:
-        aggregate -> barrier -> reduce kernel for this rank's shard (reads every rank's sums
-        over NVLink, or, in the "scatter" form, the local staging slots the aggregate kernels
-        stored into; statistic from the exact even/odd-rank halves) -> barrier carrying the
-        3-double statistic -> update kernel that gathers the gradient shards over NVLink."""
+        launch (plus the 32-thread statistic kernel).  ``"direct"`` (two ranks): aggregate kernel,
+        barrier, fused update kernel that reads both ranks' sums, barrier."""
         if self.exchange is not None:
             self.exchange_launch(None)
             return self.finish_similarity()
         sim = self._sim_step
         n = self.layout.total
-        direct = self.peer_direct and self.world <= getattr(self.ops, "MAX_FUSED_VSW", 0)
         ev = self._ev_begin()
-        scatter = not direct and self.peer_form == "scatter"
-        if scatter:
-            self.ops.vsw_aggregate_scatter(self.ctx, self.grads, self._scatter_ptrs, self.shard_len, n, 1.0)
-        elif direct:
-            # each rank's sum is divided by T BEFORE the two are added, as everywhere else on the
-            # path (the reference's div_(T) before the SUM allreduce): g = fl(S0/T) + fl(S1/T)
-            self.ops.vsw_aggregate(self.ctx, self.grads, self.px[:n], float(self.T))
-        else:
-            self.ops.vsw_aggregate(self.ctx, self.grads, self.px[:n], 1.0)         # undivided local sum
+        # each rank's sum is divided by T BEFORE the two are added, as everywhere else on the
+        # path (the reference's div_(T) before the SUM allreduce): g = fl(S0/T) + fl(S1/T)
+        self.ops.vsw_aggregate(self.ctx, self.grads, self.px[:n], float(self.T))
         self._ev_end("aggregate", None, ev)
-        dist.all_reduce(self._tok, group=self.pg)                                  # every rank's sums are in place
-        if direct:
-            # Two GPUs: the update kernel itself reads both ranks' sums (the remote one over
-            # NVLink, hidden under its own HBM traffic), averages, takes the statistic from
-            # the two ranks = the two halves, and updates: no reduce-scatter pass at all.
-            # the sums arrive divided by T: the kernel adds them as they are (divisor 1) and gets the
-            # halves E, O = S_r / (T/2) by dividing the divided sums by 1/2 (exact)
-            self.fused_local_step(None, sources=self.px_ptrs, divisor=1.0, half_divisor=0.5)
-            dist.all_reduce(self._tok, group=self.pg)      # nobody overwrites its sum while a peer still reads it
-            self.launches += 1
-            if sim:
-                self.ops.cosine_finalize(self.ctx, self.stat, self.cos)            # same bits on both ranks
-                self.launches += 1
-                return self.cos
-            return None
-        ev = self._ev_begin()
-        self.ops.peer_reduce(self.ctx, self._slot_ptrs if scatter else self.px_ptrs, self.pgrad.data_ptr(),
-                             self.shard_lo, self.shard_hi,
-                             float(self.T), half_divisor=self.T / 2, stat=self.stat if sim else None)
-        self._ev_end("peer_reduce", None, ev)
-        dist.all_reduce(self.stat if sim else self._tok, group=self.pg)            # barrier + global sums
-        self.launches += 2
-        self.update(None)
+        dist.all_reduce(self._tok, group=self.pg)                                  # both ranks' sums are in place
+        # The update kernel itself reads both ranks' sums (the remote one over NVLink, hidden under
+        # its own HBM traffic), adds them as they are (divisor 1), takes the statistic from the two
+        # ranks = the two halves (E, O = S_r / (T/2): the divided sums over 1/2, exact) and updates.
+        self.fused_local_step(None, sources=self.px_ptrs, divisor=1.0, half_divisor=0.5)
+        dist.all_reduce(self._tok, group=self.pg)      # nobody overwrites its sum while the peer still reads it
+        self.launches += 1
         if sim:
-            self.ops.cosine_finalize(self.ctx, self.stat, self.cos)                # identical on every rank
+            self.ops.cosine_finalize(self.ctx, self.stat, self.cos)                # same bits on both ranks
             self.launches += 1
             return self.cos
         return None
@@ -481,11 +441,10 @@ class GradientPath:
         if end == begin:
             return
         kw = dict(layout=self.dev_layout, base=begin)
-        peer = self.collective == "peer"
-        fused_stat = self._sim_step and self.world > 1 and self.similarity_mode == "fused" and not peer
-        if peer:
-            pass                                       # the statistic came from the reduce-scatter kernel
-        elif fused_stat:
+        if self.collective == "peer":
+            raise RuntimeError("with collective='peer' the update is part of the exchange")
+        fused_stat = self._sim_step and self.world > 1 and self.similarity_mode == "fused"
+        if fused_stat:
             kw.update(half=self.half[begin:end], half_divisor=self.T / 2, stat=self.stat)
         elif self._sim_step and self.world > 1:
             for bb in (range(self.layout.num_buckets) if b is None else (b,)):
@@ -501,9 +460,6 @@ class GradientPath:
         if self._dyn is not None:
             kw["dynamic"] = self._dyn
         g = self.main_grad[begin:end]
-        if self.collective == "peer":
-            g, kw["peer_grad"] = None, self._peer_grad
-            kw.pop("half", None); kw.pop("half_divisor", None); kw.pop("stat", None)
         ws = self._replicas(begin, end)
         o = self.opt
         ev = self._ev_begin()
@@ -789,19 +745,12 @@ class GradientPath:
             out["nvlink_in"] = 2 * 4 * n * (w - 1) // w
             return out
         if self.collective == "peer":
-            # what the kernels of the peer exchange move through THIS GPU's HBM: the aggregate
-            # reads K gradients and writes one buffer's worth of partial sums (1/n of it locally,
-            # the rest into peers, whose stores land here in turn), the reduce kernel reads the
-            # n local slots and writes its shard
+            # two-rank direct form: an aggregate kernel, then the fused kernel: this GPU's sum is read
+            # once by its own update kernel and once by the peer's; the remote sum arrives over
+            # NVLink (4n bytes in)
             out["aggregate"] = 4 * n * (K + 1)
-            out["peer_reduce"] = 4 * n + 4 * n // self.world
-            out["update"] = 4 * n * per_elem
-            out["nvlink_in"] = 2 * 4 * n * (self.world - 1) // self.world
-            if self.peer_direct:
-                # direct form: this GPU's sum is read once by its own update kernel and once by
-                # the peer's; the remote sum arrives over NVLink (4n bytes in)
-                out["fused_step"] = 4 * n * (per_elem + 1)
-                out["nvlink_in"] = 4 * n
+            out["fused_step"] = 4 * n * (per_elem + 1)
+            out["nvlink_in"] = 4 * n
         return out
 
     def close(self) -> None:
@@ -815,7 +764,7 @@ class GradientPath:
         if self.exchange is not None:
             self.exchange.close()
             self.exchange = None
-        for name in ("_px_h", "_pg_h", "_fl_h", "_peer_grad", "px", "pgrad", "xflags"):
+        for name in ("_px_h", "_pg_h", "_fl_h", "px", "pgrad", "xflags"):
             if hasattr(self, name):
                 setattr(self, name, None)
         if self.dev_layout is not None:

@@ -124,7 +124,7 @@ class IIDPTrainer(object):
         # collective="peer": several GPUs exchange gradients through this library's kernels over
         # NVLink peer memory.  peer_form="pipeline" (default): one pipelined kernel per bucket, fired
         # by the bucket's hook chain during backward ('overlap'), or one over the whole model at step
-        # time ('sequential'); the other forms run once per iteration at step time only
+        # time ('sequential'); peer_form="direct" (two GPUs) runs once per iteration at step time only
         collective = kwargs.pop("collective", "nccl")
         peer_form = kwargs.pop("peer_form", "pipeline")
         if collective == "peer" and peer_form != "pipeline" and self.weight_sync_method != "sequential":

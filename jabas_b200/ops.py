@@ -53,23 +53,6 @@ def _dyn_ptr(d) -> Optional[int]:
     return None if d is None else d._h
 
 
-class PeerGrad:
-    """The world-averaged gradient as it lies after :func:`peer_reduce`: shard ``r`` of the
-    flat buffer lives in rank ``r``'s buffer ``ptrs[r]`` (device pointers valid on this GPU)."""
-
-    def __init__(self, ptrs: Sequence[int], shard_len: int):
-        self.ptrs, self.shard_len = [int(p) for p in ptrs], int(shard_len)
-        self._arr = (ctypes.c_void_p * len(self.ptrs))(*self.ptrs)
-        self._struct = _lib.PeerSrc(self._arr, len(self.ptrs), 0, self.shard_len)
-
-    def ref(self):
-        return ctypes.pointer(self._struct)
-
-
-def _peer_ref(p: Optional[PeerGrad]):
-    return None if p is None else p.ref()
-
-
 def _ptr_array(ptrs: Sequence[int]):
     return (ctypes.c_void_p * len(ptrs))(*ptrs)
 
@@ -167,13 +150,13 @@ class DynHp:
 
     def push_sgd(self, groups: Sequence[dict], *, momentum: float = 0.0, dampening: float = 0.0,
                  nesterov: bool = False, first_step: bool = False, stream=None) -> None:
-        hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), None, None)
+        hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), None, None, 0, 0)
         _lib.check(self.ctx._lib.jabas_dynhp_push_sgd(self._h, _groups_array(groups), len(groups),
                                                       ctypes.byref(hp), _stream_handle(self.ctx.device, stream)))
 
     def push_adam(self, groups: Sequence[dict], *, beta1: float, beta2: float, eps: float,
                   decoupled: bool, stream=None) -> None:
-        hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0, None, None)
+        hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0, None, None, 0, 0)
         _lib.check(self.ctx._lib.jabas_dynhp_push_adam(self._h, _groups_array(groups), len(groups),
                                                        ctypes.byref(hp), _stream_handle(self.ctx.device, stream)))
 
@@ -224,9 +207,9 @@ def sgd_momentum(ctx: Context, g: torch.Tensor, weights: Sequence[torch.Tensor],
                  layout: Optional[Layout] = None, base: int = 0,
                  half: Optional[torch.Tensor] = None, half_divisor: float = 1.0,
                  stat: Optional[torch.Tensor] = None, grad_scale: Optional[torch.Tensor] = None,
-                 dynamic: Optional["DynHp"] = None, peer_grad: Optional[PeerGrad] = None, stream=None) -> None:
+                 dynamic: Optional["DynHp"] = None, stream=None) -> None:
     """Fused SGD-momentum update of ``weights[0]`` with write-back to every replica."""
-    hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic), _peer_ref(peer_grad))
+    hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic), 0, 0)
     wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
     _lib.check(ctx._lib.jabas_sgd_momentum_f32(
         ctx._h, None if g is None else _dev_f32(g, ctx.device, "g"), wp, len(weights),
@@ -241,9 +224,9 @@ def adam(ctx: Context, g: torch.Tensor, weights: Sequence[torch.Tensor], m: torc
          decoupled: bool, layout: Optional[Layout] = None, base: int = 0,
          half: Optional[torch.Tensor] = None, half_divisor: float = 1.0,
          stat: Optional[torch.Tensor] = None, grad_scale: Optional[torch.Tensor] = None,
-         dynamic: Optional["DynHp"] = None, peer_grad: Optional[PeerGrad] = None, stream=None) -> None:
+         dynamic: Optional["DynHp"] = None, stream=None) -> None:
     """Fused Adam (``decoupled=False``) / AdamW (``True``) update with write-back."""
-    hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0, _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic), _peer_ref(peer_grad))
+    hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0, _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic), 0, 0)
     wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
     _lib.check(ctx._lib.jabas_adam_f32(
         ctx._h, None if g is None else _dev_f32(g, ctx.device, "g"), wp, len(weights),
@@ -265,7 +248,7 @@ def vsw_sgd_momentum(ctx: Context, grads: Sequence[torch.Tensor], divisor: float
                      stat: Optional[torch.Tensor] = None, grad_scale: Optional[torch.Tensor] = None,
                      dynamic: Optional["DynHp"] = None, stream=None) -> None:
     """Single-GPU path in one launch: aggregate the VSW gradients, update, write back."""
-    hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic), None)
+    hp = _lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic), int(any(isinstance(g, int) for g in grads)), 0)
     gp = _ptr_array([_dev_f32(g, ctx.device, "grads[k]") for g in grads])
     wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
     _lib.check(ctx._lib.jabas_vsw_sgd_momentum_f32(
@@ -283,7 +266,7 @@ def vsw_adam(ctx: Context, grads: Sequence[torch.Tensor], divisor: float,
              stat: Optional[torch.Tensor] = None, grad_scale: Optional[torch.Tensor] = None,
              dynamic: Optional["DynHp"] = None, stream=None) -> None:
     """Adam / AdamW counterpart of :func:`vsw_sgd_momentum`."""
-    hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0, _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic), None)
+    hp = _lib.AdamHp(beta1, beta2, eps, int(decoupled), 0, _scale_ptr(grad_scale, ctx.device), _dyn_ptr(dynamic), int(any(isinstance(g, int) for g in grads)), 0)
     gp = _ptr_array([_dev_f32(g, ctx.device, "grads[k]") for g in grads])
     wp = _ptr_array([_dev_f32(w, ctx.device, "weights[k]") for w in weights])
     _lib.check(ctx._lib.jabas_vsw_adam_f32(
@@ -299,26 +282,6 @@ def dot_norms(ctx: Context, a: torch.Tensor, b: torch.Tensor, stat: torch.Tensor
                                             _dev_f32(b, ctx.device, "b"), a.numel(),
                                             _stat_ptr(stat, ctx.device),
                                             _stream_handle(ctx.device, stream)))
-
-
-def vsw_aggregate_scatter(ctx: Context, grads: Sequence[torch.Tensor], slot_ptrs: Sequence[int],
-                          shard_len: int, n: int, divisor: float, *, stream=None) -> None:
-    """Local sum of the K VSW gradients / divisor, scattered shard by shard into the staging
-    slots ``slot_ptrs[j]`` (raw device pointers into rank j's peer-mapped buffer)."""
-    gp = _ptr_array([_dev_f32(g, ctx.device, "grads[k]") for g in grads])
-    sp = _ptr_array([int(p) for p in slot_ptrs])
-    _lib.check(ctx._lib.jabas_vsw_aggregate_scatter_f32(ctx._h, gp, len(grads), sp, len(slot_ptrs), shard_len,
-                                                        n, divisor, _stream_handle(ctx.device, stream)))
-
-
-def peer_reduce(ctx: Context, peer_ptrs: Sequence[int], g_out_ptr: int, lo: int, hi: int, divisor: float, *,
-                half_divisor: float = 1.0, stat: Optional[torch.Tensor] = None, stream=None) -> None:
-    """This rank's shard ``[lo, hi)`` of the world-averaged gradient, read from every rank's
-    locally aggregated buffer over NVLink peer mappings (raw device pointers, rank order)."""
-    arr = _ptr_array([int(p) for p in peer_ptrs])
-    _lib.check(ctx._lib.jabas_peer_reduce_f32(ctx._h, arr, len(peer_ptrs), int(g_out_ptr), lo, hi, divisor,
-                                              half_divisor, _stat_ptr(stat, ctx.device),
-                                              _stream_handle(ctx.device, stream)))
 
 
 def sumsq(ctx: Context, x: torch.Tensor, stat: torch.Tensor, *, stream=None) -> None:
@@ -429,9 +392,9 @@ def exchange_step(exs: Sequence[Exchange], bufs: Sequence[dict], n: int, base: i
     hs = _ptr_array([e._h.value for e in exs])
     sgd = adam = None
     if kind == "sgd":
-        sgd = ctypes.pointer(_lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), None, _dyn_ptr(dynamic), None))
+        sgd = ctypes.pointer(_lib.SgdHp(momentum, dampening, int(nesterov), int(first_step), None, _dyn_ptr(dynamic), 0, 0))
     else:
-        adam = ctypes.pointer(_lib.AdamHp(beta1, beta2, eps, int(kind == "adamw"), 0, None, _dyn_ptr(dynamic), None))
+        adam = ctypes.pointer(_lib.AdamHp(beta1, beta2, eps, int(kind == "adamw"), 0, None, _dyn_ptr(dynamic), 0, 0))
     _lib.check(ctx._lib.jabas_exchange_step_f32(
         hs, arr, len(exs), int(n), int(base), int(slot_base), float(divisor), float(half_divisor),
         None if layout is None else layout._h, _groups_array(groups), len(groups), sgd, adam,
@@ -479,5 +442,5 @@ def replicate(ctx: Context, src: torch.Tensor, dsts: Sequence[torch.Tensor], *, 
                                             src.numel(), _stream_handle(ctx.device, stream)))
 
 
-__all__ = ["Context", "Layout", "DynHp", "PeerGrad", "Exchange", "exchange_step", "exchange_cosine", "exchange_flag_words", "EXCHANGE_PIECE", "peer_reduce", "vsw_aggregate_scatter", "JabasError", "MAX_VSW", "MAX_GROUPS", "vsw_aggregate", "div_",
+__all__ = ["Context", "Layout", "DynHp", "Exchange", "exchange_step", "exchange_cosine", "exchange_flag_words", "EXCHANGE_PIECE", "JabasError", "MAX_VSW", "MAX_GROUPS", "vsw_aggregate", "div_",
            "sgd_momentum", "adam", "vsw_sgd_momentum", "vsw_adam", "MAX_FUSED_VSW", "sumsq", "clip_coef", "dot_norms", "dot_norms_static", "cosine_finalize", "replicate"]

@@ -130,7 +130,7 @@ def _engine_rank(rank, world, port, collective, kind, K, q, direct=None):
         T = world * K
         form = direct or "pipeline"
         if form == "direct" and world != 2:
-            form = "pull"                                  # the direct form exists for two ranks only
+            form = "pipeline"                              # the direct form exists for two ranks only
         eng = GradientPath(layout, K, torch.device("cuda", rank), spec, total_num_decoupled_workers=T,
                            sub_group=groups[rank % 2], pair_group=pair, collective=collective, peer_form=form)
         ref = ReferencePath(layout, K, opt, total_num_decoupled_workers=T, arith="c")
@@ -190,15 +190,14 @@ def _engine_rank(rank, world, port, collective, kind, K, q, direct=None):
 
 @pytest.mark.parametrize("collective,kind,K,direct", [
     ("peer", "sgd", 4, "pipeline"), ("peer", "adamw", 2, "pipeline"), ("peer", "adam", 1, "pipeline"),
-    ("peer", "sgd", 4, "direct"), ("peer", "sgd", 3, "direct"), ("peer", "adamw", 1, "pull"), ("peer", "sgd", 2, "scatter"),
+    ("peer", "sgd", 4, "direct"), ("peer", "sgd", 3, "direct"), ("peer", "adamw", 1, "direct"),
     ("nccl", "sgd", 2, None)])
 def test_engine_exchange_modes_match_reference_path(collective, kind, K, direct):
     """The gradient path at engine level on 2 (or, when visible, 4) GPUs: the peer-memory
     exchange in its forms (``pipeline``: one persistent kernel with flag-ordered aggregate /
-    reduce / update pieces; ``direct``: the update kernel reads both ranks' sums; ``pull``: a
-    reduce kernel that reads its shard from the peers; ``scatter``: local staging slots filled
-    by scattering aggregate kernels), eager and as a replayed CUDA graph, and the NCCL
-    exchange, against the reference path over gloo."""
+    reduce / update pieces; ``direct``, two ranks: the update kernel reads both ranks' sums, T = 6
+    included, where dividing before or after the addition differs in the last bit), eager and as a
+    replayed CUDA graph, and the NCCL exchange, against the reference path over gloo."""
     world = 2 if torch.cuda.device_count() < 4 else 4
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
