@@ -252,7 +252,7 @@ JABAS_API int jabas_dot_norms_f32(jabas_ctx_t* ctx, const float* a, const float*
  * launches of one iteration that cover different ranges (one per DDP bucket) use disjoint slots.
  * Every rank must issue the same sequence of launches.  Launches of one exchange must not overlap
  * on the GPU (keep them on one stream). */
-#define JABAS_EXCHANGE_PIECE 16384u      /* default elements of one work item, per stream */
+#define JABAS_EXCHANGE_PIECE 8192u       /* default elements of one work item, per stream */
 typedef struct jabas_exchange jabas_exchange_t;
 typedef struct {
     int nranks;                     /* 2..8 */
@@ -290,6 +290,11 @@ JABAS_API int jabas_exchange_reset(jabas_exchange_t* ex);
  * the phase that gave up: 2 reduce, 3 update, 4 statistic, bits 0..23 the piece slot) and, optionally,
  * of the number of completed launches. */
 JABAS_API int jabas_exchange_status(jabas_exchange_t* ex, uint32_t* status, uint32_t* launches);
+
+/* Kernel variant of the following launches: 2 resident CTAs per SM with a 96 KB ring each, 3 with a
+ * 64 KB ring and 64 registers per thread, or 0 (default): 3 where the ring still holds three stages
+ * (at most five streams per stage: K and nranks up to 5), else 2. */
+JABAS_API int jabas_exchange_set_ctas_per_sm(jabas_exchange_t* ex, int ctas);
 
 /* Largest grid of the following launches (0, the default: every CTA the GPU can hold).  A launch
  * that shares the GPU with other work — the per-bucket launches fired during backward — should

@@ -25,10 +25,10 @@ EXPORTS = (
     "jabas_ctx_set_staging", "jabas_ctx_staging_timeouts", "jabas_ctx_set_wait_limits",
     "jabas_ctx_inject_staging_stall", "jabas_exchange_flag_words", "jabas_exchange_create",
     "jabas_exchange_destroy", "jabas_exchange_reset", "jabas_exchange_status", "jabas_exchange_step_f32",
-    "jabas_exchange_cosine", "jabas_exchange_set_trace", "jabas_exchange_set_grid_limit",
+    "jabas_exchange_cosine", "jabas_exchange_set_trace", "jabas_exchange_set_grid_limit", "jabas_exchange_set_ctas_per_sm",
 )
 
-EXCHANGE_PIECE = 16384         # JABAS_EXCHANGE_PIECE
+EXCHANGE_PIECE = 8192          # JABAS_EXCHANGE_PIECE
 
 
 class Seg(ctypes.Structure):
@@ -109,6 +109,7 @@ def load() -> ctypes.CDLL:
                                             ctypes.POINTER(AdamHp), vp]
     lib.jabas_exchange_set_trace.argtypes = [vp, vp, u64]
     lib.jabas_exchange_set_grid_limit.argtypes = [vp, u32]
+    lib.jabas_exchange_set_ctas_per_sm.argtypes = [vp, i32]
     lib.jabas_exchange_cosine.argtypes = [pvp, pvp, pvp, i32, f64, vp]
     lib.jabas_layout_create.argtypes = [vp, ctypes.POINTER(Seg), i32, u64, pvp]
     lib.jabas_layout_destroy.argtypes = [vp]

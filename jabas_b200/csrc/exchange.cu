@@ -614,8 +614,10 @@ __device__ __forceinline__ void stage_args(ExArgs* dst, const ExArgs* src)
     __syncthreads();
 }
 
-template <int OPT>
-__global__ void __launch_bounds__(kExThreads, 2) exchange_kernel(const ExArgs arg)
+// MINB: resident CTAs per SM the kernel is compiled for (2: 96 KB ring, up to 128 registers;
+// 3: 64 KB ring, 64 registers).
+template <int OPT, int MINB>
+__global__ void __launch_bounds__(kExThreads, MINB) exchange_kernel(const ExArgs arg)
 {
     extern __shared__ __align__(128) unsigned char ring[];
     __shared__ ExShared S;
@@ -626,8 +628,8 @@ __global__ void __launch_bounds__(kExThreads, 2) exchange_kernel(const ExArgs ar
 // Several ranks' exchanges in ONE launch on ONE GPU (blockIdx.y = rank): kernels that wait on
 // one another may not run as separate launches on a GPU, so single-GPU tests of the protocol
 // use this form, with the grid sized so that every CTA is resident.
-template <int OPT>
-__global__ void __launch_bounds__(kExThreads, 2) exchange_emu_kernel(const ExArgs* ranks)
+template <int OPT, int MINB>
+__global__ void __launch_bounds__(kExThreads, MINB) exchange_emu_kernel(const ExArgs* ranks)
 {
     extern __shared__ __align__(128) unsigned char ring[];
     __shared__ ExShared S;
@@ -704,6 +706,7 @@ struct jabas_exchange {
     unsigned long long* trace = nullptr;
     unsigned long long trace_cap = 0;
     unsigned grid_limit = 0;             // 0: every resident CTA of the GPU
+    int ctas_per_sm = 0;                 // kernel variant: 2 (96 KB ring), 3 (64 KB ring), 0: by stream count
     jabas_ctx_t* ctx = nullptr;
     int nranks = 0, rank = 0;
     unsigned max_slots = 0, window = 0, piece = JABAS_EXCHANGE_PIECE;
@@ -785,6 +788,14 @@ int jabas_exchange_reset(jabas_exchange_t* ex)
     if (rc) return rc;
     JB_CUDA(cudaDeviceSynchronize());
     JB_CUDA(cudaMemset(ex->d_local, 0, ex->local_bytes));
+    return JABAS_OK;
+}
+
+int jabas_exchange_set_ctas_per_sm(jabas_exchange_t* ex, int ctas)
+{
+    if (!ex) return fail(JABAS_EINVAL, "exchange is null");
+    if (ctas != 0 && ctas != 2 && ctas != 3) return fail(JABAS_EINVAL, "exchange: 2 or 3 CTAs per SM (0: automatic)");
+    ex->ctas_per_sm = ctas;
     return JABAS_OK;
 }
 
@@ -921,12 +932,21 @@ int jabas_exchange_step_f32(jabas_exchange_t* const* exs, const jabas_exchange_b
     int rc = jb_ctx_bind(ex0->ctx);
     if (rc) return rc;
     if (n == 0) return JABAS_OK;
-    ExKernel kern = sgd ? exchange_kernel<OPT_SGD> : exchange_kernel<OPT_ADAM>;
-    ExEmuKernel emu = sgd ? exchange_emu_kernel<OPT_SGD> : exchange_emu_kernel<OPT_ADAM>;
     if (bufs[0].Kg > kExMaxSlots) return fail(JABAS_EINVAL, "exchange: at most 8 VSW gradients per launch");
     // ring: one 4 KB slot per stream of the widest phase, as many stages as fit the budget
     const int slots = std::max(std::max(bufs[0].Kg, ex0->nranks), sgd ? 3 : 4);
-    int stages = kRingBudgetBytes / (slots * (int)kTileBytes);
+    // Three resident CTAs per SM with a 64 KB ring each beat two with 96 KB wherever the ring still
+    // holds three stages (measured on 2 GPUs: ResNet-50 layout 0.342 -> 0.318 ms, ViT-B/16 1.484 ->
+    // 1.426 ms, GNMT 2.158 -> 2.114 ms): more, smaller items in flight shorten the tail and hide
+    // the per-item latencies better.  With more than five streams per stage two CTAs keep a deeper ring.
+    const bool three = ex0->ctas_per_sm == 3 || (ex0->ctas_per_sm == 0 && slots * 3 * (int)kTileBytes <= 64 * 1024);
+    const int ring_budget = three ? 64 * 1024 : kRingBudgetBytes;
+    ExKernel kern = three ? (sgd ? exchange_kernel<OPT_SGD, 3> : exchange_kernel<OPT_ADAM, 3>)
+                          : (sgd ? exchange_kernel<OPT_SGD, 2> : exchange_kernel<OPT_ADAM, 2>);
+    ExEmuKernel emu = three ? (sgd ? exchange_emu_kernel<OPT_SGD, 3> : exchange_emu_kernel<OPT_ADAM, 3>)
+                            : (sgd ? exchange_emu_kernel<OPT_SGD, 2> : exchange_emu_kernel<OPT_ADAM, 2>);
+    int stages = ring_budget / (slots * (int)kTileBytes);
+    if (stages < 2) return fail(JABAS_EINVAL, "exchange: the ring holds fewer than two stages for this many streams");
     if (stages > kExMaxStages) stages = kExMaxStages;
     const size_t dyn_smem = (size_t)stages * slots * kTileBytes;
     jabas_ctx_t* ctx = ex0->ctx;
@@ -939,11 +959,11 @@ int jabas_exchange_step_f32(jabas_exchange_t* const* exs, const jabas_exchange_b
         if (per_sm == 0) {
             // occupancy for the full ring budget: the grid does not depend on the launch's stream count
             cudaError_t e = nlocal == 1
-                ? cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBudgetBytes)
-                : cudaFuncSetAttribute(emu, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBudgetBytes);
+                ? cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_budget)
+                : cudaFuncSetAttribute(emu, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_budget);
             if (e == cudaSuccess)
-                e = nlocal == 1 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kExThreads, kRingBudgetBytes)
-                                : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, emu, kExThreads, kRingBudgetBytes);
+                e = nlocal == 1 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kExThreads, ring_budget)
+                                : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, emu, kExThreads, ring_budget);
             if (e != cudaSuccess) return fail(JABAS_ECUDA, cudaGetErrorString(e));
             if (per_sm < 1) per_sm = 1;
             if (per_sm > kMaxCtasPerSm) per_sm = kMaxCtasPerSm;

@@ -210,11 +210,14 @@ class GradientPath:
         self._bucket_grid_limit = int(os.environ.get("JABAS_EXCHANGE_BUCKET_CTAS", 0)) or \
             torch.cuda.get_device_properties(self.device).multi_processor_count
         self._grid_limit_set = 0
+        self._exchange_ctas = int(os.environ.get("JABAS_EXCHANGE_CTAS_PER_SM", 0))
         self.exchange = self.ops.Exchange(self.ctx, world, self.rank,
                                           [int(p) for p in self._px_h.buffer_ptrs],
                                           [int(p) for p in self._pg_h.buffer_ptrs],
                                           [int(p) for p in self._fl_h.buffer_ptrs], max_slots, int(self.exchange_window or 0),
                                           piece)
+        if self._exchange_ctas != 0:
+            self.exchange.set_ctas_per_sm(self._exchange_ctas)
 
     def _bucket_span(self, b: Optional[int]):
         """(first element, length) of a launch over bucket ``b`` (None: the whole flat buffer); a

@@ -339,6 +339,10 @@ class Exchange:
     def reset(self) -> None:
         _lib.check(self.ctx._lib.jabas_exchange_reset(self._h))
 
+    def set_ctas_per_sm(self, ctas: int) -> None:
+        """Kernel variant: 2 resident CTAs per SM (96 KB ring, default) or 3 (64 KB ring)."""
+        _lib.check(self.ctx._lib.jabas_exchange_set_ctas_per_sm(self._h, int(ctas)))
+
     def set_grid_limit(self, max_ctas: int) -> None:
         """Largest grid of the following launches (0: the whole GPU)."""
         _lib.check(self.ctx._lib.jabas_exchange_set_grid_limit(self._h, int(max_ctas)))
