@@ -292,8 +292,8 @@ JABAS_API int jabas_exchange_reset(jabas_exchange_t* ex);
 JABAS_API int jabas_exchange_status(jabas_exchange_t* ex, uint32_t* status, uint32_t* launches);
 
 /* Kernel variant of the following launches: 2 resident CTAs per SM with a 96 KB ring each, 3 with a
- * 64 KB ring and 64 registers per thread, or 0 (default): 3 where the ring still holds three stages
- * (at most five streams per stage: K and nranks up to 5), else 2. */
+ * 64 KB ring and 64 registers per thread, or 0 (default): 3 on two ranks with at most five streams per
+ * stage, else 2 (measured choices, see exchange.cu). */
 JABAS_API int jabas_exchange_set_ctas_per_sm(jabas_exchange_t* ex, int ctas);
 
 /* Largest grid of the following launches (0, the default: every CTA the GPU can hold).  A launch

@@ -935,11 +935,13 @@ int jabas_exchange_step_f32(jabas_exchange_t* const* exs, const jabas_exchange_b
     if (bufs[0].Kg > kExMaxSlots) return fail(JABAS_EINVAL, "exchange: at most 8 VSW gradients per launch");
     // ring: one 4 KB slot per stream of the widest phase, as many stages as fit the budget
     const int slots = std::max(std::max(bufs[0].Kg, ex0->nranks), sgd ? 3 : 4);
-    // Three resident CTAs per SM with a 64 KB ring each beat two with 96 KB wherever the ring still
-    // holds three stages (measured on 2 GPUs: ResNet-50 layout 0.342 -> 0.318 ms, ViT-B/16 1.484 ->
-    // 1.426 ms, GNMT 2.158 -> 2.114 ms): more, smaller items in flight shorten the tail and hide
-    // the per-item latencies better.  With more than five streams per stage two CTAs keep a deeper ring.
-    const bool three = ex0->ctas_per_sm == 3 || (ex0->ctas_per_sm == 0 && slots * 3 * (int)kTileBytes <= 64 * 1024);
+    // Three resident CTAs per SM with a 64 KB ring each beat two with 96 KB on two GPUs (measured:
+    // ResNet-50 layout 0.342 -> 0.318 ms, ViT-B/16 1.484 -> 1.426 ms, GNMT 2.158 -> 2.114 ms): more,
+    // smaller items in flight shorten the tail and hide the per-item latencies better.  From four
+    // GPUs on, where more of the traffic crosses NVLink, the deeper ring of the two-CTA form wins
+    // (2^27 elements, 4 GPUs: 1.400 vs 1.435 ms), and so it does with more than five streams per stage.
+    const bool three = ex0->ctas_per_sm == 3 ||
+                       (ex0->ctas_per_sm == 0 && ex0->nranks == 2 && slots * 3 * (int)kTileBytes <= 64 * 1024);
     const int ring_budget = three ? 64 * 1024 : kRingBudgetBytes;
     ExKernel kern = three ? (sgd ? exchange_kernel<OPT_SGD, 3> : exchange_kernel<OPT_ADAM, 3>)
                           : (sgd ? exchange_kernel<OPT_SGD, 2> : exchange_kernel<OPT_ADAM, 2>);
