@@ -405,6 +405,11 @@ def time_engine(D, eng, args, steps, warmup, min_total_ms, use_graph, overlap, p
     for _ in range(max(warmup, 3)):
         step_fn()
     D.barrier()
+    if getattr(eng, "exchange", None) is not None and not D.all_ok(eng.exchange.status()[0] == 0):
+        # a bounded wait already ran out during warm-up: nothing worth timing (the caller falls back)
+        return {"ms_per_step": float("nan"), "min": 0.0, "max": 0.0, "samples": 0, "spread": 0.0, "timed_ms_total": 0.0,
+                "single_step_ms": float("nan"), "split": {}, "launches_per_step": 0.0, "step_fn": step_fn,
+                "eager_fn": eager_fn}
     launches0 = eng.launches
     samples = []
     total_ms, reps = 0.0, 0
