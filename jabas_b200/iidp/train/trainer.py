@@ -264,7 +264,8 @@ class IIDPTrainer(object):
                 self.original_local_models.append(copied)
                 wrapper = IndependentIdenticalDataParallel(
                     copied, device_ids=[self.gpu], output_device=[self.gpu], model_index=idx,
-                    num_local_models=K_new, total_num_models=T, reducer=self.reducer)
+                    num_local_models=K_new, total_num_models=T, reducer=self.reducer,
+                    find_unused_parameters=self.main_model.find_unused_parameters)
                 wrapper.train(self.main_model.training)
                 self.local_models.append(wrapper)
                 self.local_optimizers.append(_ReplicaOptimizer(self.main_optimizer, self.reducer, idx))
@@ -360,6 +361,7 @@ class IIDPTrainer(object):
         loss = self.criterion(out, targets)
         self.losses[k] = loss
         loss.backward()
+        self.reducer.finish_backward(k, self.local_models[k].find_unused_parameters)
 
     def step(self) -> bool:
         if not self.is_sync_step():

@@ -315,6 +315,33 @@ class VSWReducer:
                 self._fire_ready_buckets()
         return hook
 
+    def finish_backward(self, k: int, find_unused: bool) -> None:
+        """End of VSW ``k``'s backward pass.  Parameters that took no part in the graph never fire
+        their hook; their gradient views are the zeros the iteration started with.  With
+        ``find_unused_parameters`` their buckets are completed here (a zero contribution, as in
+        DistributedDataParallel); without it an incomplete bucket is an error, as there."""
+        if not self.require_sync:
+            return
+        fire = False
+        with self._lock:
+            for b in range(self.layout.num_buckets):
+                need = len(self.layout.bucket_indices[b])
+                if self._param_count[k][b] >= need:
+                    continue
+                if not find_unused:
+                    raise RuntimeError(
+                        f"VSW {k}: {need - self._param_count[k][b]} parameters of bucket {b} received no gradient in "
+                        "this backward pass; pass find_unused_parameters=True if that is intended")
+                self._param_count[k][b] = need
+                if self.device.type == "cuda":
+                    ev = torch.cuda.Event()
+                    ev.record(torch.cuda.current_stream(self.device))
+                    self._events[b].append(ev)
+                self._vsw_done[b] += 1
+                fire = fire or self._vsw_done[b] == self.K
+        if fire:
+            self._fire_ready_buckets()
+
     def _fire_ready_buckets(self) -> None:
         """Fire comm hooks in bucket order (every rank must issue its collectives in the
         same order), for every bucket that is complete on all K VSWs."""
@@ -367,9 +394,6 @@ class IndependentIdenticalDataParallel(nn.Module):
                  sync_buffer_barrier=None, bucket_cap_mb: float = DEFAULT_BUCKET_CAP_MB,
                  reducer: Optional[VSWReducer] = None, process_group=None):
         super().__init__()
-        if find_unused_parameters:
-            raise NotImplementedError("find_unused_parameters=True is not supported: every "
-                                      "parameter must receive a gradient in every backward pass")
         if not gradient_as_bucket_view:
             raise ValueError("gradient_as_bucket_view must be True")      # jabas/train/trainer.py:82-86
         self.module = module

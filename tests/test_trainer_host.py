@@ -582,3 +582,56 @@ def test_config1_resnet50_two_gloo_ranks_five_iterations():
         assert c <= 1e-5, (rank, c)
         assert same                                           # both ranks: same weights, same cosines
         assert len(cosines) == 5 and all(-1.0 <= x <= 1.0 for x in cosines)
+
+
+class _Branchy(torch.nn.Module):
+    """A model with a head that the forward pass never uses."""
+
+    def __init__(self):
+        super().__init__()
+        self.body = torch.nn.Sequential(torch.nn.Linear(20, 32), torch.nn.ReLU(), torch.nn.Linear(32, 10))
+        self.unused = torch.nn.Linear(32, 7)
+
+    def forward(self, x):
+        return self.body(x)
+
+
+def test_find_unused_parameters():
+    """Parameters outside the graph: with the flag their buckets complete with zero gradients at
+    the end of each VSW's backward (weights stay, momentum stays zero, the rest matches the
+    reference path fed with zeros there); without it the incomplete bucket is an error."""
+    def make(flag):
+        torch.manual_seed(0)
+        tr = jabas_b200.JABASTrainer("cpu", 8, 2, 0, "overlap", dict(CFG))
+        tr._backend = oracle_backend
+        tr.prepare_stream_parallel(_Branchy(), torch.nn.CrossEntropyLoss(), bucket_cap_mb=0.002, first_bucket_bytes=512,
+                                   find_unused_parameters=flag)
+        tr.prepare_weight_sync_method(ShardSGD(tr.main_model.parameters(), lr=0.1, momentum=0.9))
+        return tr
+    x, y = torch.randn(16, 20), torch.randint(0, 10, (16,))
+    tr = make(False)
+    with pytest.raises(RuntimeError, match="find_unused_parameters"):
+        tr.compute((x, y))
+    tr = make(True)
+    lay, eng = tr.reducer.layout, tr.reducer.engine
+    ref = ReferencePath(lay, 2, dict(kind="sgd", groups=[dict(lr=0.1, weight_decay=0.0)], momentum=0.9),
+                        total_num_decoupled_workers=2, arith="c")
+    for k in range(2):
+        ref.weights[k].copy_(eng.weights[k])
+    w_unused = tr.main_model.module.unused.weight.detach().clone()
+    for it in range(2):
+        xs, ys = torch.chunk(x, 2), torch.chunk(y, 2)
+        for k in range(2):                                   # per-VSW gradients by plain autograd
+            m = copy.deepcopy(tr.local_models[k].module)
+            m.zero_grad()
+            torch.nn.functional.cross_entropy(m(xs[k]), ys[k]).backward()
+            flat = torch.zeros(lay.total)
+            for p, slot in zip(m.parameters(), lay.slots):
+                if p.grad is not None:
+                    flat[slot.offset:slot.offset + slot.numel] = p.grad.reshape(-1)
+            ref.grads[k].copy_(flat)
+        ref.run_iteration()
+        tr.compute((x, y))
+        assert tr.step() is True
+        assert torch.equal(eng.weights[1], ref.weights[0])
+    assert torch.equal(tr.main_model.module.unused.weight, w_unused)
