@@ -77,6 +77,8 @@ def parse_args():
                     help="launch every kernel / collective from Python instead of replaying one CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--train-graph", action="store_true",
+                    help="on several GPUs too, time the training iteration as one CUDA-graph launch (one GPU: always)")
     ap.add_argument("--no-train-iter", action="store_true",
                     help="skip the supplementary whole-training-iteration measurement (resnet50 workload only)")
     ap.add_argument("--no-configs", action="store_true",
@@ -634,7 +636,7 @@ def run_ours(args):
 
     train_iter = None
     if args.workload == "resnet50" and not args.no_train_iter:
-        train_iter = measure_training_iteration(D, K, lbs, collective)
+        train_iter = measure_training_iteration(D, K, lbs, collective, graph=args.train_graph)
 
     if rank != 0:
         finish(D)
@@ -789,12 +791,23 @@ def run_extra_config(D, args, name, vsw, okind, collective):
         return {"error": f"{type(e).__name__}: {e}"[:300]}
 
 
-def measure_training_iteration(D, K, lbs, collective, iters=8):
+def measure_training_iteration(D, K, lbs, collective, iters=8, graph=False):
     """Supplementary: WHOLE training iterations through the trainer mirror — K VSWs' forward and
     backward of torchvision ResNet-50 (stock PyTorch / cuDNN kernels, fp32 with TF32 convolutions) on K
     streams, comm hooks fired per bucket from backward, this library's path overlapping the rest of
-    backward — on synthetic N(0,1) images.  Reports samples/sec over all ranks and the EXPOSED time
-    of the gradient path: iteration time minus the time of forward + backward alone."""
+    backward — on synthetic N(0,1) images.  Reports samples/sec over all ranks, the EXPOSED time
+    of the gradient path (iteration time minus the time of forward + backward alone) and, on one
+    GPU, the same iteration as one CUDA-graph launch, at the benchmark's local batch size and at
+    the launch-bound local batch size 8 of the reference's CPU-runnable configuration."""
+    out = _training_case(D, K, lbs, collective, iters, graph=(D.world == 1 or graph))
+    if D.world == 1 and "error" not in out:
+        small = _training_case(D, K, 8, collective, iters, graph=True)
+        out["local_batch_8"] = {k: small[k] for k in ("ms_per_iteration", "samples_per_sec", "graph", "error")
+                                if k in small}
+    return out
+
+
+def _training_case(D, K, lbs, collective, iters, graph):
     torch = D.torch
     ok, err, tr = True, None, None
     try:                                               # local part: no collective may sit in here
@@ -853,11 +866,28 @@ def measure_training_iteration(D, K, lbs, collective, iters=8):
         tr.accum_step = real_accum
         tr.reducer.engine.zero_grads()
         out = {"ms_per_iteration": ms, "samples_per_sec": D.world * K * lbs / (ms / 1e3), "iterations": iters,
+               "local_batch_size": lbs,
                "forward_backward_alone_ms": ms_fb, "gradient_path_exposed_ms": ms - ms_fb,
                "weight_sync_method": "overlap (per-bucket launches during backward)",
                "collective": ("peer-memory pipelined exchange" if collective == "peer" else "NCCL") if D.world > 1 else "none",
                "model": "torchvision resnet50, fp32 (TF32 convolutions), forward+backward by stock PyTorch kernels",
                "cosine": cos}
+        if graph:
+            try:                                       # the same iteration as ONE CUDA-graph launch
+                launches = tr.reducer.engine.launches
+                tr.enable_iteration_graph(warmup=2)
+                for _ in range(4):                     # two eager, capture + first replay, one more replay
+                    full()
+                ms_g = timed(full, iters)
+                out["graph"] = {"ms_per_iteration": ms_g, "samples_per_sec": D.world * K * lbs / (ms_g / 1e3),
+                                "launches_per_replay": tr._iter_graph["launches"].get(True),
+                                "cosine": float(tr.cos_placeholder),
+                                "what": "compute() + step() replayed as one CUDA graph: K forward/backward passes on K "
+                                        "streams, the hooks' launches, update, statistic, zeroed gradients"}
+                assert tr.reducer.engine.launches > launches
+            except Exception as e:
+                out["graph"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+        tr.disable_iteration_graph()
         tr.reducer.engine.close()
         del tr, model, x, y
         gc.collect()

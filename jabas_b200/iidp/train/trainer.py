@@ -79,6 +79,7 @@ class IIDPTrainer(object):
         #: issue the K forward/backward passes from K Python threads (as the reference does,
         #: jabas/train/trainer.py:584-588) instead of one after the other from the calling thread
         self.threaded_compute = False
+        self._iter_graph = None         # whole-iteration CUDA graphs, see enable_iteration_graph
 
     # -- helpers -----------------------------------------------------------------------
     def trainer_print(self, message, status="info"):
@@ -255,6 +256,7 @@ class IIDPTrainer(object):
         assert K_new == K_old + adjust_num_models_diff
         if self._cuda:
             torch.cuda.current_stream(self.device).synchronize()
+        self._drop_iteration_graphs()            # captured for the old set of VSWs
         T = self.total_num_decoupled_workers
         self.reducer.resize(K_new, T)
         if adjust_num_models_diff > 0:
@@ -307,8 +309,99 @@ class IIDPTrainer(object):
 
     def compute(self, data):
         inputs, targets = data[0], data[1]
+        if self._iter_graph is not None:
+            return self._graphed_compute(inputs, targets)
         K = self.num_models
         self.parallel_compute(torch.chunk(inputs, K), torch.chunk(targets, K))
+
+    # -- one CUDA-graph launch per iteration ---------------------------------------------
+    def enable_iteration_graph(self, warmup: int = 3) -> None:
+        """From now on a synchronising iteration (``compute`` then ``step``) is ONE CUDA-graph
+        launch: the K VSWs' forward and backward passes on their K streams, every launch the comm
+        hooks make from backward (aggregation, exchange or collectives, fused update, statistic)
+        and the zeroing of the gradients.  ``compute`` copies the batch into static input
+        buffers and replays the graph; ``step`` keeps the host-side bookkeeping.  What changes
+        between iterations (lr, weight decay, Adam step, first-step flag) is read by the kernels
+        from a device block refreshed before each replay.
+
+        The first ``warmup`` iterations of each kind (with and without the statistic) run eagerly
+        on the capture stream (they bring up cuDNN / cuBLAS work spaces, the per-stream reduction
+        work spaces and the communicators); that kind's graph is captured at its next iteration.  Needs
+        ``accum_step == 0``, a fixed batch shape and the single-threaded issue order; a change of
+        the VSW count drops the graphs, which are then captured again."""
+        if not self._cuda:
+            raise RuntimeError("iteration graphs need a CUDA device")
+        if self.binding is None:
+            raise RuntimeError("prepare_weight_sync_method() must be called first")
+        eng = self.reducer.engine
+        if eng._dyn is None:
+            eng._dyn = eng.ops.DynHp(eng.ctx)
+        self._iter_graph = dict(warmup=max(1, int(warmup)), seen={}, stream=torch.cuda.Stream(self.device),
+                                graphs={}, launches={}, losses={}, static=None, pool=None, replayed=False)
+
+    def disable_iteration_graph(self) -> None:
+        if self._iter_graph is not None and self._cuda:
+            torch.cuda.current_stream(self.device).synchronize()
+        self._iter_graph = None
+
+    def _drop_iteration_graphs(self) -> None:
+        G = self._iter_graph
+        if G is not None:
+            torch.cuda.synchronize(self.device)
+            G.update(graphs={}, launches={}, losses={}, static=None, pool=None, seen={}, replayed=False)
+
+    def _graphed_compute(self, inputs, targets):
+        G, K, eng = self._iter_graph, self.num_models, self.reducer.engine
+        if self.accum_step != 0 or self.threaded_compute:
+            raise RuntimeError("iteration graphs need accum_step == 0 and threaded_compute == False")
+        if G["static"] is None:
+            G["static"] = (torch.empty(inputs.shape, dtype=inputs.dtype, device=self.device),
+                           torch.empty(targets.shape, dtype=targets.dtype, device=self.device))
+        xin, tin = G["static"]
+        if inputs.shape != xin.shape or targets.shape != tin.shape:
+            raise ValueError(f"the iteration graph takes batches of shape {tuple(xin.shape)} / {tuple(tin.shape)}, "
+                             f"got {tuple(inputs.shape)} / {tuple(targets.shape)}")
+        sim = bool(self._is_similarity_step())
+        cur, s = torch.cuda.current_stream(self.device), G["stream"]
+        s.wait_stream(cur)
+        with torch.cuda.stream(s):
+            xin.copy_(inputs, non_blocking=True)
+            tin.copy_(targets, non_blocking=True)
+            self.binding.sync_hyperparams()
+            if G["seen"].get(sim, 0) < G["warmup"]:    # each kind of iteration warms up before its capture
+                G["seen"][sim] = G["seen"].get(sim, 0) + 1
+                eng.push_hyperparams()
+                self.parallel_compute(torch.chunk(xin, K), torch.chunk(tin, K))
+                cur.wait_stream(s)
+                return
+            if sim not in G["graphs"]:
+                self._capture_iteration(sim)
+            self.local_accum_step += 1
+            eng.push_hyperparams()
+            G["graphs"][sim].replay()
+        cur.wait_stream(s)
+        eng._sim_step = sim and eng.similarity
+        eng.launches += G["launches"][sim]
+        self.losses = dict(G["losses"][sim])
+        G["replayed"] = True
+
+    def _capture_iteration(self, sim: bool) -> None:
+        """Capture ``parallel_compute`` + the device part of ``step`` on the capture stream (the
+        caller has made it current).  Nothing runs and no host counter moves: the replay that
+        follows is the iteration."""
+        G, K, eng = self._iter_graph, self.num_models, self.reducer.engine
+        xin, tin = G["static"]
+        graph = torch.cuda.CUDAGraph()
+        keep = (self.local_accum_step, eng.launches)
+        with torch.cuda.graph(graph, pool=G["pool"], stream=G["stream"]):
+            self.parallel_compute(torch.chunk(xin, K), torch.chunk(tin, K))
+            self._step_device()
+        if G["pool"] is None:
+            G["pool"] = graph.pool()
+        G["graphs"][sim] = graph
+        G["launches"][sim] = eng.launches - keep[1]
+        G["losses"][sim] = dict(self.losses)
+        self.local_accum_step, eng.launches = keep
 
     def parallel_compute(self, scatter_inputs, scatter_targets, accum_step=0):
         """Forward + backward of the K VSWs, each on its own stream.  On the synchronising
@@ -366,7 +459,25 @@ class IIDPTrainer(object):
     def step(self) -> bool:
         if not self.is_sync_step():
             return False
-        eng = self.reducer.engine
+        G = self._iter_graph
+        if G is not None and G["replayed"]:
+            G["replayed"] = False                # the graph launched by compute() held the device part
+        elif G is not None:
+            cur, s = torch.cuda.current_stream(self.device), G["stream"]
+            s.wait_stream(cur)
+            with torch.cuda.stream(s):           # warm-up iterations run where the capture will
+                self._step_device()
+            cur.wait_stream(s)
+        else:
+            self._step_device()
+        self.binding.finish_step()
+        self.local_accum_step = -1
+        self.sync_step += 1
+        return True
+
+    def _step_device(self) -> None:
+        """Everything of ``step`` that is work on the GPU: join the K streams, wait for the hook
+        chains, the whole-model update of the sequential mode, the statistic, zeroed gradients."""
         if self._cuda:
             cur = torch.cuda.current_stream(self.device)
             for s in self.model_streams:
@@ -375,12 +486,8 @@ class IIDPTrainer(object):
         if self.weight_sync_method == "sequential":
             with self.reducer.stream_scope():
                 self.binding.step(None)          # one fused launch over the whole flat model
-        self.binding.finish_step()
         self._after_update()
-        eng.zero_grads()
-        self.local_accum_step = -1
-        self.sync_step += 1
-        return True
+        self.reducer.engine.zero_grads()
 
     def _after_update(self):
         """Hook for subclasses: runs after the update is enqueued, before gradients are zeroed."""

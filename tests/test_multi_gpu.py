@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _rank_main(rank, world, port, mode, kind, wsm, q, collective="nccl"):
+def _rank_main(rank, world, port, mode, kind, wsm, q, collective="nccl", graph=False):
     try:
         sys.path.insert(0, HERE)
         sys.path.insert(0, os.path.dirname(HERE))
@@ -44,15 +44,24 @@ def _rank_main(rank, world, port, mode, kind, wsm, q, collective="nccl"):
         lay = tr.reducer.layout
         g = torch.Generator().manual_seed(50 + rank)
         worst_w = worst_c = 0.0
-        for it in range(3):
+        static_copies = None
+        for it in range(9 if graph else 3):
+            if graph and it == 3:
+                # from here on compute() + step() are ONE graph launch per iteration (collectives or
+                # exchange kernels included); two more eager iterations on the capture stream first
+                tr.enable_iteration_graph(warmup=2)
             x = torch.randn(8 * K, 3, 16, 16, generator=g).cuda()
             y = torch.randint(0, 10, (8 * K,), generator=g).cuda()
             tr.compute((x, y))
+            replayed = graph and it >= 3 and tr._iter_graph["replayed"]
             tr.step()
             torch.cuda.synchronize()
-            for (k, b), t in captured.items():
+            if replayed and static_copies is None:
+                static_copies = dict(captured)      # clones made during capture: every replay refills them
+            for (k, b), t in (static_copies if replayed else captured).items():
                 ref.grads[k][lay.buckets[b][0]:lay.buckets[b][1]].copy_(t.cpu())
-            captured.clear()
+            if not replayed:
+                captured.clear()
             cos_ref = ref.run_iteration()
             wr = ref.weights[0]
             w = tr.reducer.engine.weights[K - 1].cpu()
@@ -68,6 +77,9 @@ def _rank_main(rank, world, port, mode, kind, wsm, q, collective="nccl"):
                                       for fs in tr.reducer.buffers_flat])
         if len({tuple(s) for s in sums}) != 1 or len(set(sums[0])) != 1:
             worst_w = float("inf")
+        if graph and not tr._iter_graph["graphs"]:
+            worst_w = float("inf")
+        tr.disable_iteration_graph()
         q.put((rank, worst_w, worst_c, tr.reducer.engine.launches))
         dist.barrier()
         torch.cuda.synchronize()
@@ -78,19 +90,21 @@ def _rank_main(rank, world, port, mode, kind, wsm, q, collective="nccl"):
         q.put((rank, "error", traceback.format_exc(), 0))
 
 
-@pytest.mark.parametrize("mode,kind,wsm,collective", [
-    ("fused", "sgd", "overlap", "nccl"), ("pair_exchange", "sgd", "sequential", "nccl"),
-    ("fused", "adamw", "overlap", "nccl"), ("fused", "adamw", "sequential", "nccl"),
-    ("fused", "sgd", "sequential", "peer"), ("fused", "adamw", "sequential", "peer"),
-    ("fused", "sgd", "overlap", "peer"), ("fused", "adamw", "overlap", "peer")])
-def test_two_nccl_ranks_match_reference_path(mode, kind, wsm, collective):
+@pytest.mark.parametrize("mode,kind,wsm,collective,graph", [
+    ("fused", "sgd", "overlap", "nccl", False), ("pair_exchange", "sgd", "sequential", "nccl", False),
+    ("fused", "adamw", "overlap", "nccl", False), ("fused", "adamw", "sequential", "nccl", False),
+    ("fused", "sgd", "sequential", "peer", False), ("fused", "adamw", "sequential", "peer", False),
+    ("fused", "sgd", "overlap", "peer", False), ("fused", "adamw", "overlap", "peer", False),
+    ("fused", "sgd", "overlap", "peer", True), ("fused", "adamw", "overlap", "nccl", True)])
+def test_two_nccl_ranks_match_reference_path(mode, kind, wsm, collective, graph):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + (os.getpid() + hash((mode, kind, wsm, collective))) % 400
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, mode, kind, wsm, q, collective)) for r in range(2)]
+    port = 29500 + (os.getpid() + hash((mode, kind, wsm, collective, graph))) % 400
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, mode, kind, wsm, q, collective, graph))
+             for r in range(2)]
     for p in procs:
         p.start()
     res = [q.get(timeout=300) for _ in procs]

@@ -401,3 +401,83 @@ def test_resnet50_two_vsws_five_iterations():
         for k in range(K):
             assert torch.equal(tr.reducer.engine.weights[k].cpu(), ref.weights[0]), (it, k)
         assert torch.isfinite(tr.losses[0]).item()
+
+
+@pytest.mark.parametrize("wsm,kind,K,interval,lr_step", [
+    ("overlap", "sgd", 2, 1, False), ("sequential", "adamw", 4, 1, True), ("overlap", "adamw", 2, 2, True),
+    ("sequential", "sgd", 4, 3, False)])
+def test_iteration_graph_matches_reference_path(wsm, kind, K, interval, lr_step):
+    """compute() + step() as ONE CUDA-graph launch per iteration (K forward/backward passes on K
+    streams, the hooks' launches, the update, the statistic, zeroed gradients): the weights after
+    every replay are bit-equal to the reference path fed with the gradients of that replay; the
+    lr may change between replays (device-resident hyper-parameters), and iterations with and
+    without the statistic replay their own graphs."""
+    import jabas_b200
+    from jabas_b200.iidp.optim import ShardAdamW, ShardSGD
+    from oracle.reference_path import ReferencePath
+    tr = jabas_b200.JABASTrainer(0, 8, K, 0, wsm, dict(CFG, batch_size_adjust_interval=interval))
+    tr.prepare_stream_parallel(_model(), torch.nn.CrossEntropyLoss().cuda(), bucket_cap_mb=0.05,
+                               first_bucket_bytes=4096)
+    groups = _groups(tr.main_model)
+    if kind == "sgd":
+        opt = (ShardSGD if wsm == "overlap" else torch.optim.SGD)(groups, lr=0.1, momentum=0.9)
+    else:
+        opt = (ShardAdamW if wsm == "overlap" else torch.optim.AdamW)(groups, lr=1e-2)
+    tr.prepare_weight_sync_method(opt, None, _groups)
+    tr.set_model_train()
+    od = _opt_dict(kind)
+    ref = ReferencePath(tr.reducer.layout, K, od, total_num_decoupled_workers=K, arith="c")
+    for k in range(K):
+        ref.weights[k].copy_(tr.reducer.engine.weights[k].cpu())
+    captured = _capture_vsw_gradients(tr)
+    lay = tr.reducer.layout
+    tr.enable_iteration_graph(warmup=2)
+    G = tr._iter_graph
+    g = torch.Generator().manual_seed(3)
+    static_copies = {}            # per graph: the clones made while capturing, refilled by every replay
+    replays = 0
+    for it in range(9):
+        x = torch.randn(8 * K, 3, 16, 16, generator=g).cuda()
+        y = torch.randint(0, 10, (8 * K,), generator=g).cuda()
+        if lr_step and it in (4, 7):
+            for gr, go in zip(opt.param_groups, od["groups"]):
+                gr["lr"] *= 0.5
+                go["lr"] *= 0.5
+        sim = tr._is_similarity_step()
+        ngraphs, launches = len(G["graphs"]), tr.reducer.engine.launches
+        tr.compute((x, y))
+        replayed = G["replayed"]
+        assert tr.step() is True
+        torch.cuda.synchronize()
+        assert tr.reducer.engine.launches > launches
+        if len(G["graphs"]) > ngraphs:
+            static_copies[sim] = dict(captured)
+        src = static_copies[sim] if replayed else captured
+        replays += bool(replayed)
+        assert len(src) == K * lay.num_buckets
+        for (k, b), t in src.items():
+            ref.grads[k][lay.buckets[b][0]:lay.buckets[b][1]].copy_(t.cpu())
+        cos_ref = ref.run_iteration(similarity_step=sim)
+        if sim:
+            assert abs(float(tr.cos_placeholder) - cos_ref) < 1e-5, it
+        for k in range(K):
+            assert torch.equal(tr.reducer.engine.weights[k].cpu(), ref.weights[0]), (it, k, replayed)
+        assert all(float(tr.reducer.engine.grads[k].abs().max()) == 0.0 for k in range(K))
+        assert torch.isfinite(torch.stack([tr.losses[k].detach() for k in range(K)])).all()
+    assert len(G["graphs"]) == (1 if interval == 1 else 2)
+    assert replays == {1: 7, 2: 5, 3: 5}[interval]        # two eager iterations of each kind come first
+    with pytest.raises(ValueError, match="shape"):
+        tr.compute((torch.randn(4 * K, 3, 16, 16).cuda(), torch.zeros(4 * K, dtype=torch.long).cuda()))
+    # a change of the VSW count drops the graphs; they are captured again for the new set
+    tr.change_num_models(K + 2)
+    assert not G["graphs"] and not G["seen"]
+    x = torch.randn(8 * (K + 2), 3, 16, 16, generator=g).cuda()
+    y = torch.randint(0, 10, (8 * (K + 2),), generator=g).cuda()
+    for it in range(8):
+        tr.compute((x, y))
+        tr.step()
+    torch.cuda.synchronize()
+    assert len(G["graphs"]) >= 1
+    for k in range(1, K + 2):
+        assert torch.equal(tr.reducer.engine.weights[k], tr.reducer.engine.weights[0])
+    tr.reducer.engine.close()
