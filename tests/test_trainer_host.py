@@ -635,3 +635,11 @@ def test_find_unused_parameters():
         assert tr.step() is True
         assert torch.equal(eng.weights[1], ref.weights[0])
     assert torch.equal(tr.main_model.module.unused.weight, w_unused)
+
+
+def test_iteration_graph_needs_a_cuda_device():
+    """The whole-iteration CUDA graph is a device feature: on the CPU double it refuses."""
+    tr = _make_trainer(2, "overlap", "sgd")
+    with pytest.raises(RuntimeError, match="CUDA"):
+        tr.enable_iteration_graph()
+    assert tr._iter_graph is None
