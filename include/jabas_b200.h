@@ -263,7 +263,8 @@ typedef struct {
     uint32_t max_slots;
     uint32_t window_pieces;         /* pieces per pipeline step; 0: sized from the launch grid */
     uint32_t piece_elems;           /* 0: JABAS_EXCHANGE_PIECE; else a multiple of 1024 */
-    uint32_t reserved;
+    uint32_t update_lag;            /* pipeline steps between a piece's reduce item and its update items:
+                                     * 1 or 2; 0: default.  Same value on every rank. */
 } jabas_exchange_desc_t;
 
 /* Per-rank buffers of a launch.  grads: Kg VSW gradient buffers; w: K weight replicas (w[0] is the

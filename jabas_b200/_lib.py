@@ -60,7 +60,7 @@ class ExchangeDesc(ctypes.Structure):
                 ("px", ctypes.POINTER(ctypes.c_void_p)), ("pg", ctypes.POINTER(ctypes.c_void_p)),
                 ("flags", ctypes.POINTER(ctypes.c_void_p)), ("max_slots", ctypes.c_uint32),
                 ("window_pieces", ctypes.c_uint32), ("piece_elems", ctypes.c_uint32),
-                ("reserved", ctypes.c_uint32)]
+                ("update_lag", ctypes.c_uint32)]
 
 
 class ExchangeBufs(ctypes.Structure):

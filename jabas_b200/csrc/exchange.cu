@@ -11,8 +11,8 @@
 // The flat range is cut into pieces of `piece` elements, dealt to the ranks in turn (piece P is
 // reduced by rank P mod n).  A piece of one phase is one work item.  Items stand in a queue
 // ordered by pipeline step s = 0, 1, ...: with windows of W pieces, step s holds the aggregate
-// items of window s, this rank's reduce items of window s-1 and the update items of window s-2,
-// interleaved (one reduce item, then aggregate and update items in turn), so that at any moment
+// items of window s, this rank's reduce items of window s-1 and the update items of window s-3
+// (s-2 with update_lag 1), interleaved (one reduce item, then aggregate and update items in turn), so that at any moment
 // the resident CTAs work on NVLink-bound and HBM-bound items together and the two resources
 // overlap (the aggregate items run one window further ahead than this sketch says, see
 // producer_loop).  CTAs draw items with an atomic ticket, in queue order.
@@ -20,11 +20,14 @@
 // Dependencies are per-piece flags, not collectives: an aggregate item stores the launch's epoch
 // into the flag block of the piece's owner; the owner's reduce item waits for the n flags of its
 // piece and then stores the epoch into every rank's flag block; an update item waits for that
-// flag.  An item only ever waits for items of the previous pipeline step, and tickets are drawn
+// flag.  An item only ever waits for items of earlier pipeline steps, and tickets are drawn
 // in order, so every item a wait depends on is already held by a running CTA on its GPU: no
-// deadlock, whatever the number of resident CTAs; and a consumer's producer was drawn a whole
-// step (W-odd items) earlier, so waits are short as long as a step holds more items than there
-// are CTAs.  Every wait is bounded by wall time; a wait that
+// deadlock, whatever the number of resident CTAs.  A reduce item's inputs were drawn two steps
+// earlier, an update item's reduce item two steps earlier as well (measured on 4 GPUs: a reduce
+// item takes about 40 us from its draw to the moment its flag is visible on the other GPUs — wait,
+// issue, drain, 20-30 us of system-scope release under full HBM load —, more than one step of a
+// ResNet-50-sized launch; with one step of distance the update items waited 6 us on average and
+// 25-33 us at the 95th percentile, with two 3 us and 17-20 us).  Every wait is bounded by wall time; a wait that
 // runs out records (phase, slot) in a status word, all CTAs of the launch drain, and the host
 // reads the status — the kernel never traps and never spins for ever.
 //
@@ -60,6 +63,7 @@ struct ExArgs {
     unsigned long long npieces;         // pieces of the launch
     unsigned int piece, window, nsteps, slot_base, max_slots;   // piece: elements of an item; window: pieces per step
     unsigned int total_tickets;         // length of the queue
+    unsigned int upd_lag;               // steps an update item stands behind its reduce item (1 or 2)
     int nseg, K, Kw, nranks, rank;
     int opt;                            // OPT_SGD / OPT_ADAM
     int ring_stages, ring_slots;        // shared-memory ring: stages, and 4 KB stream slots per stage
@@ -215,7 +219,7 @@ __device__ __noinline__ void producer_loop(ExShared& S, unsigned char* ring, uns
     const unsigned group_items = 2u * (unsigned)n + 1u;
     // The queue opens with the aggregate items of window 0 alone; after that, step s holds the
     // aggregate items of window s+1, the reduce items of window s-1 and the update items of window
-    // s-2.  Aggregation has no dependencies, so it runs a window further ahead than the pipeline
+    // s-ulag.  Aggregation has no dependencies, so it runs a window further ahead than the pipeline
     // needs: a reduce item's flags take about 30 us from the draw of the matching aggregate item
     // (issue, drain of the stores behind the system-scope release, NVLink), and without the lead
     // the reduce items of the first window would be drawn before that.
@@ -224,9 +228,10 @@ __device__ __noinline__ void producer_loop(ExShared& S, unsigned char* ring, uns
     const unsigned prologue = a.npieces < a.window ? (unsigned)a.npieces : a.window;
     const unsigned groups = a.window / (unsigned)n;
     const unsigned nsteps = a.nsteps;
+    const unsigned ulag = 1u + a.upd_lag;          // update items of window w stand in step w + ulag
     auto has_r = [&](unsigned st) { return st >= 1u && st <= nsteps; };
     auto has_a = [&](unsigned st) { return st + 1u < nsteps; };
-    auto has_u = [&](unsigned st) { return st >= 2u && st <= nsteps + 1u; };
+    auto has_u = [&](unsigned st) { return st >= ulag && st < nsteps + ulag; };
     auto group_len = [&](unsigned st) {
         return (has_r(st) ? 1u : 0u) + (has_a(st) ? (unsigned)n : 0u) + (has_u(st) ? (unsigned)n : 0u);
     };
@@ -249,17 +254,17 @@ __device__ __noinline__ void producer_loop(ExShared& S, unsigned char* ring, uns
         else {
             unsigned tq = t - prologue, step = 0;
             bool found = false;
-            for (; step < 2u; ++step) {                        // the first two steps are short
+            for (; step < ulag; ++step) {                      // the first steps are short
                 const unsigned len = groups * group_len(step);
                 if (tq < len) { found = true; break; }
                 tq -= len;
             }
-            if (!found && nsteps >= 4u) {                      // steps 2 .. nsteps-2 hold all three phases
-                const unsigned len = groups * group_items, nfull = nsteps - 3u;
-                if (tq < nfull * len) { step = 2u + tq / len; tq %= len; found = true; }
+            if (!found && nsteps >= ulag + 2u) {               // steps ulag .. nsteps-2 hold all three phases
+                const unsigned len = groups * group_items, nfull = nsteps - 1u - ulag;
+                if (tq < nfull * len) { step = ulag + tq / len; tq %= len; found = true; }
                 else { tq -= nfull * len; step = nsteps - 1u; }
             }
-            for (; !found && step < nsteps + 2u; ++step) {     // the last steps are short again
+            for (; !found && step < nsteps + ulag; ++step) {   // the last steps are short again
                 const unsigned len = groups * group_len(step);
                 if (tq < len) { found = true; break; }
                 tq -= len;
@@ -272,10 +277,10 @@ __device__ __noinline__ void producer_loop(ExShared& S, unsigned char* ring, uns
                 if (has_r(step)) --i;
                 if (has_a(step) && has_u(step)) {
                     idx = grp * (unsigned)n + (i >> 1);
-                    if (i & 1u) { phase = PH_UPD; win = (long long)step - 2; } else { phase = PH_AGG; win = (long long)step + 1; }
+                    if (i & 1u) { phase = PH_UPD; win = (long long)step - (long long)ulag; } else { phase = PH_AGG; win = (long long)step + 1; }
                 } else {
                     idx = grp * (unsigned)n + i;
-                    if (has_a(step)) { phase = PH_AGG; win = (long long)step + 1; } else { phase = PH_UPD; win = (long long)step - 2; }
+                    if (has_a(step)) { phase = PH_AGG; win = (long long)step + 1; } else { phase = PH_UPD; win = (long long)step - (long long)ulag; }
                 }
             }
         }
@@ -710,6 +715,7 @@ struct jabas_exchange {
     jabas_ctx_t* ctx = nullptr;
     int nranks = 0, rank = 0;
     unsigned max_slots = 0, window = 0, piece = JABAS_EXCHANGE_PIECE;
+    unsigned upd_lag = 2;                // steps between a piece's reduce item and its update items
     const float* px[kExMaxRanks] = {};
     const float* pg[kExMaxRanks] = {};
     unsigned int* flags[kExMaxRanks] = {};
@@ -743,10 +749,12 @@ int jabas_exchange_create(jabas_ctx_t* ctx, const jabas_exchange_desc_t* d, jaba
     if (d->piece_elems && (d->piece_elems % 1024u || d->piece_elems > (1u << 22)))
         return fail(JABAS_EINVAL, "exchange: piece_elems must be a multiple of 1024, at most 2^22 (0: default)");
     if (!d->px || !d->pg || !d->flags) return fail(JABAS_EINVAL, "exchange: null buffer table");
+    if (d->update_lag > 2u) return fail(JABAS_EINVAL, "exchange: update_lag is 0 (default), 1 or 2");
     jabas_exchange_t* ex = new (std::nothrow) jabas_exchange_t();
     if (!ex) return fail(JABAS_ENOMEM, "out of host memory");
     ex->ctx = ctx; ex->nranks = d->nranks; ex->rank = d->rank; ex->max_slots = d->max_slots;
     ex->window = d->window_pieces;
+    ex->upd_lag = d->update_lag ? d->update_lag : 2u;
     ex->piece = d->piece_elems ? d->piece_elems : JABAS_EXCHANGE_PIECE;
     for (int r = 0; r < d->nranks; ++r) {
         if (!d->px[r] || !d->pg[r] || !d->flags[r] || !aligned16(d->px[r]) || !aligned16(d->pg[r]) ||
@@ -873,7 +881,8 @@ static int fill_args(jabas_exchange_t* ex, unsigned grid_ctas, const jabas_excha
     window = window / ex->nranks * ex->nranks;
     if (window < (unsigned long long)ex->nranks) window = ex->nranks;
     const unsigned long long nsteps = (a.npieces + window - 1) / window;
-    if (window + (nsteps + 2) * (window / ex->nranks) * (2ull * ex->nranks + 1) >= 0x7ffffff0ull)
+    const unsigned long long ulag = 1ull + ex->upd_lag;
+    if (window + (nsteps + ulag) * (window / ex->nranks) * (2ull * ex->nranks + 1) >= 0x7ffffff0ull)
         return fail(JABAS_EINVAL, "exchange: too many work items for one launch");
     a.window = (unsigned)window; a.nsteps = (unsigned)nsteps; a.slot_base = slot_base; a.max_slots = ex->max_slots;
     {
@@ -881,12 +890,13 @@ static int fill_args(jabas_exchange_t* ex, unsigned grid_ctas, const jabas_excha
         // have a window (see producer_loop)
         unsigned long long tickets = a.npieces < window ? a.npieces : window;
         const unsigned long long groups = window / ex->nranks;
-        for (unsigned long long st = 0; st < nsteps + 2; ++st) {
+        for (unsigned long long st = 0; st < nsteps + ulag; ++st) {
             const unsigned long long len = ((st >= 1 && st <= nsteps) ? 1 : 0) + ((st + 1 < nsteps) ? ex->nranks : 0) +
-                                           ((st >= 2 && st <= nsteps + 1) ? ex->nranks : 0);
+                                           ((st >= ulag && st < nsteps + ulag) ? ex->nranks : 0);
             tickets += groups * len;
         }
         a.total_tickets = (unsigned)tickets;
+        a.upd_lag = ex->upd_lag;
     }
     a.K = b.Kg; a.Kw = b.K; a.nranks = ex->nranks; a.rank = ex->rank;
     a.divisor = divisor; a.half_divisor = half_divisor;

@@ -218,7 +218,7 @@ class GradientPath:
                                           [int(p) for p in self._px_h.buffer_ptrs],
                                           [int(p) for p in self._pg_h.buffer_ptrs],
                                           [int(p) for p in self._fl_h.buffer_ptrs], max_slots, int(self.exchange_window or 0),
-                                          piece)
+                                          piece, int(os.environ.get("JABAS_EXCHANGE_UPDATE_LAG", 0)))
         if self._exchange_ctas != 0:
             self.exchange.set_ctas_per_sm(self._exchange_ctas)
 

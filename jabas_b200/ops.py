@@ -316,12 +316,13 @@ class Exchange:
     before the first launch on any rank."""
 
     def __init__(self, ctx: Context, nranks: int, rank: int, px: Sequence[int], pg: Sequence[int],
-                 flags: Sequence[int], max_slots: int, window_pieces: int = 0, piece_elems: int = EXCHANGE_PIECE):
+                 flags: Sequence[int], max_slots: int, window_pieces: int = 0, piece_elems: int = EXCHANGE_PIECE,
+                 update_lag: int = 0):
         self.ctx, self.nranks, self.rank = ctx, int(nranks), int(rank)
         self.max_slots, self.window, self.piece = int(max_slots), int(window_pieces), int(piece_elems)
         self._px, self._pg, self._fl = _ptr_array(px), _ptr_array(pg), _ptr_array(flags)
         desc = _lib.ExchangeDesc(self.nranks, self.rank, self._px, self._pg, self._fl, self.max_slots, self.window,
-                                 self.piece, 0)
+                                 self.piece, int(update_lag))
         h = ctypes.c_void_p()
         _lib.check(ctx._lib.jabas_exchange_create(ctx._h, ctypes.byref(desc), ctypes.byref(h)))
         self._h = h

@@ -18,7 +18,7 @@ pytestmark = pytest.mark.gpu
 PIECE = 8192          # a small work item keeps the multi-chunk cases small
 
 
-def _setup(ops, ctx, n_ranks, K, total, window, max_slots=None, seed=0, kw=2):
+def _setup(ops, ctx, n_ranks, K, total, window, max_slots=None, seed=0, kw=2, lag=0):
     rng = np.random.default_rng(seed)
     max_slots = max_slots or max(1, -(-total // PIECE)) + 4
     words = ops.exchange_flag_words(max_slots)
@@ -28,7 +28,7 @@ def _setup(ops, ctx, n_ranks, K, total, window, max_slots=None, seed=0, kw=2):
     pg = [torch.zeros(total, **f32) for _ in range(n_ranks)]
     fl = [torch.zeros(words, dtype=torch.int32, device=dev) for _ in range(n_ranks)]
     exs = [ops.Exchange(ctx, n_ranks, r, [t.data_ptr() for t in px], [t.data_ptr() for t in pg],
-                        [t.data_ptr() for t in fl], max_slots, window, PIECE) for r in range(n_ranks)]
+                        [t.data_ptr() for t in fl], max_slots, window, PIECE, lag) for r in range(n_ranks)]
     w0 = rng.standard_normal(total).astype(np.float32)
     ranks = []
     for r in range(n_ranks):
@@ -101,6 +101,7 @@ def ctx():
     c.close()
 
 
+@pytest.mark.parametrize("lag", [1, 2])             # steps between a piece's reduce and update items
 @pytest.mark.parametrize("n_ranks,K,kind,total,window", [
     (2, 4, "sgd", 3 * 2 * 8192 + 4096 + 8, 2),      # 4 steps of one group, ragged last piece
     (2, 1, "adamw", 40, 4),                         # less than one piece
@@ -113,9 +114,9 @@ def ctx():
     (2, 7, "sgd", 2 * 8192 + 256, 2),               # odd K
     (4, 4, "sgd", 150 * 8192 + 1024, 0),            # many pieces, automatic window
 ])
-def test_exchange_single_gpu_all_ranks_bit_exact(ctx, n_ranks, K, kind, total, window):
+def test_exchange_single_gpu_all_ranks_bit_exact(ctx, n_ranks, K, kind, total, window, lag):
     from jabas_b200 import ops
-    exs, ranks, keep, w0, rng = _setup(ops, ctx, n_ranks, K, total, window, seed=n_ranks * 100 + K)
+    exs, ranks, keep, w0, rng = _setup(ops, ctx, n_ranks, K, total, window, seed=n_ranks * 100 + K, lag=lag)
     T = n_ranks * K
     # two param groups in alternating runs of odd length: tiles straddle segment boundaries
     segments, pos, gi = [], 0, 0
