@@ -37,7 +37,6 @@
 #include "common.cuh"
 
 #include <algorithm>
-#include <cstdlib>
 #include <new>
 #include <vector>
 
@@ -65,7 +64,6 @@ struct ExArgs {
     unsigned int piece, window, nsteps, slot_base, max_slots;   // piece: elements of an item; window: pieces per step
     unsigned int total_tickets;         // length of the queue
     unsigned int upd_lag;               // steps an update item stands behind its reduce item (1 or 2)
-    int held_max;                       // items a CTA may set aside while their flags are not up (0..kHeld)
     int nseg, K, Kw, nranks, rank;
     int opt;                            // OPT_SGD / OPT_ADAM
     int ring_stages, ring_slots;        // shared-memory ring: stages, and 4 KB stream slots per stage
@@ -199,19 +197,10 @@ struct Mail {
     int owner, phase;           // PH_AGG / PH_RED: publish that piece; PH_STOP: leave
 };
 
-// an item whose ticket was drawn before its flags were up (see producer_loop)
-struct HeldItem {
-    unsigned long long lo, hi;  // element range
-    unsigned slot, ticket;
-    int owner, phase;
-};
-constexpr int kHeld = 4;
-
 struct ExShared {
     ExArgs a;
     UpdHp H;
     Mail mail[kMailSlots];
-    HeldItem held[kHeld];
     unsigned mail_head;         // written by consumer thread 0 (release), read by the publisher (acquire)
     volatile unsigned mail_tail;
     unsigned long long full[kExMaxStages];
@@ -223,19 +212,6 @@ struct ExShared {
 };
 
 // ---- producer: one lane ---------------------------------------------------------------------
-// One poll of an item's flags (no waiting): all n aggregate flags of a reduce item's piece, or the
-// reduce flag of an update item's piece.
-__device__ __forceinline__ bool item_ready(const ExArgs& a, const unsigned* flags_local, const HeldItem& it, unsigned epoch)
-{
-    if (it.phase == PH_RED) {
-        const unsigned* f = flags_local + agg_flag_idx(it.slot, 0);
-        for (int r = 0; r < a.nranks; ++r)
-            if ((int)(ld_acquire_sys(f + r) - epoch) < 0) return false;
-        return true;
-    }
-    return (int)(ld_acquire_sys(flags_local + red_flag_idx(a.max_slots, it.slot)) - epoch) >= 0;
-}
-
 __device__ __noinline__ void producer_loop(ExShared& S, unsigned char* ring, unsigned epoch)
 {
     const ExArgs& a = S.a;
@@ -247,7 +223,7 @@ __device__ __noinline__ void producer_loop(ExShared& S, unsigned char* ring, uns
     // needs: a reduce item's flags take about 30 us from the draw of the matching aggregate item
     // (issue, drain of the stores behind the system-scope release, NVLink), and without the lead
     // the reduce items of the first window would be drawn before that.
-    // Steps hold only the phases that have a window to work on (the first and the last steps
+    // Steps hold only the phases that have a window to work on (the first and the last two steps
     // lack some), so no ticket is drawn for nothing: a ticket costs an atomic's round trip.
     const unsigned prologue = a.npieces < a.window ? (unsigned)a.npieces : a.window;
     const unsigned groups = a.window / (unsigned)n;
@@ -268,84 +244,8 @@ __device__ __noinline__ void producer_loop(ExShared& S, unsigned char* ring, uns
     int stage = 0;
     unsigned parity = 0;            // phase of the empty barriers this lane waits for next
     bool ok = true;
-
-    // Bring one item on chip, tile by tile, behind the consumers' progress through the ring.
-    auto issue = [&](const HeldItem& it) {
-        unsigned long long* tr = (a.trace && it.ticket < a.trace_cap) ? a.trace + 6ull * it.ticket : nullptr;
-        if (tr) tr[2] = gtime_ns();
-        for (unsigned long long e0 = it.lo; ok && e0 < it.hi; e0 += kTileElems) {
-            if (!mbar_wait_bounded(&S.empty[stage], parity ^ 1u, 2 * a.wait_ns + 10000000ull)) {
-                record_timeout(a, PH_RING, it.slot);
-                ok = false;
-                break;
-            }
-            const unsigned long long left = it.hi - e0;
-            const unsigned nvec = left >= kTileElems ? (unsigned)kTileVecs : (unsigned)(left >> 2);
-            const unsigned bytes = nvec * 16u;
-            TileDesc& d = S.desc[stage];
-            d.lo = e0; d.nvec = nvec; d.phase = it.phase; d.owner = it.owner; d.slot = it.slot;
-            d.last = e0 + kTileElems >= it.hi;
-            d.ticket = it.ticket;
-            unsigned char* sb = ring + (size_t)stage * stage_bytes;
-            fence_proxy_async_smem();
-            if (it.phase == PH_AGG) {
-                mbar_expect_tx(&S.full[stage], bytes * (unsigned)a.K);
-                for (int k = 0; k < a.K; ++k) bulk_load(sb + k * kTileBytes, a.gk[k] + e0, bytes, &S.full[stage]);
-            } else if (it.phase == PH_RED) {
-                mbar_expect_tx(&S.full[stage], bytes * (unsigned)n);
-                for (int r = 0; r < n; ++r) bulk_load(sb + r * kTileBytes, a.px[r] + e0, bytes, &S.full[stage]);
-            } else {
-                const unsigned ns = 2u + (load_m ? 1u : 0u) + (a.opt == OPT_ADAM ? 1u : 0u);
-                mbar_expect_tx(&S.full[stage], bytes * ns);
-                bulk_load(sb, a.pg[it.owner] + e0, bytes, &S.full[stage]);
-                bulk_load(sb + kTileBytes, a.w[0] + e0, bytes, &S.full[stage]);
-                if (load_m) bulk_load(sb + 2 * kTileBytes, a.m + e0, bytes, &S.full[stage]);
-                if (a.opt == OPT_ADAM) bulk_load(sb + 3 * kTileBytes, a.v + e0, bytes, &S.full[stage]);
-            }
-            if (++stage == a.ring_stages) { stage = 0; parity ^= 1u; }
-        }
-        if (tr) tr[3] = gtime_ns();
-    };
-    // Stand in the wait of an item's flags (bounded), then issue it.
-    auto wait_and_issue = [&](const HeldItem& it) {
-        if (it.phase == PH_RED) ok = wait_epoch_n(flags_local + agg_flag_idx(it.slot, 0), n, epoch, a.wait_ns, status);
-        else ok = wait_epoch(flags_local + red_flag_idx(a.max_slots, it.slot), epoch, a.wait_ns, status);
-        if (!ok) { record_timeout(a, it.phase, it.slot); return; }
-        issue(it);
-    };
-    // Items whose flags were not up when their ticket was drawn are set aside (at most kHeld per
-    // CTA) and the lane draws on; it looks at them again before every draw and stands in a wait
-    // only when the list is full or the queue is empty.  Whatever a held item depends on has a
-    // smaller ticket on its rank, so it has been drawn and is issued, held or waited for by a
-    // resident CTA that never waits on a later ticket: every item is issued in the end.
-    HeldItem* held = S.held;
-    int nheld = 0;
-    auto drop_oldest = [&]() {
-        for (int i = 1; i < nheld; ++i) held[i - 1] = held[i];
-        --nheld;
-    };
-
     unsigned t = atomicAdd(a.ctrl + CTL_QUEUE, 1u);
-    while (ok) {
-        bool issued = false;
-        for (int i = 0; i < nheld; ++i) {
-            if (item_ready(a, flags_local, held[i], epoch)) {
-                const HeldItem it = held[i];
-                for (int j = i + 1; j < nheld; ++j) held[j - 1] = held[j];
-                --nheld;
-                issue(it);
-                issued = true;
-                break;
-            }
-        }
-        if (issued) continue;
-        if (t >= total) {                                   // queue empty (or a wait ran out somewhere)
-            if (nheld == 0 || (t & kQueueAbort)) break;
-            const HeldItem it = held[0];
-            drop_oldest();
-            wait_and_issue(it);
-            continue;
-        }
+    while (ok && t < total) {
         const unsigned nxt = atomicAdd(a.ctrl + CTL_QUEUE, 1u);      // resolves while this item is issued
         int phase;
         long long win;
@@ -386,25 +286,53 @@ __device__ __noinline__ void producer_loop(ExShared& S, unsigned char* ring, uns
         }
         const unsigned long long P = (unsigned long long)(win < 0 ? 0 : win) * a.window + idx;
         if (win >= 0 && win < (long long)a.nsteps && P < a.npieces) {
-            HeldItem it;
-            it.slot = a.slot_base + (unsigned)P;
-            it.owner = (int)(P % (unsigned)n);
-            it.phase = phase;
-            it.ticket = t;
-            it.lo = a.base + P * a.piece;
-            it.hi = it.lo + a.piece;
-            if (it.hi > end) it.hi = end;
+            const unsigned slot = a.slot_base + (unsigned)P;
+            const int owner = (int)(P % (unsigned)n);
+            const unsigned long long lo = a.base + P * a.piece;
+            unsigned long long hi = lo + a.piece;
+            if (hi > end) hi = end;
             unsigned long long* tr = (a.trace && t < a.trace_cap) ? a.trace + 6ull * t : nullptr;
             if (tr) { tr[0] = ((unsigned long long)phase << 56) | ((unsigned long long)blockIdx.x << 32) | (unsigned)P; tr[1] = gtime_ns(); }
-            if (phase == PH_AGG || item_ready(a, flags_local, it, epoch)) issue(it);
-            else if (nheld < a.held_max) held[nheld++] = it;
-            else if (nheld == 0) wait_and_issue(it);
-            else {
-                const HeldItem oldest = held[0];
-                drop_oldest();
-                held[nheld++] = it;
-                wait_and_issue(oldest);
+            if (phase == PH_RED) {
+                ok = wait_epoch_n(flags_local + agg_flag_idx(slot, 0), n, epoch, a.wait_ns, status);
+                if (!ok) record_timeout(a, PH_RED, slot);
+            } else if (phase == PH_UPD) {
+                ok = wait_epoch(flags_local + red_flag_idx(a.max_slots, slot), epoch, a.wait_ns, status);
+                if (!ok) record_timeout(a, PH_UPD, slot);
             }
+            if (tr) tr[2] = gtime_ns();
+            for (unsigned long long e0 = lo; ok && e0 < hi; e0 += kTileElems) {
+                if (!mbar_wait_bounded(&S.empty[stage], parity ^ 1u, 2 * a.wait_ns + 10000000ull)) {
+                    record_timeout(a, PH_RING, slot);
+                    ok = false;
+                    break;
+                }
+                const unsigned long long left = hi - e0;
+                const unsigned nvec = left >= kTileElems ? (unsigned)kTileVecs : (unsigned)(left >> 2);
+                const unsigned bytes = nvec * 16u;
+                TileDesc& d = S.desc[stage];
+                d.lo = e0; d.nvec = nvec; d.phase = phase; d.owner = owner; d.slot = slot;
+                d.last = e0 + kTileElems >= hi;
+                d.ticket = t;
+                unsigned char* sb = ring + (size_t)stage * stage_bytes;
+                fence_proxy_async_smem();
+                if (phase == PH_AGG) {
+                    mbar_expect_tx(&S.full[stage], bytes * (unsigned)a.K);
+                    for (int k = 0; k < a.K; ++k) bulk_load(sb + k * kTileBytes, a.gk[k] + e0, bytes, &S.full[stage]);
+                } else if (phase == PH_RED) {
+                    mbar_expect_tx(&S.full[stage], bytes * (unsigned)n);
+                    for (int r = 0; r < n; ++r) bulk_load(sb + r * kTileBytes, a.px[r] + e0, bytes, &S.full[stage]);
+                } else {
+                    const unsigned ns = 2u + (load_m ? 1u : 0u) + (a.opt == OPT_ADAM ? 1u : 0u);
+                    mbar_expect_tx(&S.full[stage], bytes * ns);
+                    bulk_load(sb, a.pg[owner] + e0, bytes, &S.full[stage]);
+                    bulk_load(sb + kTileBytes, a.w[0] + e0, bytes, &S.full[stage]);
+                    if (load_m) bulk_load(sb + 2 * kTileBytes, a.m + e0, bytes, &S.full[stage]);
+                    if (a.opt == OPT_ADAM) bulk_load(sb + 3 * kTileBytes, a.v + e0, bytes, &S.full[stage]);
+                }
+                if (++stage == a.ring_stages) { stage = 0; parity ^= 1u; }
+            }
+            if (tr) tr[3] = gtime_ns();
         }
         t = nxt;
     }
@@ -788,7 +716,6 @@ struct jabas_exchange {
     int nranks = 0, rank = 0;
     unsigned max_slots = 0, window = 0, piece = JABAS_EXCHANGE_PIECE;
     unsigned upd_lag = 2;                // steps between a piece's reduce item and its update items
-    int held_max = 4;                    // = kHeld
     const float* px[kExMaxRanks] = {};
     const float* pg[kExMaxRanks] = {};
     unsigned int* flags[kExMaxRanks] = {};
@@ -828,7 +755,6 @@ int jabas_exchange_create(jabas_ctx_t* ctx, const jabas_exchange_desc_t* d, jaba
     ex->ctx = ctx; ex->nranks = d->nranks; ex->rank = d->rank; ex->max_slots = d->max_slots;
     ex->window = d->window_pieces;
     ex->upd_lag = d->update_lag ? d->update_lag : 2u;
-    if (const char* e = getenv("JABAS_EXCHANGE_HELD")) ex->held_max = std::min(4, std::max(0, atoi(e)));   // experiment
     ex->piece = d->piece_elems ? d->piece_elems : JABAS_EXCHANGE_PIECE;
     for (int r = 0; r < d->nranks; ++r) {
         if (!d->px[r] || !d->pg[r] || !d->flags[r] || !aligned16(d->px[r]) || !aligned16(d->pg[r]) ||
@@ -971,7 +897,6 @@ static int fill_args(jabas_exchange_t* ex, unsigned grid_ctas, const jabas_excha
         }
         a.total_tickets = (unsigned)tickets;
         a.upd_lag = ex->upd_lag;
-        a.held_max = ex->held_max;
     }
     a.K = b.Kg; a.Kw = b.K; a.nranks = ex->nranks; a.rank = ex->rank;
     a.divisor = divisor; a.half_divisor = half_divisor;
