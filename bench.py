@@ -15,7 +15,8 @@ weights N(0, 1).
 Rank 0 prints ONE JSON line.  ``value`` is samples/sec of the GRADIENT PATH ALONE with the
 gradients resident in HBM (``metric_scope``); ``e2e`` is the same metric with every step's K
 gradient sets copied from pinned host memory and the cosine read back inside the timed region;
-``training_iteration`` is a whole training iteration (forward, backward, path) for context.
+``training_iteration`` is a whole training iteration (forward, backward, path) for context, eager and
+(one GPU, or ``--train-graph``) as one CUDA-graph launch.
 
 Timing: the ``--steps`` steps between two barriers are one sample; the sample is repeated until
 at least half a second of device time has been measured, and ``ms_per_step`` is the median
