@@ -334,15 +334,24 @@ class IIDPTrainer(object):
         if self.binding is None:
             raise RuntimeError("prepare_weight_sync_method() must be called first")
         eng = self.reducer.engine
-        if eng._dyn is None:
+        own_block = eng._dyn is None
+        if own_block:
             eng._dyn = eng.ops.DynHp(eng.ctx)
-        self._iter_graph = dict(warmup=max(1, int(warmup)), seen={}, stream=torch.cuda.Stream(self.device),
+        self._iter_graph = dict(own_block=own_block, warmup=max(1, int(warmup)), seen={}, stream=torch.cuda.Stream(self.device),
                                 graphs={}, launches={}, losses={}, static=None, pool=None, replayed=False)
 
     def disable_iteration_graph(self) -> None:
-        if self._iter_graph is not None and self._cuda:
-            torch.cuda.current_stream(self.device).synchronize()
+        """Back to eager iterations: the graphs go, and the kernels take their hyper-parameters
+        from the launch arguments again."""
+        G = self._iter_graph
+        if G is None:
+            return
+        torch.cuda.synchronize(self.device)
         self._iter_graph = None
+        eng = self.reducer.engine
+        if G["own_block"] and eng._dyn is not None and getattr(eng, "_graph", None) is None:
+            eng._dyn.close()
+            eng._dyn = None
 
     def _drop_iteration_graphs(self) -> None:
         G = self._iter_graph

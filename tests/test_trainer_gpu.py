@@ -481,3 +481,48 @@ def test_iteration_graph_matches_reference_path(wsm, kind, K, interval, lr_step)
     for k in range(1, K + 2):
         assert torch.equal(tr.reducer.engine.weights[k], tr.reducer.engine.weights[0])
     tr.reducer.engine.close()
+
+
+def test_iteration_graph_can_be_switched_off():
+    """After ``disable_iteration_graph`` the trainer runs eagerly again and a changed lr reaches the
+    kernels through the launch arguments (the device-resident block is gone)."""
+    import jabas_b200
+    from jabas_b200.iidp.optim import ShardSGD
+    from oracle.reference_path import ReferencePath
+    K = 2
+    tr = jabas_b200.JABASTrainer(0, 8, K, 0, "overlap", dict(CFG))
+    tr.prepare_stream_parallel(_model(), torch.nn.CrossEntropyLoss().cuda(), bucket_cap_mb=0.05,
+                               first_bucket_bytes=4096)
+    opt = ShardSGD(_groups(tr.main_model), lr=0.1, momentum=0.9)
+    tr.prepare_weight_sync_method(opt, None, _groups)
+    tr.set_model_train()
+    od = _opt_dict("sgd")
+    ref = ReferencePath(tr.reducer.layout, K, od, total_num_decoupled_workers=K, arith="c")
+    for k in range(K):
+        ref.weights[k].copy_(tr.reducer.engine.weights[k].cpu())
+    captured = _capture_vsw_gradients(tr)
+    lay, eng = tr.reducer.layout, tr.reducer.engine
+    g = torch.Generator().manual_seed(9)
+    tr.enable_iteration_graph(warmup=1)
+    static = None
+    for it in range(6):
+        if it == 4:
+            tr.disable_iteration_graph()
+            assert tr._iter_graph is None and eng._dyn is None
+            for gr, go in zip(opt.param_groups, od["groups"]):
+                gr["lr"] *= 0.25
+                go["lr"] *= 0.25
+        x = torch.randn(8 * K, 3, 16, 16, generator=g).cuda()
+        y = torch.randint(0, 10, (8 * K,), generator=g).cuda()
+        tr.compute((x, y))
+        replayed = tr._iter_graph is not None and tr._iter_graph["replayed"]
+        tr.step()
+        torch.cuda.synchronize()
+        if replayed and static is None:
+            static = dict(captured)
+        for (k, b), t in (static if replayed else captured).items():
+            ref.grads[k][lay.buckets[b][0]:lay.buckets[b][1]].copy_(t.cpu())
+        ref.run_iteration()
+        assert torch.equal(eng.weights[K - 1].cpu(), ref.weights[0]), (it, replayed)
+    assert static is not None
+    eng.close()
