@@ -12,7 +12,8 @@
 // reduced by rank P mod n).  A piece of one phase is one work item.  Items stand in a queue
 // ordered by pipeline step s = 0, 1, ...: with windows of W pieces, step s holds the aggregate
 // items of window s, this rank's reduce items of window s-1 and the update items of window s-3
-// (s-2 with update_lag 1), interleaved (one reduce item, then aggregate and update items in turn), so that at any moment
+// (s-2 with update_lag 1), interleaved (one reduce item, then aggregate and update items in
+// turn), so that at any moment
 // the resident CTAs work on NVLink-bound and HBM-bound items together and the two resources
 // overlap (the aggregate items run one window further ahead than this sketch says, see
 // producer_loop).  CTAs draw items with an atomic ticket, in queue order.
@@ -27,13 +28,15 @@
 // item takes about 40 us from its draw to the moment its flag is visible on the other GPUs — wait,
 // issue, drain, 20-30 us of system-scope release under full HBM load —, more than one step of a
 // ResNet-50-sized launch; with one step of distance the update items waited 6 us on average and
-// 25-33 us at the 95th percentile, with two 3 us and 17-20 us).  Every wait is bounded by wall time; a wait that
+// 25-33 us at the 95th percentile, with two 3 us and 17-20 us).  Every wait is bounded by wall
+// time; a wait that
 // runs out records (phase, slot) in a status word, all CTAs of the launch drain, and the host
 // reads the status — the kernel never traps and never spins for ever.
 //
 // Summation order is fixed (VSWs ascending, then ranks ascending, each term divided by T first:
 // the reference's div_(T) before the SUM allreduce), so every rank computes bit-identical
-// gradients and weights.  Plain peer loads and stores only: no multicast, no TMA.
+// gradients and weights.  Tiles come on chip by bulk copies without multicast (cp.async.bulk,
+// from local or peer memory), flags go out as plain peer stores: no multicast anywhere.
 #include "common.cuh"
 
 #include <algorithm>
